@@ -1,0 +1,314 @@
+"""Python access to libbkm.so - the B200 k-means iteration library (C ABI in include/bkm.h).
+
+This module is a thin ctypes binding plus `KMeans`, a class with the call sequence of the
+reference's IKMeansAlgorithm (experimental/k-means/k-means/headers/interface.hpp:8-49 of
+krulis-martin/cuda-kmeans): initialize / run / getMeans / getAssignment / cleanup.  All
+computation happens in the CUDA library; there is no Python or CPU fallback, and importing
+works without a GPU only so that the binding itself can be checked.
+
+The directory name contains a hyphen, so load it with importlib (see `load()` in
+__graft_entry__.py) or put the directory itself on sys.path under another name.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libbkm.so")
+
+OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_UNSUPPORTED, ERR_STATE, ERR_DEVICE = range(7)
+LAYOUT_AOS, LAYOUT_SOA = 0, 1
+ASSIGN_AUTO, ASSIGN_EXACT, ASSIGN_SIMT, ASSIGN_TC = 0, 1, 2, 3
+UPDATE_AUTO, UPDATE_SHARED, UPDATE_GLOBAL = 0, 1, 2
+ASSIGN_NAMES = {ASSIGN_AUTO: "auto", ASSIGN_EXACT: "exact", ASSIGN_SIMT: "simt", ASSIGN_TC: "tc"}
+UPDATE_NAMES = {UPDATE_AUTO: "auto", UPDATE_SHARED: "shared", UPDATE_GLOBAL: "global"}
+
+# Every symbol include/bkm.h declares (the CPU test suite checks the library exports them all).
+SYMBOLS = [
+    "bkm_last_error", "bkm_version", "bkm_device_count", "bkm_workspace_bytes", "bkm_assign_f32",
+    "bkm_update_f32", "bkm_iterate_f32", "bkm_workspace_check", "bkm_create", "bkm_destroy",
+    "bkm_set_stream", "bkm_set_option", "bkm_initialize", "bkm_initialize_device", "bkm_run",
+    "bkm_run_async", "bkm_synchronize", "bkm_get_means", "bkm_get_assignment", "bkm_get_sizes",
+    "bkm_device_means", "bkm_device_assignment", "bkm_set_means", "bkm_iterations_done",
+    "bkm_phase_ms", "bkm_counters", "bkm_comm_unique_id", "bkm_comm_init", "bkm_shard_range",
+    "bkm_kmeans_host_f32",
+]
+
+
+class BkmError(RuntimeError):
+    """A libbkm call returned a non-zero status; `.code` holds it."""
+
+    def __init__(self, code, message):
+        super().__init__("libbkm error %d: %s" % (code, message))
+        self.code = code
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("n", ctypes.c_uint64), ("k", ctypes.c_uint32), ("dim", ctypes.c_uint32),
+        ("layout", ctypes.c_int32), ("layout_means", ctypes.c_int32), ("device", ctypes.c_int32),
+        ("variant_assign", ctypes.c_int32), ("variant_update", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded C library.  Fails loudly when it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("%s is missing - build it with `python cuda-kmeans_b200/build.py` "
+                          "(or __graft_entry__.build()); there is no fallback path" % LIB_PATH)
+    L = ctypes.CDLL(LIB_PATH)
+    vp, u64, u32, ci, sz = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int, ctypes.c_size_t
+    L.bkm_last_error.restype = ctypes.c_char_p
+    L.bkm_last_error.argtypes = []
+    L.bkm_version.restype = ci
+    L.bkm_device_count.restype = ci
+    L.bkm_workspace_bytes.restype = sz
+    L.bkm_workspace_bytes.argtypes = [u64, u32, u32]
+    L.bkm_assign_f32.argtypes = [vp, vp, vp, u64, u32, u32, ci, ci, ci, vp, sz, vp]
+    L.bkm_update_f32.argtypes = [vp, vp, vp, vp, u64, u32, u32, ci, ci, ci, vp, sz, vp]
+    L.bkm_iterate_f32.argtypes = [vp, vp, vp, vp, vp, u64, u32, u32, ci, ci, ci, ci, vp, sz, vp]
+    L.bkm_workspace_check.argtypes = [vp, vp]
+    L.bkm_create.argtypes = [ctypes.POINTER(Config), ctypes.POINTER(vp)]
+    L.bkm_destroy.argtypes = [vp]
+    L.bkm_set_stream.argtypes = [vp, vp]
+    L.bkm_set_option.argtypes = [vp, ctypes.c_char_p, ctypes.c_double]
+    L.bkm_initialize.argtypes = [vp, vp, vp]
+    L.bkm_initialize_device.argtypes = [vp, vp, vp]
+    L.bkm_run.argtypes = [vp, u32]
+    L.bkm_run_async.argtypes = [vp, u32]
+    L.bkm_synchronize.argtypes = [vp]
+    L.bkm_get_means.argtypes = [vp, vp]
+    L.bkm_get_assignment.argtypes = [vp, vp]
+    L.bkm_get_sizes.argtypes = [vp, vp]
+    L.bkm_device_means.argtypes = [vp, ctypes.POINTER(vp)]
+    L.bkm_device_assignment.argtypes = [vp, ctypes.POINTER(vp)]
+    L.bkm_set_means.argtypes = [vp, vp]
+    L.bkm_iterations_done.argtypes = [vp, ctypes.POINTER(u64)]
+    L.bkm_phase_ms.argtypes = [vp, ctypes.POINTER(ctypes.c_float)]
+    L.bkm_counters.argtypes = [vp, ctypes.POINTER(u64)]
+    L.bkm_comm_unique_id.argtypes = [vp, sz]
+    L.bkm_comm_init.argtypes = [vp, vp, sz, ci, ci]
+    L.bkm_shard_range.argtypes = [u64, ci, ci, ctypes.POINTER(u64), ctypes.POINTER(u64)]
+    L.bkm_kmeans_host_f32.argtypes = [vp, vp, vp, u64, u32, u32, u32, ci, ci, ci]
+    for name in SYMBOLS:
+        fn = getattr(L, name)
+        if name not in ("bkm_last_error", "bkm_workspace_bytes"):
+            fn.restype = ci
+    _lib = L
+    return L
+
+
+def check(rc):
+    if rc != OK:
+        raise BkmError(rc, lib().bkm_last_error().decode("utf-8", "replace"))
+
+
+def device_count():
+    return lib().bkm_device_count()
+
+
+def workspace_bytes(n, k, dim):
+    return lib().bkm_workspace_bytes(n, k, dim)
+
+
+def shard_range(n_total, world_size, rank):
+    """(begin, count) of the contiguous shard of `rank` (pure host arithmetic)."""
+    b, c = ctypes.c_uint64(), ctypes.c_uint64()
+    check(lib().bkm_shard_range(n_total, world_size, rank, ctypes.byref(b), ctypes.byref(c)))
+    return b.value, c.value
+
+
+def comm_unique_id():
+    """128 bytes identifying a new NCCL communicator (rank 0 creates, all ranks receive)."""
+    buf = ctypes.create_string_buffer(128)
+    check(lib().bkm_comm_unique_id(buf, 128))
+    return buf.raw
+
+
+# ---- kernel-runner entry points on raw device pointers (ints) -------------------------------
+
+def assign(points, means, assignment, n, k, dim, layout, layout_means, workspace, workspace_size,
+           variant=ASSIGN_AUTO, stream=0):
+    check(lib().bkm_assign_f32(points, means, assignment, n, k, dim, layout, layout_means, variant,
+                               workspace, workspace_size, stream))
+
+
+def update(points, assignment, means, sizes, n, k, dim, layout, layout_means, workspace, workspace_size,
+           variant=UPDATE_AUTO, stream=0):
+    check(lib().bkm_update_f32(points, assignment, means, sizes, n, k, dim, layout, layout_means, variant,
+                               workspace, workspace_size, stream))
+
+
+def iterate(points, means_in, means_out, sizes, assignment, n, k, dim, layout, layout_means,
+            workspace, workspace_size, variant_assign=ASSIGN_AUTO, variant_update=UPDATE_AUTO, stream=0):
+    check(lib().bkm_iterate_f32(points, means_in, means_out, sizes, assignment, n, k, dim, layout,
+                                layout_means, variant_assign, variant_update, workspace, workspace_size, stream))
+
+
+def workspace_check(workspace, stream=0):
+    check(lib().bkm_workspace_check(workspace, stream))
+
+
+def kmeans_host(points, means, n, k, dim, iters, layout=LAYOUT_AOS, layout_means=None, device=0):
+    """Whole job on HOST arrays (bkm_kmeans_host_f32): returns (final means, assignment)."""
+    layout_means = layout if layout_means is None else layout_means
+    pts = np.ascontiguousarray(points, dtype=np.float32).reshape(-1)
+    out_means = np.ascontiguousarray(means, dtype=np.float32).reshape(-1).copy()
+    if pts.size != n * dim or out_means.size != k * dim:
+        raise ValueError("array sizes do not match n, k, dim")
+    asg = np.empty(n, dtype=np.uint32)
+    check(lib().bkm_kmeans_host_f32(pts.ctypes.data, out_means.ctypes.data, asg.ctypes.data,
+                                    n, k, dim, iters, layout, layout_means, device))
+    return out_means, asg
+
+
+class KMeans:
+    """Fixed-iteration k-means on one GPU (or one rank's shard), over the driver handle.
+
+    Mirrors IKMeansAlgorithm / CudaKMeansAlgorithm of the reference
+    (headers/interface.hpp:8-49, headers/cuda.hpp:19-112): `initialize` uploads data and
+    initial means, `run` performs the configured number of iterations, `getMeans` /
+    `getAssignment` fetch the results, `cleanup` releases the device state.
+    """
+
+    def __init__(self, layout=LAYOUT_AOS, layout_means=None, device=0, variant_assign=ASSIGN_AUTO,
+                 variant_update=UPDATE_AUTO):
+        self.layout = layout
+        self.layout_means = layout if layout_means is None else layout_means
+        self.device = device
+        self.variant_assign = variant_assign
+        self.variant_update = variant_update
+        self._h = None
+        self.dim = self.k = self.n = 0
+        self.iters = 1
+        self._options = {}
+        self._stream = None
+
+    # -- reference-style interface --
+    def initialize(self, dim, k, n, iters, data, means):
+        """`data`/`means`: host numpy arrays in the configured layouts (n*dim and k*dim floats)."""
+        self._create(dim, k, n, iters)
+        pts = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        mns = np.ascontiguousarray(means, dtype=np.float32).reshape(-1)
+        if pts.size != n * dim or mns.size != k * dim:
+            raise ValueError("array sizes do not match n, k, dim")
+        check(lib().bkm_initialize(self._h, pts.ctypes.data, mns.ctypes.data))
+
+    def initialize_device(self, dim, k, n, iters, data_ptr, means_ptr):
+        """Same with device pointers (ints); the points are borrowed and must stay alive."""
+        self._create(dim, k, n, iters)
+        check(lib().bkm_initialize_device(self._h, data_ptr, means_ptr))
+
+    def run(self, iters=None):
+        check(lib().bkm_run(self._need(), self.iters if iters is None else iters))
+
+    def run_async(self, iters=None):
+        check(lib().bkm_run_async(self._need(), self.iters if iters is None else iters))
+
+    def synchronize(self):
+        check(lib().bkm_synchronize(self._need()))
+
+    def getMeans(self):
+        out = np.empty(self.k * self.dim, dtype=np.float32)
+        check(lib().bkm_get_means(self._need(), out.ctypes.data))
+        return out
+
+    def getAssignment(self):
+        out = np.empty(self.n, dtype=np.uint32)
+        check(lib().bkm_get_assignment(self._need(), out.ctypes.data))
+        return out
+
+    def getSizes(self):
+        out = np.empty(self.k, dtype=np.uint32)
+        check(lib().bkm_get_sizes(self._need(), out.ctypes.data))
+        return out
+
+    def getIterations(self):
+        return self.iters
+
+    def cleanup(self):
+        if self._h is not None:
+            lib().bkm_destroy(self._h)
+            self._h = None
+
+    # -- extras --
+    def set_means(self, means):
+        mns = np.ascontiguousarray(means, dtype=np.float32).reshape(-1)
+        if mns.size != self.k * self.dim:
+            raise ValueError("means size does not match k*dim")
+        check(lib().bkm_set_means(self._need(), mns.ctypes.data))
+
+    def set_option(self, name, value):
+        self._options[name] = float(value)
+        if self._h is not None:
+            check(lib().bkm_set_option(self._h, name.encode(), float(value)))
+
+    def set_stream(self, stream_ptr):
+        self._stream = stream_ptr
+        if self._h is not None:
+            check(lib().bkm_set_stream(self._h, stream_ptr))
+
+    def comm_init(self, unique_id, world_size, rank):
+        buf = ctypes.create_string_buffer(bytes(unique_id), 128)
+        check(lib().bkm_comm_init(self._need(), buf, 128, world_size, rank))
+
+    def device_means(self):
+        p = ctypes.c_void_p()
+        check(lib().bkm_device_means(self._need(), ctypes.byref(p)))
+        return p.value
+
+    def device_assignment(self):
+        p = ctypes.c_void_p()
+        check(lib().bkm_device_assignment(self._need(), ctypes.byref(p)))
+        return p.value
+
+    def iterations_done(self):
+        v = ctypes.c_uint64()
+        check(lib().bkm_iterations_done(self._need(), ctypes.byref(v)))
+        return v.value
+
+    def phase_ms(self):
+        """dict of mean device milliseconds per phase over the most recent run."""
+        arr = (ctypes.c_float * 6)()
+        check(lib().bkm_phase_ms(self._need(), arr))
+        names = ["assign", "recheck", "update", "allreduce", "finalize", "iteration"]
+        return dict(zip(names, [float(x) for x in arr]))
+
+    def counters(self):
+        arr = (ctypes.c_uint64 * 4)()
+        check(lib().bkm_counters(self._need(), arr))
+        return {"rechecked": int(arr[0]), "launches_per_iter": int(arr[1]),
+                "assign_variant": ASSIGN_NAMES.get(int(arr[2]), "?"),
+                "update_variant": UPDATE_NAMES.get(int(arr[3]), "?")}
+
+    def _create(self, dim, k, n, iters):
+        self.cleanup()
+        self.dim, self.k, self.n, self.iters = int(dim), int(k), int(n), int(iters)
+        cfg = Config(n=self.n, k=self.k, dim=self.dim, layout=self.layout, layout_means=self.layout_means,
+                     device=self.device, variant_assign=self.variant_assign,
+                     variant_update=self.variant_update, reserved=0)
+        h = ctypes.c_void_p()
+        check(lib().bkm_create(ctypes.byref(cfg), ctypes.byref(h)))
+        self._h = h
+        if self._stream is not None:
+            check(lib().bkm_set_stream(self._h, self._stream))
+        for name, value in self._options.items():
+            check(lib().bkm_set_option(self._h, name.encode(), value))
+
+    def _need(self):
+        if self._h is None:
+            raise BkmError(ERR_STATE, "initialize() has not been called")
+        return self._h
+
+    def __del__(self):
+        try:
+            self.cleanup()
+        except Exception:
+            pass

@@ -1,0 +1,744 @@
+// Host side of libbkm.so: the C ABI declared in include/bkm.h, the fixed-iteration driver and
+// the NCCL exchange of the per-iteration sums and sizes.  Mirrors the call sequence of the
+// reference's CudaKMeansAlgorithm (headers/cuda.hpp:45-112 of krulis-martin/cuda-kmeans):
+// initialize copies data and means to the device, run loops assignment -> update with the
+// means double-buffered, results are fetched afterwards.
+#include "../../include/bkm.h"
+#include "kernels.cuh"
+
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int code, const char* fmt, ...)
+{
+	char buf[512];
+	va_list ap;
+	va_start(ap, fmt);
+	vsnprintf(buf, sizeof(buf), fmt, ap);
+	va_end(ap);
+	g_error = buf;
+	return code;
+}
+
+#define CUDA_TRY(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) \
+	return fail(BKM_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
+
+bool layout_ok(int l) { return l == BKM_LAYOUT_AOS || l == BKM_LAYOUT_SOA; }
+
+// ---- NCCL, resolved at run time so that the library loads on machines without it ----------
+
+typedef struct { char internal[128]; } nccl_unique_id;
+struct Nccl {
+	void* lib = nullptr;
+	int (*GetUniqueId)(nccl_unique_id*) = nullptr;
+	int (*CommInitRank)(void**, int, nccl_unique_id, int) = nullptr;
+	int (*CommDestroy)(void*) = nullptr;
+	int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+	int (*GroupStart)() = nullptr;
+	int (*GroupEnd)() = nullptr;
+	const char* (*GetErrorString)(int) = nullptr;
+	bool ok = false;
+};
+constexpr int NCCL_UINT32 = 3, NCCL_FLOAT32 = 7, NCCL_SUM = 0;
+
+Nccl* nccl()
+{
+	static Nccl inst;
+	static bool tried = false;
+	if (!tried) {
+		tried = true;
+		// RTLD_NOLOAD first: reuse the copy a host application (e.g. PyTorch) already loaded.
+		void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+		if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+		if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+		if (lib) {
+			inst.lib = lib;
+			inst.GetUniqueId = reinterpret_cast<decltype(inst.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+			inst.CommInitRank = reinterpret_cast<decltype(inst.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+			inst.CommDestroy = reinterpret_cast<decltype(inst.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+			inst.AllReduce = reinterpret_cast<decltype(inst.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+			inst.GroupStart = reinterpret_cast<decltype(inst.GroupStart)>(dlsym(lib, "ncclGroupStart"));
+			inst.GroupEnd = reinterpret_cast<decltype(inst.GroupEnd)>(dlsym(lib, "ncclGroupEnd"));
+			inst.GetErrorString = reinterpret_cast<decltype(inst.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+			inst.ok = inst.GetUniqueId && inst.CommInitRank && inst.CommDestroy && inst.AllReduce &&
+				inst.GroupStart && inst.GroupEnd && inst.GetErrorString;
+		}
+	}
+	return &inst;
+}
+
+#define NCCL_TRY(expr) do { int r_ = (expr); if (r_ != 0) \
+	return fail(BKM_ERR_NCCL, "%s failed: %s", #expr, nccl()->GetErrorString(r_)); } while (0)
+
+// ---- workspace carving ----------------------------------------------------------------------
+
+struct Workspace {
+	bkm::Control* ctl = nullptr;
+	float* acc = nullptr;          // k*dim sums
+	uint32_t* counts = nullptr;    // k sizes (directly behind acc)
+	float* cprep = nullptr;        // CUDA-core rows
+	size_t cprep_bytes = 0;
+	bkm::TcMeans tm{};
+	size_t tm_bytes = 0;           // b_hi + b_lo
+	uint32_t* flag_list = nullptr; // n entries
+	uint32_t* asg_scratch = nullptr; // n entries (iterate without an assignment output)
+	bkm::TcPoints tp{};
+	size_t bytes = 0;
+};
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Lays the workspace out behind `base` (may be null: only the size is computed).
+Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_points)
+{
+	Workspace w;
+	size_t off = 0;
+	auto take = [&](size_t bytes) -> char* {
+		char* p = base ? base + off : nullptr;
+		off += align256(bytes);
+		return p;
+	};
+	w.ctl = reinterpret_cast<bkm::Control*>(take(sizeof(bkm::Control)));
+	const size_t kd = (size_t)k * dim;
+	char* accp = take(kd * sizeof(float) + (size_t)k * sizeof(uint32_t));
+	w.acc = reinterpret_cast<float*>(accp);
+	w.counts = accp ? reinterpret_cast<uint32_t*>(accp + kd * sizeof(float)) : nullptr;
+	w.cprep_bytes = (size_t)bkm::simt_rows(k) * bkm::simt_row_stride(dim) * sizeof(float);
+	w.cprep = reinterpret_cast<float*>(take(w.cprep_bytes));
+	w.tm.k_pad = bkm::tc_kpad(k);
+	w.tm.d_pad = bkm::tc_dpad(dim);
+	const size_t plane = (size_t)w.tm.k_pad * w.tm.d_pad * sizeof(float);
+	w.tm_bytes = 2 * align256(plane);
+	w.tm.b_hi = reinterpret_cast<float*>(take(plane));
+	w.tm.b_lo = reinterpret_cast<float*>(take(plane));
+	w.tm.cnorm = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * sizeof(float)));
+	w.flag_list = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
+	w.asg_scratch = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
+	if (with_tc_points) {
+		w.tp.n_pad = bkm::round_up64(n, bkm::TC_MTILE);
+		w.tp.d_pad = w.tm.d_pad;
+		const size_t aplane = (size_t)w.tp.n_pad * w.tp.d_pad * sizeof(float);
+		w.tp.a_hi = reinterpret_cast<float*>(take(aplane));
+		w.tp.a_lo = reinterpret_cast<float*>(take(aplane));
+		w.tp.xnorm = reinterpret_cast<float*>(take((size_t)w.tp.n_pad * sizeof(float)));
+	}
+	w.bytes = off;
+	return w;
+}
+
+int device_sm_count(int device, int* out)
+{
+	CUDA_TRY(cudaDeviceGetAttribute(out, cudaDevAttrMultiProcessorCount, device));
+	return BKM_OK;
+}
+
+int resolve_assign(int variant, const bkm::Shape& s, int* out)
+{
+	switch (variant) {
+	case BKM_ASSIGN_AUTO:
+		if (bkm::assign_simt_supported(s)) *out = BKM_ASSIGN_SIMT;
+		else if (bkm::assign_tc_supported(s)) *out = BKM_ASSIGN_TC;
+		else *out = BKM_ASSIGN_EXACT;
+		return BKM_OK;
+	case BKM_ASSIGN_EXACT:
+		*out = variant;
+		return BKM_OK;
+	case BKM_ASSIGN_SIMT:
+		if (!bkm::assign_simt_supported(s)) return fail(BKM_ERR_UNSUPPORTED, "the SIMT assignment handles dim 1..8 only (dim=%u)", s.dim);
+		*out = variant;
+		return BKM_OK;
+	case BKM_ASSIGN_TC:
+		if (!bkm::assign_tc_supported(s)) return fail(BKM_ERR_UNSUPPORTED, "the tensor-core assignment does not handle n=%llu k=%u dim=%u",
+			(unsigned long long)s.n, s.k, s.dim);
+		*out = variant;
+		return BKM_OK;
+	default:
+		return fail(BKM_ERR_INVALID, "unknown assignment variant %d", variant);
+	}
+}
+
+int resolve_update(int variant, const bkm::Shape& s, int device, int* out)
+{
+	switch (variant) {
+	case BKM_UPDATE_AUTO:
+		*out = bkm::update_shared_fits(s, device) ? BKM_UPDATE_SHARED : BKM_UPDATE_GLOBAL;
+		return BKM_OK;
+	case BKM_UPDATE_SHARED:
+		if (!bkm::update_shared_fits(s, device)) return fail(BKM_ERR_UNSUPPORTED, "k*dim = %llu floats do not fit shared memory",
+			(unsigned long long)s.k * s.dim);
+		*out = variant;
+		return BKM_OK;
+	case BKM_UPDATE_GLOBAL:
+		*out = variant;
+		return BKM_OK;
+	default:
+		return fail(BKM_ERR_INVALID, "unknown update variant %d", variant);
+	}
+}
+
+int check_shape(uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means)
+{
+	if (n == 0 || k == 0 || dim == 0) return fail(BKM_ERR_INVALID, "n, k and dim must be positive (n=%llu k=%u dim=%u)",
+		(unsigned long long)n, k, dim);
+	if (n >= (1ull << 32)) return fail(BKM_ERR_UNSUPPORTED, "at most 2^32-1 points per GPU (n=%llu)", (unsigned long long)n);
+	if ((uint64_t)k * dim >= (1ull << 31)) return fail(BKM_ERR_UNSUPPORTED, "k*dim must stay below 2^31");
+	if (!layout_ok(layout) || !layout_ok(layout_means)) return fail(BKM_ERR_INVALID, "unknown layout code");
+	return BKM_OK;
+}
+
+// Enqueues one assignment pass (fast pass + exact re-check, or the exact kernel alone).
+int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* asg, const bkm::Shape& s,
+	const Workspace& w, int slot, bkm::TcPlan* plan, float margin_scale, int sm_count, cudaStream_t stream,
+	cudaEvent_t mid)
+{
+	if (variant == BKM_ASSIGN_EXACT) {
+		CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, nullptr, nullptr, sm_count, stream));
+		if (mid) CUDA_TRY(cudaEventRecord(mid, stream));
+		return BKM_OK;
+	}
+	if (variant == BKM_ASSIGN_SIMT) {
+		CUDA_TRY(bkm::launch_assign_simt(pts, w.cprep, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream));
+	} else {
+		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream));
+	}
+	if (mid) CUDA_TRY(cudaEventRecord(mid, stream));
+	CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, w.flag_list, &w.ctl->flag_count, sm_count, stream));
+	return BKM_OK;
+}
+
+} // namespace
+
+// ---------------------------------------------------------------------------------------------
+
+struct bkm_handle_s {
+	bkm_config_t cfg{};
+	bkm::Shape shape{};
+	int sm_count = 0;
+	cudaStream_t stream = nullptr;
+	cudaStream_t own_stream = nullptr;
+	const float* d_points = nullptr;
+	float* d_points_owned = nullptr;
+	float* d_means[2] = {nullptr, nullptr};
+	uint32_t* d_asg = nullptr;
+	uint32_t* d_sizes = nullptr;
+	char* d_ws = nullptr;
+	Workspace ws;
+	bkm::TcPlan* plan = nullptr;
+	int assign_variant = 0, update_variant = 0;
+	int cur = 0, slot = 0;
+	bool initialized = false;
+	uint64_t iters_done = 0;
+	float margin_scale = 1.0f;
+	bool phase_timing = true;
+	// NCCL
+	void* comm = nullptr;
+	int world = 1, rank = 0;
+	// phase events of the most recent run
+	static constexpr int EV_RING = 256, EV_PER = 6;
+	cudaEvent_t ev[EV_RING][EV_PER] = {};
+	bool ev_made = false;
+	uint32_t ev_count = 0;
+	uint32_t launches_per_iter = 0;
+};
+
+extern "C" {
+
+const char* bkm_last_error(void) { return g_error.c_str(); }
+
+int bkm_version(void) { return 100; }
+
+int bkm_device_count(void)
+{
+	int n = 0;
+	if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+	return n;
+}
+
+size_t bkm_workspace_bytes(uint64_t n, uint32_t k, uint32_t dim)
+{
+	if (n == 0 || k == 0 || dim == 0 || n >= (1ull << 32) || (uint64_t)k * dim >= (1ull << 31)) return 0;
+	return carve(nullptr, n, k, dim, true).bytes;
+}
+
+int bkm_shard_range(uint64_t n_total, int world_size, int rank, uint64_t* begin, uint64_t* count)
+{
+	if (world_size <= 0 || rank < 0 || rank >= world_size || !begin || !count)
+		return fail(BKM_ERR_INVALID, "bad shard arguments (world_size=%d rank=%d)", world_size, rank);
+	const uint64_t base = n_total / (uint64_t)world_size, rem = n_total % (uint64_t)world_size;
+	const uint64_t r = (uint64_t)rank;
+	*begin = r * base + std::min<uint64_t>(r, rem);
+	*count = base + (r < rem ? 1 : 0);
+	return BKM_OK;
+}
+
+// ---- kernel-runner entry points ---------------------------------------------------------------
+
+static int stateless_common(uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means,
+	void* workspace, size_t workspace_bytes, bkm::Shape* s, Workspace* w, int* device, int* sm_count)
+{
+	int rc = check_shape(n, k, dim, layout, layout_means);
+	if (rc) return rc;
+	if (!workspace) return fail(BKM_ERR_INVALID, "workspace is null");
+	if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(BKM_ERR_INVALID, "workspace must be 256-byte aligned");
+	*w = carve(static_cast<char*>(workspace), n, k, dim, true);
+	if (workspace_bytes < w->bytes) return fail(BKM_ERR_INVALID, "workspace too small: %zu < %zu bytes", workspace_bytes, w->bytes);
+	s->n = n; s->k = k; s->dim = dim; s->soa = layout == BKM_LAYOUT_SOA; s->soa_means = layout_means == BKM_LAYOUT_SOA;
+	CUDA_TRY(cudaGetDevice(device));
+	return device_sm_count(*device, sm_count);
+}
+
+static int stateless_assign(const float* points, const float* means, uint32_t* assignment, const bkm::Shape& s,
+	const Workspace& w, int variant, int device, int sm_count, cudaStream_t st)
+{
+	int v = 0;
+	int rc = resolve_assign(variant, s, &v);
+	if (rc) return rc;
+	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	bkm::TcPlan* plan = nullptr;
+	if (v == BKM_ASSIGN_SIMT) {
+		CUDA_TRY(cudaMemsetAsync(w.cprep, 0, w.cprep_bytes, st));
+		bkm::launch_prepare_means(means, s, w.cprep, nullptr, w.ctl, 0, st);
+	} else if (v == BKM_ASSIGN_TC) {
+		CUDA_TRY(cudaMemsetAsync(w.tm.b_hi, 0, w.tm_bytes, st));
+		bkm::launch_prepare_means(means, s, nullptr, &w.tm, w.ctl, 0, st);
+		CUDA_TRY(bkm::launch_split_points(points, s, w.tp, st));
+		const char* err = nullptr;
+		plan = bkm::tc_plan_create(s, w.tp, w.tm, device, &err);
+		if (!plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
+	}
+	CUDA_TRY(cudaGetLastError());
+	rc = enqueue_assign(v, points, means, assignment, s, w, 0, plan, 1.0f, sm_count, st, nullptr);
+	if (plan) bkm::tc_plan_destroy(plan);   // tensor maps are copied into the launch parameters
+	return rc;
+}
+
+static int stateless_update(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
+	const bkm::Shape& s, const Workspace& w, int variant, int device, int sm_count, cudaStream_t st, bool clear_ctl)
+{
+	int v = 0;
+	int rc = resolve_update(variant, s, device, &v);
+	if (rc) return rc;
+	if (clear_ctl) CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	CUDA_TRY(cudaMemsetAsync(w.acc, 0, (size_t)s.k * s.dim * sizeof(float) + (size_t)s.k * sizeof(uint32_t), st));
+	bkm::launch_update(points, assignment, w.acc, w.counts, s, v, w.ctl, sm_count, st);
+	bkm::launch_finalize(w.acc, w.counts, means, sizes, s, nullptr, nullptr, w.ctl, 1, st);
+	CUDA_TRY(cudaGetLastError());
+	return BKM_OK;
+}
+
+int bkm_assign_f32(const float* points, const float* means, uint32_t* assignment,
+	uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means,
+	int variant, void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!points || !means || !assignment) return fail(BKM_ERR_INVALID, "null pointer argument");
+	bkm::Shape s; Workspace w; int device = 0, sm = 0;
+	int rc = stateless_common(n, k, dim, layout, layout_means, workspace, workspace_bytes, &s, &w, &device, &sm);
+	if (rc) return rc;
+	return stateless_assign(points, means, assignment, s, w, variant, device, sm, static_cast<cudaStream_t>(stream));
+}
+
+int bkm_update_f32(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
+	uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means,
+	int variant, void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!points || !means || !assignment || !sizes) return fail(BKM_ERR_INVALID, "null pointer argument");
+	bkm::Shape s; Workspace w; int device = 0, sm = 0;
+	int rc = stateless_common(n, k, dim, layout, layout_means, workspace, workspace_bytes, &s, &w, &device, &sm);
+	if (rc) return rc;
+	return stateless_update(points, assignment, means, sizes, s, w, variant, device, sm, static_cast<cudaStream_t>(stream), true);
+}
+
+int bkm_iterate_f32(const float* points, const float* means_in, float* means_out, uint32_t* sizes,
+	uint32_t* assignment, uint64_t n, uint32_t k, uint32_t dim, int layout,
+	int layout_means, int variant_assign, int variant_update,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!points || !means_in || !means_out || !sizes) return fail(BKM_ERR_INVALID, "null pointer argument");
+	if (means_in == means_out) return fail(BKM_ERR_INVALID, "means_in and means_out must differ");
+	bkm::Shape s; Workspace w; int device = 0, sm = 0;
+	int rc = stateless_common(n, k, dim, layout, layout_means, workspace, workspace_bytes, &s, &w, &device, &sm);
+	if (rc) return rc;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	uint32_t* asg = assignment ? assignment : w.asg_scratch;
+	rc = stateless_assign(points, means_in, asg, s, w, variant_assign, device, sm, st);
+	if (rc) return rc;
+	return stateless_update(points, asg, means_out, sizes, s, w, variant_update, device, sm, st, false);
+}
+
+// Waits for `stream` and returns BKM_ERR_DEVICE if a kernel of the last stateless call on this
+// workspace recorded an error.
+int bkm_workspace_check(const void* workspace, void* stream)
+{
+	if (!workspace) return fail(BKM_ERR_INVALID, "workspace is null");
+	bkm::Control c;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	CUDA_TRY(cudaMemcpyAsync(&c, workspace, sizeof(c), cudaMemcpyDeviceToHost, st));
+	CUDA_TRY(cudaStreamSynchronize(st));
+	if (c.status) return fail(BKM_ERR_DEVICE, "kernel status 0x%x (1=wait timeout, 2=assignment out of range, 4=list overflow)", c.status);
+	return BKM_OK;
+}
+
+// ---- driver -------------------------------------------------------------------------------------
+
+int bkm_create(const bkm_config_t* cfg, bkm_handle_t* out)
+{
+	if (!cfg || !out) return fail(BKM_ERR_INVALID, "null argument");
+	*out = nullptr;
+	if (cfg->reserved != 0) return fail(BKM_ERR_INVALID, "reserved must be 0");
+	int rc = check_shape(cfg->n, cfg->k, cfg->dim, cfg->layout, cfg->layout_means);
+	if (rc) return rc;
+	int ndev = bkm_device_count();
+	if (ndev == 0) return fail(BKM_ERR_CUDA, "no CUDA device");
+	if (cfg->device < 0 || cfg->device >= ndev) return fail(BKM_ERR_INVALID, "device %d out of range (0..%d)", cfg->device, ndev - 1);
+	CUDA_TRY(cudaSetDevice(cfg->device));
+
+	bkm_handle_s* h = new (std::nothrow) bkm_handle_s();
+	if (!h) return fail(BKM_ERR_INVALID, "out of host memory");
+	h->cfg = *cfg;
+	h->shape.n = cfg->n; h->shape.k = cfg->k; h->shape.dim = cfg->dim;
+	h->shape.soa = cfg->layout == BKM_LAYOUT_SOA; h->shape.soa_means = cfg->layout_means == BKM_LAYOUT_SOA;
+	auto bail = [&](int code) { bkm_destroy(h); return code; };
+	if ((rc = device_sm_count(cfg->device, &h->sm_count))) return bail(rc);
+	if ((rc = resolve_assign(cfg->variant_assign, h->shape, &h->assign_variant))) return bail(rc);
+	if ((rc = resolve_update(cfg->variant_update, h->shape, cfg->device, &h->update_variant))) return bail(rc);
+
+	cudaError_t e;
+	if ((e = cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking)) != cudaSuccess)
+		return bail(fail(BKM_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)));
+	h->stream = h->own_stream;
+	const size_t kd = (size_t)cfg->k * cfg->dim;
+	const bool tc = h->assign_variant == BKM_ASSIGN_TC;
+	h->ws = carve(nullptr, cfg->n, cfg->k, cfg->dim, tc);
+	if ((e = cudaMalloc(&h->d_means[0], kd * sizeof(float))) != cudaSuccess ||
+		(e = cudaMalloc(&h->d_means[1], kd * sizeof(float))) != cudaSuccess ||
+		(e = cudaMalloc(&h->d_asg, cfg->n * sizeof(uint32_t))) != cudaSuccess ||
+		(e = cudaMalloc(&h->d_sizes, (size_t)cfg->k * sizeof(uint32_t))) != cudaSuccess ||
+		(e = cudaMalloc(&h->d_ws, h->ws.bytes)) != cudaSuccess)
+		return bail(fail(BKM_ERR_CUDA, "cudaMalloc: %s", cudaGetErrorString(e)));
+	h->ws = carve(h->d_ws, cfg->n, cfg->k, cfg->dim, tc);
+	if ((e = cudaMemset(h->d_ws, 0, h->ws.bytes)) != cudaSuccess ||
+		(e = cudaMemset(h->d_asg, 0, cfg->n * sizeof(uint32_t))) != cudaSuccess ||
+		(e = cudaMemset(h->d_sizes, 0, (size_t)cfg->k * sizeof(uint32_t))) != cudaSuccess)
+		return bail(fail(BKM_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e)));
+	for (int i = 0; i < bkm_handle_s::EV_RING; ++i)
+		for (int j = 0; j < bkm_handle_s::EV_PER; ++j)
+			if ((e = cudaEventCreate(&h->ev[i][j])) != cudaSuccess)
+				return bail(fail(BKM_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e)));
+	h->ev_made = true;
+	*out = h;
+	return BKM_OK;
+}
+
+int bkm_destroy(bkm_handle_t h)
+{
+	if (!h) return BKM_OK;
+	cudaSetDevice(h->cfg.device);
+	if (h->stream) cudaStreamSynchronize(h->stream);
+	if (h->comm && nccl()->ok) nccl()->CommDestroy(h->comm);
+	if (h->plan) bkm::tc_plan_destroy(h->plan);
+	for (int i = 0; i < bkm_handle_s::EV_RING; ++i)
+		for (int j = 0; j < bkm_handle_s::EV_PER; ++j)
+			if (h->ev[i][j]) cudaEventDestroy(h->ev[i][j]);
+	cudaFree(h->d_points_owned);
+	cudaFree(h->d_means[0]);
+	cudaFree(h->d_means[1]);
+	cudaFree(h->d_asg);
+	cudaFree(h->d_sizes);
+	cudaFree(h->d_ws);
+	if (h->own_stream) cudaStreamDestroy(h->own_stream);
+	delete h;
+	return BKM_OK;
+}
+
+int bkm_set_stream(bkm_handle_t h, void* stream)
+{
+	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	h->stream = stream ? static_cast<cudaStream_t>(stream) : h->own_stream;
+	return BKM_OK;
+}
+
+int bkm_set_option(bkm_handle_t h, const char* name, double value)
+{
+	if (!h || !name) return fail(BKM_ERR_INVALID, "null argument");
+	if (!strcmp(name, "margin_scale")) {
+		if (!(value > 0.0)) return fail(BKM_ERR_INVALID, "margin_scale must be positive");
+		h->margin_scale = (float)value;
+		return BKM_OK;
+	}
+	if (!strcmp(name, "phase_timing")) { h->phase_timing = value != 0.0; return BKM_OK; }
+	return fail(BKM_ERR_INVALID, "unknown option '%s'", name);
+}
+
+static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind kind)
+{
+	const bkm::Shape& s = h->shape;
+	const size_t kd = (size_t)s.k * s.dim;
+	cudaStream_t st = h->stream;
+	h->cur = 0; h->slot = 0; h->iters_done = 0; h->ev_count = 0;
+	CUDA_TRY(cudaMemcpyAsync(h->d_means[0], means, kd * sizeof(float), kind, st));
+	CUDA_TRY(cudaMemsetAsync(h->d_ws, 0, (size_t)(reinterpret_cast<char*>(h->ws.flag_list) - h->d_ws), st));
+	CUDA_TRY(cudaMemsetAsync(h->d_asg, 0, s.n * sizeof(uint32_t), st));
+	CUDA_TRY(cudaMemsetAsync(h->d_sizes, 0, (size_t)s.k * sizeof(uint32_t), st));
+	if (h->assign_variant == BKM_ASSIGN_TC) {
+		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, st));
+		if (h->plan) { bkm::tc_plan_destroy(h->plan); h->plan = nullptr; }
+		const char* err = nullptr;
+		h->plan = bkm::tc_plan_create(s, h->ws.tp, h->ws.tm, h->cfg.device, &err);
+		if (!h->plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
+	}
+	bkm::launch_prepare_means(h->d_means[0], s,
+		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot, st);
+	CUDA_TRY(cudaGetLastError());
+	CUDA_TRY(cudaStreamSynchronize(st));
+	h->initialized = true;
+	return BKM_OK;
+}
+
+int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_means)
+{
+	if (!h || !host_points || !host_means) return fail(BKM_ERR_INVALID, "null argument");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	const size_t bytes = (size_t)h->shape.n * h->shape.dim * sizeof(float);
+	if (!h->d_points_owned) CUDA_TRY(cudaMalloc(&h->d_points_owned, bytes));
+	h->d_points = h->d_points_owned;
+	CUDA_TRY(cudaMemcpyAsync(h->d_points_owned, host_points, bytes, cudaMemcpyHostToDevice, h->stream));
+	return initialize_common(h, host_means, cudaMemcpyHostToDevice);
+}
+
+int bkm_initialize_device(bkm_handle_t h, const float* dev_points, const float* dev_means)
+{
+	if (!h || !dev_points || !dev_means) return fail(BKM_ERR_INVALID, "null argument");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	h->d_points = dev_points;
+	return initialize_common(h, dev_means, cudaMemcpyDeviceToDevice);
+}
+
+int bkm_set_means(bkm_handle_t h, const float* host_means)
+{
+	if (!h || !host_means) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->initialized) return fail(BKM_ERR_STATE, "set_means before initialize");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	const bkm::Shape& s = h->shape;
+	cudaStream_t st = h->stream;
+	CUDA_TRY(cudaMemcpyAsync(h->d_means[h->cur], host_means, (size_t)s.k * s.dim * sizeof(float), cudaMemcpyHostToDevice, st));
+	// the preparation fills cmax2[slot] with atomicMax, so the slot starts from zero
+	CUDA_TRY(cudaMemsetAsync(&h->ws.ctl->cmax2[h->slot], 0, sizeof(float), st));
+	bkm::launch_prepare_means(h->d_means[h->cur], s,
+		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot, st);
+	CUDA_TRY(cudaGetLastError());
+	CUDA_TRY(cudaStreamSynchronize(st));
+	return BKM_OK;
+}
+
+int bkm_run_async(bkm_handle_t h, uint32_t iters)
+{
+	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	if (!h->initialized) return fail(BKM_ERR_STATE, "run before initialize");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	const bkm::Shape& s = h->shape;
+	cudaStream_t st = h->stream;
+	const size_t kd = (size_t)s.k * s.dim;
+	h->ev_count = 0;
+	for (uint32_t it = 0; it < iters; ++it) {
+		const int next = h->cur ^ 1;
+		const bool timed = h->phase_timing && (iters - it) <= (uint32_t)bkm_handle_s::EV_RING;
+		cudaEvent_t* ev = timed ? h->ev[h->ev_count] : nullptr;
+		if (timed) CUDA_TRY(cudaEventRecord(ev[0], st));
+		int rc = enqueue_assign(h->assign_variant, h->d_points, h->d_means[h->cur], h->d_asg, s, h->ws, h->slot,
+			h->plan, h->margin_scale, h->sm_count, st, timed ? ev[1] : nullptr);
+		if (rc) return rc;
+		if (timed) CUDA_TRY(cudaEventRecord(ev[2], st));
+		bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, s, h->update_variant, h->ws.ctl, h->sm_count, st);
+		if (timed) CUDA_TRY(cudaEventRecord(ev[3], st));
+		if (h->comm) {
+			Nccl* nc = nccl();
+			NCCL_TRY(nc->GroupStart());
+			NCCL_TRY(nc->AllReduce(h->ws.acc, h->ws.acc, kd, NCCL_FLOAT32, NCCL_SUM, h->comm, st));
+			NCCL_TRY(nc->AllReduce(h->ws.counts, h->ws.counts, s.k, NCCL_UINT32, NCCL_SUM, h->comm, st));
+			NCCL_TRY(nc->GroupEnd());
+		}
+		if (timed) CUDA_TRY(cudaEventRecord(ev[4], st));
+		bkm::launch_finalize(h->ws.acc, h->ws.counts, h->d_means[next], h->d_sizes, s,
+			h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+			h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st);
+		if (timed) { CUDA_TRY(cudaEventRecord(ev[5], st)); ++h->ev_count; }
+		CUDA_TRY(cudaGetLastError());
+		h->cur = next;
+		h->slot ^= 1;
+		++h->iters_done;
+	}
+	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + 2u;
+	return BKM_OK;
+}
+
+int bkm_synchronize(bkm_handle_t h)
+{
+	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	bkm::Control c;
+	CUDA_TRY(cudaMemcpy(&c, h->ws.ctl, sizeof(c), cudaMemcpyDeviceToHost));
+	if (c.status) {
+		cudaMemset(&h->ws.ctl->status, 0, sizeof(uint32_t));
+		return fail(BKM_ERR_DEVICE, "kernel status 0x%x (1=wait timeout, 2=assignment out of range, 4=list overflow)", c.status);
+	}
+	return BKM_OK;
+}
+
+int bkm_run(bkm_handle_t h, uint32_t iters)
+{
+	int rc = bkm_run_async(h, iters);
+	if (rc) return rc;
+	return bkm_synchronize(h);
+}
+
+int bkm_get_means(bkm_handle_t h, float* host_means)
+{
+	if (!h || !host_means) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->initialized) return fail(BKM_ERR_STATE, "no results before initialize");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaMemcpyAsync(host_means, h->d_means[h->cur], (size_t)h->shape.k * h->shape.dim * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	return BKM_OK;
+}
+
+int bkm_get_assignment(bkm_handle_t h, uint32_t* host_assignment)
+{
+	if (!h || !host_assignment) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->initialized) return fail(BKM_ERR_STATE, "no results before initialize");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaMemcpyAsync(host_assignment, h->d_asg, h->shape.n * sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	return BKM_OK;
+}
+
+int bkm_get_sizes(bkm_handle_t h, uint32_t* host_sizes)
+{
+	if (!h || !host_sizes) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->initialized) return fail(BKM_ERR_STATE, "no results before initialize");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaMemcpyAsync(host_sizes, h->d_sizes, (size_t)h->shape.k * sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	return BKM_OK;
+}
+
+int bkm_device_means(bkm_handle_t h, const float** dev_means)
+{
+	if (!h || !dev_means) return fail(BKM_ERR_INVALID, "null argument");
+	*dev_means = h->d_means[h->cur];
+	return BKM_OK;
+}
+
+int bkm_device_assignment(bkm_handle_t h, const uint32_t** dev_assignment)
+{
+	if (!h || !dev_assignment) return fail(BKM_ERR_INVALID, "null argument");
+	*dev_assignment = h->d_asg;
+	return BKM_OK;
+}
+
+int bkm_iterations_done(bkm_handle_t h, uint64_t* out)
+{
+	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	*out = h->iters_done;
+	return BKM_OK;
+}
+
+int bkm_phase_ms(bkm_handle_t h, float out[6])
+{
+	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	for (int p = 0; p < 6; ++p) out[p] = 0.0f;
+	if (h->ev_count == 0) return BKM_OK;
+	for (uint32_t i = 0; i < h->ev_count; ++i) {
+		float ms = 0.0f;
+		for (int p = 0; p < 5; ++p) {
+			CUDA_TRY(cudaEventElapsedTime(&ms, h->ev[i][p], h->ev[i][p + 1]));
+			out[p] += ms;
+		}
+		CUDA_TRY(cudaEventElapsedTime(&ms, h->ev[i][0], h->ev[i][5]));
+		out[5] += ms;
+	}
+	for (int p = 0; p < 6; ++p) out[p] /= (float)h->ev_count;
+	return BKM_OK;
+}
+
+int bkm_counters(bkm_handle_t h, uint64_t out[4])
+{
+	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	bkm::Control c;
+	CUDA_TRY(cudaMemcpy(&c, h->ws.ctl, sizeof(c), cudaMemcpyDeviceToHost));
+	out[0] = c.last_flag_count;
+	out[1] = h->launches_per_iter;
+	out[2] = (uint64_t)h->assign_variant;
+	out[3] = (uint64_t)h->update_variant;
+	return BKM_OK;
+}
+
+// ---- multi-GPU ----------------------------------------------------------------------------------
+
+int bkm_comm_unique_id(void* id, size_t id_bytes)
+{
+	if (!id || id_bytes < sizeof(nccl_unique_id)) return fail(BKM_ERR_INVALID, "id buffer must hold 128 bytes");
+	Nccl* nc = nccl();
+	if (!nc->ok) return fail(BKM_ERR_NCCL, "libnccl.so.2 not found");
+	nccl_unique_id uid;
+	NCCL_TRY(nc->GetUniqueId(&uid));
+	memcpy(id, &uid, sizeof(uid));
+	return BKM_OK;
+}
+
+int bkm_comm_init(bkm_handle_t h, const void* id, size_t id_bytes, int world_size, int rank)
+{
+	if (!h || !id || id_bytes < sizeof(nccl_unique_id)) return fail(BKM_ERR_INVALID, "bad argument");
+	if (world_size < 1 || rank < 0 || rank >= world_size) return fail(BKM_ERR_INVALID, "bad world_size/rank");
+	if (h->comm) return fail(BKM_ERR_STATE, "communicator already initialised");
+	Nccl* nc = nccl();
+	if (!nc->ok) return fail(BKM_ERR_NCCL, "libnccl.so.2 not found");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	nccl_unique_id uid;
+	memcpy(&uid, id, sizeof(uid));
+	NCCL_TRY(nc->CommInitRank(&h->comm, world_size, uid, rank));
+	h->world = world_size;
+	h->rank = rank;
+	return BKM_OK;
+}
+
+// ---- host-buffer convenience ----------------------------------------------------------------------
+
+int bkm_kmeans_host_f32(const float* host_points, float* means, uint32_t* assignment,
+	uint64_t n, uint32_t k, uint32_t dim, uint32_t iters, int layout, int layout_means, int device)
+{
+	if (!host_points || !means || !assignment) return fail(BKM_ERR_INVALID, "null argument");
+	bkm_config_t cfg{};
+	cfg.n = n; cfg.k = k; cfg.dim = dim; cfg.layout = layout; cfg.layout_means = layout_means; cfg.device = device;
+	bkm_handle_t h = nullptr;
+	int rc = bkm_create(&cfg, &h);
+	if (rc) return rc;
+	if ((rc = bkm_initialize(h, host_points, means)) == BKM_OK &&
+		(rc = bkm_run(h, iters)) == BKM_OK &&
+		(rc = bkm_get_means(h, means)) == BKM_OK)
+		rc = bkm_get_assignment(h, assignment);
+	std::string keep = g_error;
+	bkm_destroy(h);
+	g_error = keep;
+	return rc;
+}
+
+} // extern "C"

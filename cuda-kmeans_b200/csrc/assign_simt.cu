@@ -1,0 +1,282 @@
+// Assignment on CUDA cores.
+//
+//  * assign_exact_kernel: one warp per point, lanes over the means, the reference's arithmetic
+//    (sequential subtract / multiply / add without fusing, square root, strictly-smaller
+//    comparison in ascending index order).  Used for every point by the EXACT variant and
+//    for the queued near-ties of the fast passes.  Replaces baseAssignmentKernel
+//    (kernels/kernels.cu:182-199 of the reference) and follows serial.hpp:21-35.
+//
+//  * assign_simt_kernel<D>: small-d fast pass.  The prepared means ([|c|^2, -2c...] rows)
+//    are staged into shared memory with a bulk TMA copy; every thread keeps P points in
+//    registers and evaluates |c|^2 - 2 x.c with D fused multiply-adds per mean, tracking the
+//    best and second-best value.  A point whose two best values are closer than the rounding
+//    band of this formulation is queued for the exact kernel, so the final result equals the
+//    reference's for every point.  Covers the shape range of cachedFixedAssignmentKernel
+//    (kernels/kernels.cu:218-273) and cachedAllMeansAssignmentKernel (:330-374).
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+#include <cmath>
+
+namespace bkm {
+
+// ------------------------------------------------------------------------------------------
+// exact kernel
+// ------------------------------------------------------------------------------------------
+
+template<bool SOA, bool SOAM>
+__global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restrict__ pts,
+	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
+	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
+{
+	extern __shared__ float sx[];
+	const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+	float* x = sx + (size_t)warp * d;
+	uint64_t total = n;
+	if (list != nullptr) {
+		uint64_t c = *list_count;
+		total = c < n ? c : n;
+	}
+	for (uint64_t w = (uint64_t)blockIdx.x * wpb + warp; w < total; w += (uint64_t)gridDim.x * wpb) {
+		const uint64_t i = list ? (uint64_t)list[w] : w;
+		__syncwarp();
+		for (uint32_t j = lane; j < d; j += 32) x[j] = pts[at<SOA>(i, j, n, d)];
+		__syncwarp();
+		float best = INFINITY;
+		uint32_t bidx = 0xffffffffu;
+		for (uint32_t m = lane; m < k; m += 32) {
+			float sum = 0.0f;
+			for (uint32_t j = 0; j < d; ++j) {
+				float diff = __fsub_rn(x[j], means[at<SOAM>(m, j, k, d)]);
+				sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+			}
+			float dist = __fsqrt_rn(sum);
+			if (dist < best || bidx == 0xffffffffu) { best = dist; bidx = m; }
+		}
+		// lowest (distance, index) pair over the warp = what the sequential scan would keep
+		#pragma unroll
+		for (int off = 16; off > 0; off >>= 1) {
+			float ob = __shfl_xor_sync(0xffffffffu, best, off);
+			uint32_t oi = __shfl_xor_sync(0xffffffffu, bidx, off);
+			if (oi != 0xffffffffu && (bidx == 0xffffffffu || ob < best || (ob == best && oi < bidx))) { best = ob; bidx = oi; }
+		}
+		if (lane == 0) asg[i] = bidx;
+	}
+}
+
+cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
+{
+	// shared memory: one copy of the point per warp
+	uint32_t warps = 8;
+	while (warps > 1 && (size_t)warps * s.dim * sizeof(float) > 96 * 1024) warps >>= 1;
+	size_t smem = (size_t)warps * s.dim * sizeof(float);
+	if (smem > 200 * 1024) return cudaErrorInvalidValue;
+	uint64_t want = list ? (uint64_t)sm_count * 8 : (s.n + warps - 1) / warps;
+	uint32_t grid = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(want, 1), (uint64_t)sm_count * 16);
+	dim3 block(warps * 32);
+#define BKM_LAUNCH_EXACT(SOA, SOAM) do { \
+		auto kern = assign_exact_kernel<SOA, SOAM>; \
+		if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; } \
+		kern<<<grid, block, smem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count); \
+	} while (0)
+	if (s.soa && s.soa_means) BKM_LAUNCH_EXACT(true, true);
+	else if (s.soa && !s.soa_means) BKM_LAUNCH_EXACT(true, false);
+	else if (!s.soa && s.soa_means) BKM_LAUNCH_EXACT(false, true);
+	else BKM_LAUNCH_EXACT(false, false);
+#undef BKM_LAUNCH_EXACT
+	return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// small-d fast pass
+// ------------------------------------------------------------------------------------------
+
+constexpr int SIMT_THREADS = 256;
+constexpr int SIMT_P = 2;            // points per thread
+constexpr int SIMT_TILE_ROWS = 1024; // means per shared-memory tile
+
+template<int D, bool SOA>
+__global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* __restrict__ pts,
+	const float* __restrict__ cprep, uint32_t* __restrict__ asg, uint64_t n, uint32_t rows,
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef, int vec_ok)
+{
+	constexpr int RS = (D + 1 + 3) / 4 * 4;
+	constexpr int P = SIMT_P;
+	extern __shared__ __align__(128) float tile[];
+	__shared__ __align__(8) uint64_t bar;
+
+	const uint32_t tid = threadIdx.x;
+	const uint32_t ntiles = (rows + SIMT_TILE_ROWS - 1) / SIMT_TILE_ROWS;
+	const uint64_t per_block = (uint64_t)SIMT_THREADS * P;
+	const uint64_t nblocks = (n + per_block - 1) / per_block;
+	uint32_t phase = 0;
+	bool ok = true;
+
+	if (tid == 0) {
+		ptx::mbar_init(&bar, 1);
+		ptx::fence_mbar_init();
+	}
+	__syncthreads();
+
+	if (ntiles == 1) {
+		if (tid == 0) {
+			uint32_t bytes = rows * RS * (uint32_t)sizeof(float);
+			ptx::mbar_arrive_expect_tx(&bar, bytes);
+			ptx::bulk_g2s(tile, cprep, bytes, &bar);
+		}
+		ok = ptx::mbar_wait(&bar, phase);
+		phase ^= 1;
+	}
+	const float cmax2 = ctl->cmax2[slot];
+
+	for (uint64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+		float x[P][D];
+		uint64_t idx[P];
+		float xn[P];
+		const uint64_t base = blk * per_block;
+		if (SOA) {
+			#pragma unroll
+			for (int p = 0; p < P; ++p) {
+				idx[p] = base + (uint64_t)p * SIMT_THREADS + tid;
+				#pragma unroll
+				for (int j = 0; j < D; ++j) x[p][j] = idx[p] < n ? pts[(size_t)j * n + idx[p]] : 0.0f;
+			}
+		} else {
+			#pragma unroll
+			for (int p = 0; p < P; ++p) idx[p] = base + (uint64_t)tid * P + p;
+			if ((P * D) % 4 == 0 && vec_ok && idx[P - 1] < n) {
+				// 128-bit loads: the thread's P points are P*D consecutive floats
+				const float4* src = reinterpret_cast<const float4*>(pts + (size_t)idx[0] * D);
+				float buf[P * D];
+				#pragma unroll
+				for (int q = 0; q < (P * D) / 4; ++q) {
+					float4 v = src[q];
+					buf[4 * q + 0] = v.x; buf[4 * q + 1] = v.y; buf[4 * q + 2] = v.z; buf[4 * q + 3] = v.w;
+				}
+				#pragma unroll
+				for (int p = 0; p < P; ++p)
+					#pragma unroll
+					for (int j = 0; j < D; ++j) x[p][j] = buf[p * D + j];
+			} else {
+				#pragma unroll
+				for (int p = 0; p < P; ++p)
+					#pragma unroll
+					for (int j = 0; j < D; ++j) x[p][j] = idx[p] < n ? pts[(size_t)idx[p] * D + j] : 0.0f;
+			}
+		}
+		float best[P], second[P];
+		uint32_t bidx[P];
+		#pragma unroll
+		for (int p = 0; p < P; ++p) {
+			best[p] = INFINITY; second[p] = INFINITY; bidx[p] = 0;
+			float s2 = 0.0f;
+			#pragma unroll
+			for (int j = 0; j < D; ++j) s2 = fmaf(x[p][j], x[p][j], s2);
+			xn[p] = s2;
+		}
+
+		for (uint32_t t = 0; t < ntiles; ++t) {
+			uint32_t trows = rows - t * SIMT_TILE_ROWS;
+			if (trows > SIMT_TILE_ROWS) trows = SIMT_TILE_ROWS;
+			if (ntiles > 1) {
+				__syncthreads();   // everyone is done reading the previous tile
+				if (tid == 0) {
+					uint32_t bytes = trows * RS * (uint32_t)sizeof(float);
+					ptx::mbar_arrive_expect_tx(&bar, bytes);
+					ptx::bulk_g2s(tile, cprep + (size_t)t * SIMT_TILE_ROWS * RS, bytes, &bar);
+				}
+				ok = ptx::mbar_wait(&bar, phase) && ok;
+				phase ^= 1;
+			}
+			const uint32_t mbase = t * SIMT_TILE_ROWS;
+			#pragma unroll 4
+			for (uint32_t m = 0; m < trows; ++m) {
+				float r[RS];
+				const float4* row = reinterpret_cast<const float4*>(tile + (size_t)m * RS);
+				#pragma unroll
+				for (int q = 0; q < RS / 4; ++q) {
+					float4 v = row[q];
+					r[4 * q + 0] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+				}
+				#pragma unroll
+				for (int p = 0; p < P; ++p) {
+					float v = r[0];
+					#pragma unroll
+					for (int j = 0; j < D; ++j) v = fmaf(x[p][j], r[1 + j], v);
+					const bool lt = v < best[p];
+					second[p] = fminf(second[p], fmaxf(best[p], v));
+					best[p] = fminf(best[p], v);
+					bidx[p] = lt ? (mbase + m) : bidx[p];
+				}
+			}
+		}
+
+		#pragma unroll
+		for (int p = 0; p < P; ++p) {
+			if (idx[p] < n) {
+				asg[idx[p]] = bidx[p];
+				const float margin = margin_coef * (xn[p] + cmax2);
+				if (second[p] - best[p] <= margin) {
+					uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
+					if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)idx[p];
+					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+				}
+			}
+		}
+	}
+	if (!ok && tid == 0) atomicOr(&ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
+}
+
+bool assign_simt_supported(const Shape& s)
+{
+	return s.dim >= 1 && s.dim <= 8 && s.n < (1ull << 32);
+}
+
+template<int D>
+static cudaError_t launch_simt_d(const float* pts, const float* cprep, uint32_t* asg, const Shape& s,
+	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream)
+{
+	constexpr int RS = (D + 1 + 3) / 4 * 4;
+	const uint32_t rows = simt_rows(s.k);
+	const uint32_t trows = rows < (uint32_t)SIMT_TILE_ROWS ? rows : (uint32_t)SIMT_TILE_ROWS;
+	const size_t smem = (size_t)trows * RS * sizeof(float);
+	const uint64_t per_block = (uint64_t)SIMT_THREADS * SIMT_P;
+	const uint64_t nblocks = (s.n + per_block - 1) / per_block;
+	// persistent grid: a whole number of resident blocks per SM
+	int per_sm = 1;
+	const float margin_coef = margin_scale * (float)(D + 8) * 2.384185791015625e-07f; // (D+8) * 2^-22
+	const int vec_ok = ((reinterpret_cast<uintptr_t>(pts) & 15u) == 0) ? 1 : 0;
+#define BKM_LAUNCH_SIMT(SOA) do { \
+		auto kern = assign_simt_kernel<D, SOA>; \
+		cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+		if (e != cudaSuccess) return e; \
+		e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, SIMT_THREADS, smem); \
+		if (e != cudaSuccess) return e; \
+		if (per_sm < 1) per_sm = 1; \
+		uint32_t grid = (uint32_t)std::min<uint64_t>(nblocks, (uint64_t)sm_count * per_sm); \
+		if (grid < 1) grid = 1; \
+		kern<<<grid, SIMT_THREADS, smem, stream>>>(pts, cprep, asg, s.n, rows, ctl, slot, flag_list, margin_coef, vec_ok); \
+	} while (0)
+	if (s.soa) BKM_LAUNCH_SIMT(true); else BKM_LAUNCH_SIMT(false);
+#undef BKM_LAUNCH_SIMT
+	return cudaGetLastError();
+}
+
+cudaError_t launch_assign_simt(const float* pts, const float* cprep, uint32_t* asg, const Shape& s,
+	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream)
+{
+	switch (s.dim) {
+	case 1: return launch_simt_d<1>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 2: return launch_simt_d<2>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 3: return launch_simt_d<3>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 4: return launch_simt_d<4>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 5: return launch_simt_d<5>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 6: return launch_simt_d<6>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 7: return launch_simt_d<7>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 8: return launch_simt_d<8>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	default: return cudaErrorInvalidValue;
+	}
+}
+
+} // namespace bkm

@@ -1,0 +1,497 @@
+// Assignment on the 5th-generation tensor cores (tcgen05 + TMEM), GEMM form.
+//
+//   |x - c|^2 = |x|^2 + ( |c|^2 - 2 x.c )          argmin over c ignores |x|^2
+//
+// The x.c contraction runs as split-TF32 ("3xTF32"): every fp32 operand is split once into a
+// tf32 high part and a tf32 low part (x = xh + xl), and xh*ch + xh*cl + xl*ch is accumulated in
+// fp32 in tensor memory, which restores fp32-level accuracy of the products.  The argmin over
+// the centroids is taken in the epilogue straight out of tensor memory; the N x k distance
+// matrix never exists in HBM.  Because the GEMM form cancels, a point whose best and
+// second-best values are closer than the error band of this formulation is queued for the
+// exact CUDA-core kernel, so the final assignment equals the reference arithmetic
+// (headers/serial.hpp:21-35 of krulis-martin/cuda-kmeans) for every point.  The kernel covers
+// the shape range of the reference's cachedRegsAssignmentKernel (kernels/kernels.cu:548-661).
+//
+// Kernel organisation (one persistent CTA per SM, 10 warps):
+//   warp 0     : TMA producer.  Point tiles (128 points x 32 dims, hi and lo plane) are loaded
+//                once per block of 4 tiles and stay in shared memory; centroid tiles (up to 128
+//                centroids x 32 dims, hi and lo) stream through a 2-stage ring.
+//   warp 1     : allocates the 512 TMEM columns, issues 12 tcgen05.mma (kind::tf32, M=128,
+//                N<=128, K=8) per (point tile, centroid tile) into one of 4 accumulators.
+//   warps 2..9 : epilogue.  Two warps per 32-lane TMEM quarter (each takes half of the columns)
+//                read the accumulator with tcgen05.ld, add |c|^2, and keep (best, second, index)
+//                per point in registers across all centroid tiles.
+// All mbarrier waits are bounded; a wait that runs out sets STATUS_WAIT_TIMEOUT and lets every
+// role fall through to the end, where TMEM is released.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+#include <cmath>
+#include <new>
+
+namespace bkm {
+
+constexpr uint32_t TC_MA = 4;            // point tiles per block (= TMEM accumulators)
+constexpr uint32_t TC_NB = 2;            // centroid-tile stages
+constexpr uint32_t TC_NT_MAX = 128;      // centroids per tile
+constexpr uint32_t TC_EPI_WARPS = 8;
+constexpr uint32_t TC_THREADS = (2 + TC_EPI_WARPS) * 32;
+constexpr uint32_t TC_MAX_KPAD = 4096;   // |c|^2 of all centroids is kept in shared memory
+constexpr uint32_t TC_TMEM_COLS = 512;
+
+constexpr uint32_t PLANE_BYTES = TC_MTILE * TC_KCHUNK * 4;       // 16 KiB: 128 rows x 128 B
+constexpr uint32_t A_TILE_BYTES = 2 * PLANE_BYTES;               // hi + lo
+constexpr uint32_t B_STAGE_BYTES = 2 * PLANE_BYTES;
+constexpr uint32_t SM_A_OFF = 0;
+constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;   // 131072
+constexpr uint32_t SM_CN_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // 196608
+constexpr uint32_t SM_MERGE_OFF = SM_CN_OFF + TC_MAX_KPAD * 4;   // 212992
+constexpr uint32_t MERGE_BYTES = 3 * TC_MA * TC_MTILE * 4;       // second half's (best, second, idx)
+constexpr uint32_t SM_BAR_OFF = SM_MERGE_OFF + MERGE_BYTES;
+constexpr uint32_t SM_TOTAL = SM_BAR_OFF + 256;
+constexpr uint32_t SM_ALLOC = SM_TOTAL + 1024;                   // slack for 1024-byte alignment
+
+uint32_t tc_nt_cols(uint32_t k) { return k >= TC_NT_MAX ? TC_NT_MAX : round_up(k, 32); }
+uint32_t tc_kpad(uint32_t k) { return round_up(k, tc_nt_cols(k)); }
+
+bool assign_tc_supported(const Shape& s)
+{
+	return s.dim <= TC_KCHUNK && tc_kpad(s.k) <= TC_MAX_KPAD && s.n < (1ull << 32) - 1024;
+}
+
+// ------------------------------------------------------------------------------------------
+// one-off split of the points
+// ------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float to_tf32(float x)
+{
+	uint32_t u;
+	asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+	return __uint_as_float(u);
+}
+
+// 32 points x 32 dims per step through a padded shared tile, so that both the read (along
+// points for SoA, along dims for AoS) and the write (along dims) are coalesced.
+template<bool SOA>
+__global__ void __launch_bounds__(256) split_points_kernel(const float* __restrict__ pts, float* __restrict__ a_hi,
+	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t n_pad, uint32_t d, uint32_t d_pad)
+{
+	__shared__ float tile[32][33];
+	const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+	for (uint64_t p0 = (uint64_t)blockIdx.x * 32; p0 < n_pad; p0 += (uint64_t)gridDim.x * 32) {
+		float norm[4] = {0.f, 0.f, 0.f, 0.f};
+		for (uint32_t c0 = 0; c0 < d_pad; c0 += 32) {
+			__syncthreads();
+			#pragma unroll
+			for (uint32_t r = 0; r < 4; ++r) {
+				const uint32_t rr = ty + r * 8;
+				if (SOA) {
+					const uint64_t p = p0 + tx;
+					const uint32_t j = c0 + rr;
+					tile[tx][rr] = (p < n && j < d) ? pts[(size_t)j * n + p] : 0.0f;     // tile[point][dim]
+				} else {
+					const uint64_t p = p0 + rr;
+					const uint32_t j = c0 + tx;
+					tile[rr][tx] = (p < n && j < d) ? pts[(size_t)p * d + j] : 0.0f;
+				}
+			}
+			__syncthreads();
+			#pragma unroll
+			for (uint32_t r = 0; r < 4; ++r) {
+				const uint32_t rr = ty + r * 8;     // point within the group
+				const float x = tile[rr][tx];
+				const float hi = to_tf32(x);
+				const float lo = to_tf32(x - hi);
+				const size_t o = (size_t)(p0 + rr) * d_pad + c0 + tx;
+				a_hi[o] = hi;
+				a_lo[o] = lo;
+				norm[r] = fmaf(x, x, norm[r]);
+			}
+		}
+		#pragma unroll
+		for (uint32_t r = 0; r < 4; ++r) {
+			float s = norm[r];
+			#pragma unroll
+			for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+			if (tx == 0) xnorm[p0 + ty + r * 8] = s;
+		}
+	}
+}
+
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, cudaStream_t stream)
+{
+	const uint64_t groups = tp.n_pad / 32;
+	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148 * 16);
+	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad);
+	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad);
+	return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// the assignment kernel
+// ------------------------------------------------------------------------------------------
+
+struct TcBars {
+	uint64_t a_full[TC_MA];
+	uint64_t a_empty[TC_MA];
+	uint64_t b_full[TC_NB];
+	uint64_t b_empty[TC_NB];
+	uint64_t acc_full[TC_MA];
+	uint64_t acc_empty[TC_MA];
+	uint32_t tmem_slot;
+	uint32_t abort_flag;
+};
+static_assert(sizeof(TcBars) <= 256, "barrier block too large");
+
+// Bounded wait that also gives up when another role already failed.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+{
+	for (uint32_t i = 0; i < ptx::WAIT_LIMIT; ++i) {
+		if (ptx::mbar_try_wait(bar, parity)) return true;
+		if ((i & 255u) == 255u && *abort_flag) return false;
+	}
+	*abort_flag = 1;
+	return false;
+}
+
+// K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr)
+{
+	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void track(float v, uint32_t col, float& best, float& second, uint32_t& idx)
+{
+	const bool lt = v < best;
+	second = fminf(second, fmaxf(best, v));
+	best = fminf(best, v);
+	idx = lt ? col : idx;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
+	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+	const float* __restrict__ cnorm, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
+	uint64_t n, uint32_t n_tiles, uint32_t k_pad, uint32_t nt_cols, uint32_t idesc,
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef)
+{
+	extern __shared__ uint8_t smem_raw[];
+	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+	TcBars* bars = reinterpret_cast<TcBars*>(smem + SM_BAR_OFF);
+	float* cn_s = reinterpret_cast<float*>(smem + SM_CN_OFF);
+	float* mg_best = reinterpret_cast<float*>(smem + SM_MERGE_OFF);
+	float* mg_second = mg_best + TC_MA * TC_MTILE;
+	uint32_t* mg_idx = reinterpret_cast<uint32_t*>(mg_second + TC_MA * TC_MTILE);
+	volatile uint32_t* abort_flag = &bars->abort_flag;
+
+	const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+	const uint32_t n_ctiles = k_pad / nt_cols;
+	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
+
+	if (threadIdx.x == 0) {
+		for (uint32_t i = 0; i < TC_MA; ++i) {
+			ptx::mbar_init(&bars->a_full[i], 1);
+			ptx::mbar_init(&bars->a_empty[i], 1);
+			ptx::mbar_init(&bars->acc_full[i], 1);
+			ptx::mbar_init(&bars->acc_empty[i], TC_EPI_WARPS);
+		}
+		for (uint32_t i = 0; i < TC_NB; ++i) {
+			ptx::mbar_init(&bars->b_full[i], 1);
+			ptx::mbar_init(&bars->b_empty[i], 1);
+		}
+		bars->abort_flag = 0;
+		ptx::fence_mbar_init();
+	}
+	if (warp == 1) {
+		ptx::tmem_alloc(&bars->tmem_slot, TC_TMEM_COLS);
+		ptx::tmem_relinquish();
+	}
+	for (uint32_t i = threadIdx.x; i < k_pad; i += TC_THREADS) cn_s[i] = cnorm[i];
+	ptx::tc_fence_before();
+	__syncthreads();
+	ptx::tc_fence_after();
+	const uint32_t tmem_base = bars->tmem_slot;
+
+	if (warp == 0) {
+		// ---------------- TMA producer ----------------
+		if (lane == 0) {
+			ptx::prefetch_tmap(&tm_a_hi); ptx::prefetch_tmap(&tm_a_lo);
+			ptx::prefetch_tmap(&tm_b_hi); ptx::prefetch_tmap(&tm_b_lo);
+			uint32_t a_use[TC_MA] = {0, 0, 0, 0};
+			uint32_t b_count = 0;
+			bool ok = true;
+			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+				for (uint32_t i = 0; i < tiles && ok; ++i) {
+					ok = wait_or_abort(&bars->a_empty[i], (a_use[i] & 1u) ^ 1u, abort_flag);
+					if (!ok) break;
+					uint8_t* dst = smem + SM_A_OFF + i * A_TILE_BYTES;
+					const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE);
+					ptx::mbar_arrive_expect_tx(&bars->a_full[i], A_TILE_BYTES);
+					ptx::tma_load_2d(dst, &tm_a_hi, 0, row, &bars->a_full[i]);
+					ptx::tma_load_2d(dst + PLANE_BYTES, &tm_a_lo, 0, row, &bars->a_full[i]);
+					++a_use[i];
+				}
+				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+					const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
+					ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
+					if (!ok) break;
+					uint8_t* dst = smem + SM_B_OFF + s * B_STAGE_BYTES;
+					ptx::mbar_arrive_expect_tx(&bars->b_full[s], 2 * nt_cols * TC_KCHUNK * 4);
+					ptx::tma_load_2d(dst, &tm_b_hi, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
+					ptx::tma_load_2d(dst + PLANE_BYTES, &tm_b_lo, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
+					++b_count;
+				}
+			}
+			// Do not leave while an own copy may still be in flight towards this CTA's shared memory.
+			for (uint32_t i = 0; i < TC_MA; ++i)
+				if (a_use[i]) ptx::mbar_wait(&bars->a_full[i], (a_use[i] - 1) & 1u);
+			for (uint32_t back = 0; back < TC_NB && back < b_count; ++back) {
+				const uint32_t c = b_count - 1 - back;
+				ptx::mbar_wait(&bars->b_full[c % TC_NB], (c / TC_NB) & 1u);
+			}
+		}
+	} else if (warp == 1) {
+		// ---------------- MMA issuer ----------------
+		if (lane == 0) {
+			uint32_t a_use[TC_MA] = {0, 0, 0, 0};
+			uint32_t acc_use[TC_MA] = {0, 0, 0, 0};
+			uint32_t b_count = 0;
+			bool ok = true;
+			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+					const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
+					ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
+					if (!ok) break;
+					const uint32_t b_addr = ptx::smem_u32(smem + SM_B_OFF + s * B_STAGE_BYTES);
+					const uint64_t b_hi = make_desc(b_addr), b_lo = make_desc(b_addr + PLANE_BYTES);
+					for (uint32_t i = 0; i < tiles; ++i) {
+						if (j == 0) {
+							ok = wait_or_abort(&bars->a_full[i], a_use[i] & 1u, abort_flag);
+							if (!ok) break;
+						}
+						ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
+						if (!ok) break;
+						ptx::tc_fence_after();
+						const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + i * A_TILE_BYTES);
+						const uint64_t a_hi = make_desc(a_addr), a_lo = make_desc(a_addr + PLANE_BYTES);
+						const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
+						// small cross terms first, the dominant hi*hi term last; +2 in the
+						// descriptor's address field = 32 bytes = one K step of 8 tf32 values
+						#pragma unroll
+						for (uint32_t ks = 0; ks < 4; ++ks) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
+						#pragma unroll
+						for (uint32_t ks = 0; ks < 4; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
+						#pragma unroll
+						for (uint32_t ks = 0; ks < 4; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
+						ptx::mma_commit(&bars->acc_full[i]);
+						++acc_use[i];
+						if (j == n_ctiles - 1) {
+							ptx::mma_commit(&bars->a_empty[i]);
+							++a_use[i];
+						}
+					}
+					if (!ok) break;
+					ptx::mma_commit(&bars->b_empty[s]);
+					++b_count;
+				}
+			}
+		}
+	} else {
+		// ---------------- epilogue ----------------
+		const uint32_t q = warp & 3u;              // TMEM lane quarter this warp may read
+		const uint32_t h = (warp - 2) >> 2;        // which half of the tile's columns
+		const uint32_t row = q * 32 + lane;
+		const uint32_t colbase = h * 64;
+		const float cmax2 = ctl->cmax2[slot];
+		uint32_t acc_use[TC_MA] = {0, 0, 0, 0};
+		bool ok = true;
+		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+			float best[TC_MA], second[TC_MA];
+			uint32_t idx[TC_MA];
+			#pragma unroll
+			for (uint32_t i = 0; i < TC_MA; ++i) { best[i] = INFINITY; second[i] = INFINITY; idx[i] = 0; }
+			for (uint32_t j = 0; j < n_ctiles; ++j) {
+				#pragma unroll
+				for (uint32_t i = 0; i < TC_MA; ++i) {
+					if (i < tiles) {
+						if (ok) ok = __all_sync(0xffffffffu, wait_or_abort(&bars->acc_full[i], acc_use[i] & 1u, abort_flag));
+						++acc_use[i];
+						if (ok && colbase < nt_cols) {
+							ptx::tc_fence_after();
+							const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
+							const uint32_t gcol = j * nt_cols + colbase;
+							const bool two = colbase + 32 < nt_cols;
+							uint32_t v0[32], v1[32];
+							ptx::tmem_ld32(taddr, v0);
+							if (two) ptx::tmem_ld32(taddr + 32, v1);
+							ptx::tmem_ld_wait();
+							const float4* c4 = reinterpret_cast<const float4*>(cn_s + gcol);
+							#pragma unroll
+							for (uint32_t t = 0; t < 8; ++t) {
+								const float4 c = c4[t];
+								track(__uint_as_float(v0[4 * t + 0]) + c.x, gcol + 4 * t + 0, best[i], second[i], idx[i]);
+								track(__uint_as_float(v0[4 * t + 1]) + c.y, gcol + 4 * t + 1, best[i], second[i], idx[i]);
+								track(__uint_as_float(v0[4 * t + 2]) + c.z, gcol + 4 * t + 2, best[i], second[i], idx[i]);
+								track(__uint_as_float(v0[4 * t + 3]) + c.w, gcol + 4 * t + 3, best[i], second[i], idx[i]);
+							}
+							if (two) {
+								#pragma unroll
+								for (uint32_t t = 0; t < 8; ++t) {
+									const float4 c = c4[8 + t];
+									track(__uint_as_float(v1[4 * t + 0]) + c.x, gcol + 32 + 4 * t + 0, best[i], second[i], idx[i]);
+									track(__uint_as_float(v1[4 * t + 1]) + c.y, gcol + 32 + 4 * t + 1, best[i], second[i], idx[i]);
+									track(__uint_as_float(v1[4 * t + 2]) + c.z, gcol + 32 + 4 * t + 2, best[i], second[i], idx[i]);
+									track(__uint_as_float(v1[4 * t + 3]) + c.w, gcol + 32 + 4 * t + 3, best[i], second[i], idx[i]);
+								}
+							}
+							ptx::tc_fence_before();
+						}
+						__syncwarp();
+						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
+					}
+				}
+			}
+			// merge the two column halves: half 1 hands its state over through shared memory
+			if (h == 1) {
+				#pragma unroll
+				for (uint32_t i = 0; i < TC_MA; ++i) {
+					mg_best[i * TC_MTILE + row] = best[i];
+					mg_second[i * TC_MTILE + row] = second[i];
+					mg_idx[i * TC_MTILE + row] = idx[i];
+				}
+			}
+			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+			if (h == 0) {
+				#pragma unroll
+				for (uint32_t i = 0; i < TC_MA; ++i) {
+					if (i < tiles) {
+						const float ob = mg_best[i * TC_MTILE + row], os = mg_second[i * TC_MTILE + row];
+						const uint32_t oi = mg_idx[i * TC_MTILE + row];
+						const float b = fminf(best[i], ob);
+						const float s2 = fminf(fminf(second[i], os), fmaxf(best[i], ob));
+						const uint32_t bi = (ob < best[i] || (ob == best[i] && oi < idx[i])) ? oi : idx[i];
+						const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
+						if (p < n && ok) {
+							asg[p] = bi;
+							const float margin = margin_coef * (xnorm[p] + cmax2);
+							if (s2 - b <= margin) {
+								const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
+								if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
+								else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+							}
+						}
+					}
+				}
+			}
+			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+		}
+	}
+
+	ptx::tc_fence_before();
+	__syncthreads();
+	if (warp == 1) {
+		__syncwarp();
+		ptx::tc_fence_after();
+		ptx::tmem_dealloc(tmem_base, TC_TMEM_COLS);
+	}
+	if (threadIdx.x == 0 && bars->abort_flag) atomicOr(&ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+
+struct TcPlan {
+	CUtensorMap a_hi, a_lo, b_hi, b_lo;
+	Shape s;
+	TcPoints tp;
+	TcMeans tm;
+	uint32_t nt_cols;
+	uint32_t idesc;
+	int sm_count;
+};
+
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode()
+{
+	static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+	static bool tried = false;
+	if (!tried) {
+		tried = true;
+		void* p = nullptr;
+		cudaDriverEntryPointQueryResult qres;
+		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+			qres == cudaDriverEntryPointSuccess)
+			fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+	}
+	return fn;
+}
+
+// [rows][cols] fp32 row-major, box = box_rows x 32 columns, 128-byte swizzle.
+static bool encode_plane(CUtensorMap* out, const float* base, uint64_t rows, uint32_t cols, uint32_t box_rows)
+{
+	auto enc = get_encode();
+	if (!enc) return false;
+	cuuint64_t dims[2] = {cols, rows};
+	cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
+	cuuint32_t box[2] = {TC_KCHUNK, box_rows};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+		CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	return r == CUDA_SUCCESS;
+}
+
+TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err)
+{
+	static const char* e_sup = "shape not supported by the tensor-core assignment";
+	static const char* e_map = "cuTensorMapEncodeTiled failed or is unavailable";
+	static const char* e_attr = "cannot set the shared-memory size of the tensor-core kernel";
+	if (!assign_tc_supported(s) || tp.d_pad != TC_KCHUNK || tm.d_pad != TC_KCHUNK) { if (err) *err = e_sup; return nullptr; }
+	TcPlan* p = new (std::nothrow) TcPlan();
+	if (!p) return nullptr;
+	p->s = s; p->tp = tp; p->tm = tm;
+	p->nt_cols = tc_nt_cols(s.k);
+	// c_format = f32 (bit 4), a/b format = tf32 (bits 7.., 10..), K-major both, N>>3 at bit 17, M>>4 at bit 24
+	p->idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p->nt_cols >> 3) << 17) | ((TC_MTILE >> 4) << 24);
+	if (cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) p->sm_count = 148;
+	if (!encode_plane(&p->a_hi, tp.a_hi, tp.n_pad, tp.d_pad, TC_MTILE) ||
+		!encode_plane(&p->a_lo, tp.a_lo, tp.n_pad, tp.d_pad, TC_MTILE) ||
+		!encode_plane(&p->b_hi, tm.b_hi, tm.k_pad, tm.d_pad, p->nt_cols) ||
+		!encode_plane(&p->b_lo, tm.b_lo, tm.k_pad, tm.d_pad, p->nt_cols)) {
+		if (err) *err = e_map;
+		delete p;
+		return nullptr;
+	}
+	if (cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM_ALLOC) != cudaSuccess) {
+		cudaGetLastError();
+		if (err) *err = e_attr;
+		delete p;
+		return nullptr;
+	}
+	return p;
+}
+
+void tc_plan_destroy(TcPlan* plan) { delete plan; }
+
+cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
+	float margin_scale, cudaStream_t stream)
+{
+	if (!p) return cudaErrorInvalidValue;
+	const uint32_t n_tiles = (uint32_t)(p->tp.n_pad / TC_MTILE);
+	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
+	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
+	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
+	const float margin_coef = margin_scale * (40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
+	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
+		p->tm.cnorm, p->tp.xnorm, asg, p->s.n, n_tiles, p->tm.k_pad, p->nt_cols, p->idesc,
+		ctl, slot, flag_list, margin_coef);
+	return cudaGetLastError();
+}
+
+} // namespace bkm

@@ -1,0 +1,57 @@
+// Shared definitions of the k-means kernels: status word, layout indexing, launch helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstddef>
+
+namespace bkm {
+
+// Bits of the device status word.  Kernels never trap; a bounded wait that runs out or an
+// internal inconsistency sets a bit here and the host turns it into BKM_ERR_DEVICE.
+enum : uint32_t {
+	STATUS_WAIT_TIMEOUT = 1u,   // an mbarrier / flag wait hit its iteration limit
+	STATUS_BAD_INDEX = 2u,      // an assignment >= k was seen by the update
+	STATUS_LIST_OVERFLOW = 4u,  // the near-tie list was too short (cannot happen when sized n)
+};
+
+// Device-resident control block shared by the kernels of one handle / one stateless call.
+struct Control {
+	uint32_t status;       // STATUS_* bits
+	uint32_t flag_count;   // number of points queued for the exact re-check
+	float cmax2[2];        // max over clusters of |mean|^2; the preparation of iteration t
+	                       // writes slot (t+1)&1 with atomicMax and clears slot t&1
+	uint32_t last_flag_count; // flag_count of the last finished iteration (for reporting)
+	uint32_t pad[3];
+};
+
+// Element offset of (item, dim) in a buffer of `items` vectors of `dims` floats.
+// AoS: item*dims + dim, SoA: dim*items + item (the reference's layout policies, ALIGN = 1).
+template<bool SOA>
+__host__ __device__ __forceinline__ size_t at(size_t item, size_t dim, size_t items, size_t dims)
+{
+	return SOA ? dim * items + item : item * dims + dim;
+}
+
+__host__ __device__ __forceinline__ size_t at_rt(int soa, size_t item, size_t dim, size_t items, size_t dims)
+{
+	return soa ? dim * items + item : item * dims + dim;
+}
+
+__host__ __device__ __forceinline__ uint32_t round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
+__host__ __device__ __forceinline__ uint64_t round_up64(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
+
+// Row stride (floats) of the prepared means used by the CUDA-core assignment:
+// [ |c|^2, -2*c_0 ... -2*c_{d-1}, 0-padding ] rounded to a multiple of 4 floats.
+__host__ __device__ __forceinline__ uint32_t simt_row_stride(uint32_t dim) { return round_up(dim + 1, 4); }
+
+// Rows of the prepared means: k rounded to a multiple of 4; padding rows have |c|^2 = +inf.
+__host__ __device__ __forceinline__ uint32_t simt_rows(uint32_t k) { return round_up(k, 4); }
+
+// Geometry of the tensor-core operands: K (dimension) padded to 32 floats (one 128-byte
+// swizzle row), point rows padded to 128, mean rows padded to 16.
+constexpr uint32_t TC_KCHUNK = 32;
+constexpr uint32_t TC_MTILE = 128;
+__host__ __device__ __forceinline__ uint32_t tc_dpad(uint32_t dim) { return round_up(dim, TC_KCHUNK); }
+
+} // namespace bkm

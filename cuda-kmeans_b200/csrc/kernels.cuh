@@ -1,0 +1,76 @@
+// Internal launch interface between the host driver (api.cu) and the kernel files.
+#pragma once
+
+#include "common.cuh"
+
+namespace bkm {
+
+struct Shape {
+	uint64_t n;     // local points
+	uint32_t k;
+	uint32_t dim;
+	int soa;        // points layout is SoA
+	int soa_means;  // means layout is SoA
+};
+
+// Operands of the tensor-core assignment derived from the means (rewritten every iteration).
+struct TcMeans {
+	float* b_hi;     // [k_pad][d_pad] tf32 high part of -2*mean, K-major
+	float* b_lo;     // [k_pad][d_pad] tf32 low part
+	float* cnorm;    // [k_pad] |mean|^2, +inf for padding rows
+	uint32_t k_pad;  // k rounded up to the centroid tile
+	uint32_t d_pad;  // dim rounded up to TC_KCHUNK
+};
+
+// Operands derived from the points (written once per initialize).
+struct TcPoints {
+	float* a_hi;     // [n_pad][d_pad]
+	float* a_lo;     // [n_pad][d_pad]
+	float* xnorm;    // [n_pad] |x|^2
+	uint64_t n_pad;  // n rounded up to TC_MTILE
+	uint32_t d_pad;
+};
+
+// ---- means preparation + divide (update.cu) ----
+
+// means (given layout) -> CUDA-core rows and/or tensor-core operands; cmax2 -> ctl slot.
+// `cprep` / `tc` may be null.  Also clears flag_count.
+// `slot` is the cmax2 slot to fill (it must be zero on entry).
+void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,
+	Control* ctl, int slot, cudaStream_t stream);
+
+// acc/counts -> means_out (given layout), sizes_out, then the same preparation as above from
+// the fresh means; clears acc, counts and flag_count for the next iteration.
+void launch_finalize(float* acc, uint32_t* counts, float* means_out, uint32_t* sizes_out, const Shape& s,
+	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
+
+// ---- update (update.cu) ----
+// variant: BKM_UPDATE_SHARED or BKM_UPDATE_GLOBAL (already resolved).  acc/counts must be zero.
+// Returns false when the shared variant cannot hold k*dim in shared memory.
+bool update_shared_fits(const Shape& s, int device);
+void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, const Shape& s,
+	int variant, Control* ctl, int sm_count, cudaStream_t stream);
+
+// ---- assignment on CUDA cores (assign_simt.cu) ----
+// Exact reference arithmetic.  With list != null only the points list[0..*list_count) are done.
+cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream);
+
+// Small-d fast pass (dim <= 8): approximate distances, near-ties appended to flag_list.
+bool assign_simt_supported(const Shape& s);
+cudaError_t launch_assign_simt(const float* pts, const float* cprep, uint32_t* asg, const Shape& s,
+	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream);
+
+// ---- assignment on tensor cores (assign_tc.cu) ----
+bool assign_tc_supported(const Shape& s);
+uint32_t tc_kpad(uint32_t k);
+// One-off split of the points into tf32 hi/lo K-major planes + |x|^2.
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, cudaStream_t stream);
+// Opaque per-handle state (tensor maps).  Created once the operand buffers exist.
+struct TcPlan;
+TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err);
+void tc_plan_destroy(TcPlan* plan);
+cudaError_t launch_assign_tc(TcPlan* plan, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
+	float margin_scale, cudaStream_t stream);
+
+} // namespace bkm

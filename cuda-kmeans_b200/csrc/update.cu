@@ -1,0 +1,282 @@
+// Update step: per-cluster sums and sizes, merge, divide, and the preparation of the
+// assignment operands from the fresh means.
+//
+//  * update_kernel<SOA, SHARED>: every block owns a contiguous slice of the points and
+//    accumulates it with atomics either into shared-memory copies of the k x dim buckets
+//    (SHARED; `replicas` copies, picked by warp so that warps hitting the same hot cluster do
+//    not contend on one address) followed by one merge into the global accumulators, or
+//    straight into the global accumulators when k*dim does not fit.  Replaces
+//    updateAtomicPointKernel / updateAtomicFineKernel / updateAtomicShmKernel
+//    (kernels/kernels.cu:727-743, 771-791, 818-858 of the reference) and follows the shared
+//    privatisation idea of atomicShm2Kernel (bucketing-cuda kernels/kernels.cu:382-422).
+//
+//  * finalize_prepare_kernel: mean = sum / size (an empty cluster keeps zeros), written in the
+//    means layout - the work of reducePrivCopiesKernel + divideMeansKernel
+//    (kernels/kernels.cu:116-135, 150-163) - fused with the derivation of the operands the
+//    next assignment reads and with clearing the accumulators (fillZeros, :13-17).
+#include "kernels.cuh"
+#include "../../include/bkm.h"
+
+#include <algorithm>
+#include <cmath>
+
+namespace bkm {
+
+constexpr int UPD_THREADS = 512;
+constexpr size_t SMEM_LIMIT = 227 * 1024;
+
+__device__ __forceinline__ float tf32_rna(float x)
+{
+	uint32_t u;
+	asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+	return __uint_as_float(u);
+}
+
+// ------------------------------------------------------------------------------------------
+// finalize / prepare
+// ------------------------------------------------------------------------------------------
+
+template<bool FINALIZE>
+__global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict__ acc, uint32_t* __restrict__ counts,
+	const float* __restrict__ means_in, float* __restrict__ means_out, uint32_t* __restrict__ sizes_out,
+	uint32_t k, uint32_t d, int soa_means,
+	float* __restrict__ cprep, uint32_t rs, uint32_t srows,
+	float* __restrict__ b_hi, float* __restrict__ b_lo, float* __restrict__ cnorm, uint32_t k_pad, uint32_t d_pad,
+	Control* __restrict__ ctl, int slot)
+{
+	const uint32_t lane = threadIdx.x & 31u;
+	const uint32_t wpb = blockDim.x >> 5;
+	uint32_t rows_total = k;
+	if (cprep && srows > rows_total) rows_total = srows;
+	if (cnorm && k_pad > rows_total) rows_total = k_pad;
+
+	for (uint32_t c = blockIdx.x * wpb + (threadIdx.x >> 5); c < rows_total; c += gridDim.x * wpb) {
+		if (c < k) {
+			uint32_t cnt = 0;
+			if (FINALIZE) cnt = counts[c];
+			const float divisor = (float)cnt;
+			float s2 = 0.0f;
+			for (uint32_t j = lane; j < d; j += 32) {
+				float mean;
+				const size_t mi = at_rt(soa_means, c, j, k, d);
+				if (FINALIZE) {
+					const float sum = acc[(size_t)c * d + j];
+					acc[(size_t)c * d + j] = 0.0f;
+					mean = cnt ? __fdiv_rn(sum, divisor) : 0.0f;
+					means_out[mi] = mean;
+				} else {
+					mean = means_in[mi];
+				}
+				s2 = fmaf(mean, mean, s2);
+				const float b = -2.0f * mean;
+				if (cprep) cprep[(size_t)c * rs + 1 + j] = b;
+				if (b_hi) {
+					const float hi = tf32_rna(b);
+					const float lo = tf32_rna(b - hi);
+					b_hi[(size_t)c * d_pad + j] = hi;
+					b_lo[(size_t)c * d_pad + j] = lo;
+				}
+			}
+			#pragma unroll
+			for (int off = 16; off > 0; off >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+			__syncwarp();
+			if (lane == 0) {
+				if (cprep) cprep[(size_t)c * rs] = s2;
+				if (cnorm) cnorm[c] = s2;
+				atomicMax(reinterpret_cast<int*>(&ctl->cmax2[slot]), __float_as_int(s2));
+				if (FINALIZE) { sizes_out[c] = cnt; counts[c] = 0; }
+			}
+		} else if (lane == 0) {
+			// padding rows can never win: their |c|^2 is +inf (the -2c part stays zero)
+			if (cprep && c < srows) cprep[(size_t)c * rs] = INFINITY;
+			if (cnorm && c < k_pad) cnorm[c] = INFINITY;
+		}
+	}
+	if (blockIdx.x == 0 && threadIdx.x == 0) {
+		ctl->last_flag_count = ctl->flag_count;
+		ctl->flag_count = 0;
+		ctl->cmax2[slot ^ 1] = 0.0f;
+	}
+}
+
+static void launch_fp(bool finalize, float* acc, uint32_t* counts, const float* means_in, float* means_out,
+	uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
+{
+	const uint32_t rs = simt_row_stride(s.dim);
+	const uint32_t srows = simt_rows(s.k);
+	uint32_t rows_total = s.k;
+	if (cprep) rows_total = std::max(rows_total, srows);
+	if (tc) rows_total = std::max(rows_total, tc->k_pad);
+	const uint32_t wpb = 8;
+	uint32_t grid = (rows_total + wpb - 1) / wpb;
+	grid = std::min<uint32_t>(std::max<uint32_t>(grid, 1), 148 * 8);
+	float* bh = tc ? tc->b_hi : nullptr;
+	float* bl = tc ? tc->b_lo : nullptr;
+	float* cn = tc ? tc->cnorm : nullptr;
+	uint32_t kp = tc ? tc->k_pad : 0, dp = tc ? tc->d_pad : 0;
+	if (finalize)
+		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, means_in, means_out, sizes_out,
+			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, kp, dp, ctl, slot);
+	else
+		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, means_in, means_out, sizes_out,
+			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, kp, dp, ctl, slot);
+}
+
+void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,
+	Control* ctl, int slot, cudaStream_t stream)
+{
+	launch_fp(false, nullptr, nullptr, means, nullptr, nullptr, s, cprep, tc, ctl, slot, stream);
+}
+
+void launch_finalize(float* acc, uint32_t* counts, float* means_out, uint32_t* sizes_out, const Shape& s,
+	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
+{
+	launch_fp(true, acc, counts, nullptr, means_out, sizes_out, s, cprep, tc, ctl, slot, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// update
+// ------------------------------------------------------------------------------------------
+
+template<bool SOA, bool SHARED>
+__global__ void __launch_bounds__(UPD_THREADS) update_kernel(const float* __restrict__ pts,
+	const uint32_t* __restrict__ asg, float* __restrict__ acc, uint32_t* __restrict__ counts,
+	uint64_t n, uint32_t k, uint32_t d, uint32_t dstride, uint32_t replicas, Control* __restrict__ ctl)
+{
+	extern __shared__ __align__(16) float sacc[];
+	const uint32_t tid = threadIdx.x;
+	const size_t rep_floats = (size_t)k * dstride;
+	uint32_t* scnt = reinterpret_cast<uint32_t*>(sacc + rep_floats * replicas);
+
+	float* my;
+	uint32_t* mycnt;
+	uint32_t stride;
+	if (SHARED) {
+		for (size_t e = tid; e < rep_floats * replicas + (size_t)k * replicas; e += UPD_THREADS) sacc[e] = 0.0f;
+		__syncthreads();
+		const uint32_t r = (tid >> 5) % replicas;
+		my = sacc + rep_floats * r;
+		mycnt = scnt + (size_t)k * r;
+		stride = dstride;
+	} else {
+		my = acc;
+		mycnt = counts;
+		stride = d;
+	}
+
+	// contiguous slice of points per block, a multiple of 32 points
+	uint64_t per = (n + gridDim.x - 1) / gridDim.x;
+	per = (per + 31) / 32 * 32;
+	const uint64_t p0 = (uint64_t)blockIdx.x * per;
+	uint64_t p1 = p0 + per;
+	if (p1 > n) p1 = n;
+	bool bad = false;
+
+	if (p0 < p1) {
+		if (SOA) {
+			for (uint64_t i = p0 + tid; i < p1; i += UPD_THREADS) {
+				const uint32_t a = asg[i];
+				if (a >= k) { bad = true; continue; }
+				atomicAdd(&mycnt[a], 1u);
+				float* row = my + (size_t)a * stride;
+				uint32_t j = 0;
+				for (; j + 4 <= d; j += 4) {
+					const float v0 = pts[(size_t)(j + 0) * n + i];
+					const float v1 = pts[(size_t)(j + 1) * n + i];
+					const float v2 = pts[(size_t)(j + 2) * n + i];
+					const float v3 = pts[(size_t)(j + 3) * n + i];
+					atomicAdd(&row[j + 0], v0);
+					atomicAdd(&row[j + 1], v1);
+					atomicAdd(&row[j + 2], v2);
+					atomicAdd(&row[j + 3], v3);
+				}
+				for (; j < d; ++j) atomicAdd(&row[j], pts[(size_t)j * n + i]);
+			}
+		} else {
+			// flat walk over the (p1-p0)*d values of the slice; (point, dim) advance without division
+			const uint64_t count = (p1 - p0) * d;
+			const float* src = pts + (size_t)p0 * d;
+			const uint32_t* a_src = asg + p0;
+			uint64_t il = tid / d;
+			uint32_t j = tid % d;
+			const uint32_t step_i = UPD_THREADS / d, step_j = UPD_THREADS % d;
+			for (uint64_t le = tid; le < count; le += UPD_THREADS) {
+				const uint32_t a = a_src[il];
+				const float v = src[le];
+				if (a < k) {
+					atomicAdd(&my[(size_t)a * stride + j], v);
+					if (j == 0) atomicAdd(&mycnt[a], 1u);
+				} else {
+					bad = true;
+				}
+				il += step_i;
+				j += step_j;
+				if (j >= d) { j -= d; ++il; }
+			}
+		}
+	}
+	if (bad) atomicOr(&ctl->status, (uint32_t)STATUS_BAD_INDEX);
+
+	if (SHARED) {
+		__syncthreads();
+		const uint32_t kd = k * d;
+		uint32_t c = tid / d, j = tid % d;
+		const uint32_t step_c = UPD_THREADS / d, step_j = UPD_THREADS % d;
+		for (uint32_t e = tid; e < kd; e += UPD_THREADS) {
+			float s = 0.0f;
+			for (uint32_t r = 0; r < replicas; ++r) s += sacc[rep_floats * r + (size_t)c * dstride + j];
+			if (s != 0.0f) atomicAdd(&acc[e], s);
+			c += step_c;
+			j += step_j;
+			if (j >= d) { j -= d; ++c; }
+		}
+		for (uint32_t cc = tid; cc < k; cc += UPD_THREADS) {
+			uint32_t t = 0;
+			for (uint32_t r = 0; r < replicas; ++r) t += scnt[(size_t)k * r + cc];
+			if (t) atomicAdd(&counts[cc], t);
+		}
+	}
+}
+
+static size_t update_replica_bytes(const Shape& s)
+{
+	const uint32_t dstride = s.dim | 1u;
+	return (size_t)s.k * (dstride + 1) * sizeof(float);
+}
+
+bool update_shared_fits(const Shape& s, int /*device*/)
+{
+	return update_replica_bytes(s) <= SMEM_LIMIT - 1024 && (uint64_t)s.k * s.dim < (1ull << 31);
+}
+
+void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, const Shape& s,
+	int variant, Control* ctl, int sm_count, cudaStream_t stream)
+{
+	const uint32_t dstride = s.dim | 1u;
+	const bool shared = variant == BKM_UPDATE_SHARED;
+	uint32_t replicas = 1;
+	size_t smem = 0;
+	if (shared) {
+		const size_t per = update_replica_bytes(s);
+		// aim at two resident blocks per SM when one replica is small enough, and at most 4 replicas
+		const size_t budget = per <= 100 * 1024 ? 100 * 1024 : SMEM_LIMIT - 1024;
+		replicas = (uint32_t)std::min<size_t>(4, std::max<size_t>(1, budget / per));
+		smem = per * replicas;
+	}
+	int per_sm = 1;
+#define BKM_LAUNCH_UPD(SOA, SH) do { \
+		auto kern = update_kernel<SOA, SH>; \
+		if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+		cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, UPD_THREADS, smem); \
+		if (per_sm < 1) per_sm = 1; \
+		if (per_sm > 4) per_sm = 4; \
+		uint64_t want = (s.n + 1023) / 1024; \
+		uint32_t grid = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(want, 1), (uint64_t)sm_count * per_sm); \
+		kern<<<grid, UPD_THREADS, smem, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dstride, replicas, ctl); \
+	} while (0)
+	if (s.soa) { if (shared) BKM_LAUNCH_UPD(true, true); else BKM_LAUNCH_UPD(true, false); }
+	else       { if (shared) BKM_LAUNCH_UPD(false, true); else BKM_LAUNCH_UPD(false, false); }
+#undef BKM_LAUNCH_UPD
+}
+
+} // namespace bkm

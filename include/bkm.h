@@ -1,0 +1,217 @@
+/*
+ * bkm.h - C ABI of the B200 k-means iteration library (libbkm.so).
+ *
+ * The library implements one Lloyd iteration (nearest-centroid assignment + bucketed
+ * sum/count update + divide) and the fixed-iteration loop around it, in fp32, on NVIDIA
+ * B200 (sm_100a).  It is the drop-in for the per-iteration hot path of
+ * krulis-martin/cuda-kmeans; each entry point names the reference interface it replaces
+ * (paths relative to experimental/k-means/k-means/ of that project).
+ *
+ * Conventions
+ *   - Every function returns BKM_OK (0) or an error code; bkm_last_error() then returns a
+ *     thread-local, human-readable message.  No exception crosses this boundary.
+ *   - Layout codes follow the reference's layout policies with ALIGN = 1
+ *     (headers/layout_policies.hpp:16-36, 40-60):
+ *       BKM_LAYOUT_AOS: element (item i, dimension j) at  p[i*dim + j]
+ *       BKM_LAYOUT_SOA: element (item i, dimension j) at  p[j*items + i]
+ *     where items = n for points and items = k for means.
+ *   - Nearest means the smallest Euclidean distance as the reference's serial code computes
+ *     it (headers/serial.hpp:21-35): the lowest index wins exact ties.
+ *   - An empty cluster gets the all-zero mean (headers/serial.hpp:49-54, 66-67).
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     BKM_ERR_CUDA.
+ */
+#ifndef BKM_H
+#define BKM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BKM_OK 0
+#define BKM_ERR_INVALID 1      /* bad argument (null pointer, zero size, unknown code) */
+#define BKM_ERR_CUDA 2         /* a CUDA runtime/driver call failed, or no device */
+#define BKM_ERR_NCCL 3         /* NCCL missing or a NCCL call failed */
+#define BKM_ERR_UNSUPPORTED 4  /* shape outside what the selected variant handles */
+#define BKM_ERR_STATE 5        /* call order violated (e.g. run before initialize) */
+#define BKM_ERR_DEVICE 6       /* a kernel reported an internal error (bounded wait ran out) */
+
+#define BKM_LAYOUT_AOS 0
+#define BKM_LAYOUT_SOA 1
+
+/* Assignment variants (the counterpart of choosing ASGN_KERNEL in headers/cuda.hpp:15-19). */
+#define BKM_ASSIGN_AUTO 0   /* pick by shape */
+#define BKM_ASSIGN_EXACT 1  /* CUDA cores, reference arithmetic for every point (any shape) */
+#define BKM_ASSIGN_SIMT 2   /* CUDA cores, small-d fast path (dim <= 8), near-ties re-checked exactly */
+#define BKM_ASSIGN_TC 3     /* tcgen05 tensor cores, split-TF32 GEMM form, near-ties re-checked exactly */
+
+/* Update variants (the counterpart of choosing UPDATE_KERNEL). */
+#define BKM_UPDATE_AUTO 0
+#define BKM_UPDATE_SHARED 1  /* shared-memory privatised buckets + one global merge */
+#define BKM_UPDATE_GLOBAL 2  /* global atomics only (any k*dim) */
+
+const char* bkm_last_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int bkm_version(void);
+
+/* Number of visible CUDA devices (0 without a GPU; never fails). */
+int bkm_device_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Kernel-runner entry points: device pointers in, device pointers out, stream-ordered, no
+ * allocation.  `workspace` is device scratch of at least bkm_workspace_bytes(n,k,dim) bytes,
+ * 256-byte aligned, owned by the caller; its contents are undefined between calls.
+ * `stream` is a cudaStream_t (NULL = legacy default stream, which is what the reference's
+ * runners launch on, kernels/kernels.cu:201-207).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Scratch size for the three calls below (0 on overflow or bad arguments). */
+size_t bkm_workspace_bytes(uint64_t n, uint32_t k, uint32_t dim);
+
+/* assignment[i] = index of the mean nearest to point i.
+ * Replaces ASGN_KERNEL::run(const AssignmentProblemInstance<F,IDX_T>&, CudaExecParameters&)
+ * (headers/kernels.cuh:8-20, 81-93; runners kernels/kernels.cu:201-207, 297-319, 688-717). */
+int bkm_assign_f32(const float* points, const float* means, uint32_t* assignment,
+                   uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means,
+                   int variant, void* workspace, size_t workspace_bytes, void* stream);
+
+/* means[c][:] = average of the points with assignment c, sizes[c] = their number.  The
+ * outputs are fully overwritten (the caller need not zero them, and may).
+ * Replaces UPDATE_KERNEL::run(const UpdateProblemInstance<F,IDX_T>&, CudaExecParameters&)
+ * including its trailing merge and divide (headers/kernels.cuh:24-36, 96-105; runners
+ * kernels/kernels.cu:746-761, 794-809, 861-878). */
+int bkm_update_f32(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
+                   uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means,
+                   int variant, void* workspace, size_t workspace_bytes, void* stream);
+
+/* One whole iteration: means_out/sizes from means_in.  `assignment` may be NULL when the
+ * caller does not want it, as in the reference's fused runners.
+ * Replaces KERNEL::run(const FusedProblemInstance<F,IDX_T>&, CudaExecParameters&)
+ * (headers/kernels.cuh:40-52, 108-116; runners kernels/kernels.cu:951-998, 1146-1190). */
+int bkm_iterate_f32(const float* points, const float* means_in, float* means_out, uint32_t* sizes,
+                    uint32_t* assignment, uint64_t n, uint32_t k, uint32_t dim, int layout,
+                    int layout_means, int variant_assign, int variant_update,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Waits for `stream` and returns BKM_ERR_DEVICE if a kernel of the calls issued on this
+ * workspace since its last check recorded an error (a bounded wait that ran out, an assignment
+ * value >= k fed to the update).  The counterpart of the reference's CUCH(cudaGetLastError())
+ * after each runner (headers/cuda.hpp:76, 83). */
+int bkm_workspace_check(const void* workspace, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fixed-iteration driver.  Replaces CudaKMeansAlgorithm (headers/cuda.hpp:19-112) behind the
+ * IKMeansAlgorithm call sequence initialize / run / getMeans / getAssignment / cleanup
+ * (headers/interface.hpp:8-49).  One handle drives one GPU; with world_size > 1 every rank
+ * holds a contiguous shard of the points and the per-iteration sums and sizes are
+ * all-reduced with NCCL before the divide.
+ * ------------------------------------------------------------------------------------------ */
+
+typedef struct bkm_handle_s* bkm_handle_t;
+
+typedef struct bkm_config_s {
+	uint64_t n;            /* points held by THIS handle (the local shard) */
+	uint32_t k;            /* clusters */
+	uint32_t dim;          /* dimensions */
+	int32_t layout;        /* BKM_LAYOUT_* of the points (local shard: items = n) */
+	int32_t layout_means;  /* BKM_LAYOUT_* of the means */
+	int32_t device;        /* CUDA device ordinal */
+	int32_t variant_assign;/* BKM_ASSIGN_* */
+	int32_t variant_update;/* BKM_UPDATE_* */
+	int32_t reserved;      /* must be 0 */
+} bkm_config_t;
+
+/* Allocates the device state for the configuration (no data yet). */
+int bkm_create(const bkm_config_t* config, bkm_handle_t* out);
+
+/* Frees everything the handle owns (cleanup(), headers/cuda.hpp:102-111). */
+int bkm_destroy(bkm_handle_t h);
+
+/* Makes all work of the handle run on `stream` (a cudaStream_t of the handle's device)
+ * instead of the stream the handle created for itself. */
+int bkm_set_stream(bkm_handle_t h, void* stream);
+
+/* Tunables: "margin_scale" (float multiplier on the near-tie band, default 1),
+ * "blocks_per_sm_update" etc.  Unknown names fail with BKM_ERR_INVALID. */
+int bkm_set_option(bkm_handle_t h, const char* name, double value);
+
+/* initialize(): copies points and initial means from HOST memory, runs the one-off
+ * preprocessing of the immutable points, resets the iteration state
+ * (headers/cuda.hpp:45-68).  Synchronous. */
+int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_means);
+
+/* Same with DEVICE pointers.  The points are borrowed, not copied: they must stay valid and
+ * unchanged until the next initialize or destroy.  The means are copied. */
+int bkm_initialize_device(bkm_handle_t h, const float* dev_points, const float* dev_means);
+
+/* run(): `iters` iterations of assign -> update (-> all-reduce) -> divide, then one
+ * synchronisation, like headers/cuda.hpp:70-88.  Iterations continue from the current
+ * means, so run(a) followed by run(b) equals run(a+b). */
+int bkm_run(bkm_handle_t h, uint32_t iters);
+
+/* As bkm_run without the final synchronisation (enqueue only). */
+int bkm_run_async(bkm_handle_t h, uint32_t iters);
+
+/* Waits for the handle's stream and reports any error a kernel recorded. */
+int bkm_synchronize(bkm_handle_t h);
+
+/* getMeans()/getAssignment(): results of the last completed iteration to HOST memory
+ * (headers/cuda.hpp:90-100).  The assignment is the one computed in the last iteration,
+ * i.e. against the means of the iteration before.  Sizes are the (global) cluster sizes. */
+int bkm_get_means(bkm_handle_t h, float* host_means);
+int bkm_get_assignment(bkm_handle_t h, uint32_t* host_assignment);
+int bkm_get_sizes(bkm_handle_t h, uint32_t* host_sizes);
+
+/* Device pointers of the same results (valid until the next run/initialize/destroy). */
+int bkm_device_means(bkm_handle_t h, const float** dev_means);
+int bkm_device_assignment(bkm_handle_t h, const uint32_t** dev_assignment);
+
+/* Replaces the current means from HOST memory (resume from saved centroids). */
+int bkm_set_means(bkm_handle_t h, const float* host_means);
+
+/* Iterations completed since the last initialize. */
+int bkm_iterations_done(bkm_handle_t h, uint64_t* out);
+
+/* Device time per phase, averaged over the iterations of the most recent run (at most the
+ * last 256), in milliseconds: out[0]=assignment pass, out[1]=exact re-check of near-ties,
+ * out[2]=update, out[3]=all-reduce, out[4]=divide + operand preparation, out[5]=whole
+ * iteration.  Taken with CUDA events on the handle's stream. */
+int bkm_phase_ms(bkm_handle_t h, float out[6]);
+
+/* Counters of the most recent iteration: out[0]=points re-checked exactly,
+ * out[1]=kernels launched per iteration, out[2]=assignment variant used,
+ * out[3]=update variant used. */
+int bkm_counters(bkm_handle_t h, uint64_t out[4]);
+
+/* ---- multi-GPU (one process per GPU) ------------------------------------------------------ */
+
+/* Fills `id` (128 bytes) with a fresh NCCL unique id; rank 0 calls it and hands the bytes
+ * to the other ranks by whatever means the launcher offers. */
+int bkm_comm_unique_id(void* id, size_t id_bytes);
+
+/* Joins the handle to a communicator of `world_size` ranks.  Collective: every rank calls it
+ * with the same id.  After it, every bkm_run all-reduces sums and sizes over the ranks. */
+int bkm_comm_init(bkm_handle_t h, const void* id, size_t id_bytes, int world_size, int rank);
+
+/* [begin, begin+count) of the points rank `rank` of `world_size` holds when `n_total` points
+ * are split into contiguous, near-equal shards (pure host arithmetic, no GPU needed). */
+int bkm_shard_range(uint64_t n_total, int world_size, int rank, uint64_t* begin, uint64_t* count);
+
+/* ---- host-buffer convenience --------------------------------------------------------------
+ * The whole job with HOST buffers in one call: create, initialize (host->device), run,
+ * fetch results (device->host), destroy - the sequence the reference harness performs in
+ * run_kmeans (k-means.cpp:118-189).  `means` holds the initial means on entry and the final
+ * means on return. */
+int bkm_kmeans_host_f32(const float* host_points, float* means, uint32_t* assignment,
+                        uint64_t n, uint32_t k, uint32_t dim, uint32_t iters,
+                        int layout, int layout_means, int device);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* BKM_H */

@@ -1,0 +1,62 @@
+"""TEST INFRASTRUCTURE - build recipe for the CPU checkers.
+
+Builds two shared libraries:
+
+* ``oracle/libkmoracle.so`` from ``oracle/kmeans_oracle.c`` (the plain-C restatement), and
+* ``oracle/_ref/libkmref.so`` from ``oracle/ref_shim.cpp`` + the reference project's own
+  headers, compiled where they lie (``-I <reference>/experimental/k-means/k-means/headers``)
+  with the flags of the reference Makefile (``-O3 -std=c++14 -DNDEBUG``,
+  experimental/k-means/k-means/Makefile:1-3).  Skipped when the reference checkout is absent
+  (the prebuilt file is then used if it exists).
+
+Run ``python oracle/build_oracle.py``; the reference location can be overridden with the
+environment variable ``KMEANS_REFERENCE_DIR``.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_DIR = os.environ.get("KMEANS_REFERENCE_DIR", "/root/reference")
+REF_HEADERS = os.path.join(REF_DIR, "experimental", "k-means", "k-means", "headers")
+
+ORACLE_SO = os.path.join(HERE, "libkmoracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libkmref.so")
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def build_oracle(force=False):
+    src = os.path.join(HERE, "kmeans_oracle.c")
+    if not force and _newer(ORACLE_SO, [src]):
+        return ORACLE_SO
+    cmd = ["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
+           "-o", ORACLE_SO, src, "-lm"]
+    subprocess.check_call(cmd)
+    return ORACLE_SO
+
+
+def build_ref(force=False):
+    """Returns the path of the compiled reference, or None when it cannot be had."""
+    src = os.path.join(HERE, "ref_shim.cpp")
+    have_ref = os.path.isfile(os.path.join(REF_HEADERS, "serial.hpp"))
+    if not have_ref:
+        return REF_SO if os.path.exists(REF_SO) else None
+    if not force and _newer(REF_SO, [src]):
+        return REF_SO
+    os.makedirs(os.path.dirname(REF_SO), exist_ok=True)
+    cmd = ["g++", "-O3", "-std=c++14", "-DNDEBUG", "-fPIC", "-shared", "-I", REF_HEADERS,
+           "-o", REF_SO, src]
+    subprocess.check_call(cmd)
+    return REF_SO
+
+
+if __name__ == "__main__":
+    force = "--force" in sys.argv
+    print(build_oracle(force))
+    print(build_ref(force))

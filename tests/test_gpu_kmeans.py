@@ -1,0 +1,147 @@
+"""GPU: the fixed-iteration driver (bkm_create ... bkm_run) against the oracle: golden
+trajectories, the benchmark configurations at reduced size, and size-independent properties
+at full size."""
+import numpy as np
+import pytest
+
+from helpers import assignment_mismatches, means_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _stepwise(pkg, oracle, data, means, n, k, d, iters, layout, layout_means, **kw):
+    """Runs `iters` iterations one at a time; after each, the GPU's assignment must equal the
+    oracle's assignment for the GPU's previous means (near-ties excepted), and the GPU's means
+    the oracle's update of that assignment."""
+    km = pkg.KMeans(layout=layout, layout_means=layout_means, **kw)
+    km.initialize(d, k, n, iters, data, means)
+    prev = np.asarray(means, dtype=np.float32).reshape(-1).copy()
+    total_exact = 0
+    for it in range(iters):
+        km.run(1)
+        asg, cur = km.getAssignment(), km.getMeans()
+        exact, bad = assignment_mismatches(oracle, asg, data, prev, n, k, d, layout, layout_means)
+        assert bad == 0, (it, exact, bad)
+        total_exact += exact
+        want, sizes = oracle.update(data, asg, n, k, d, layout, layout_means)
+        ok, err = means_close(cur, want)
+        assert ok, (it, err)
+        assert np.array_equal(km.getSizes(), sizes), it
+        prev = cur
+    info = km.counters()
+    km.cleanup()
+    return total_exact, info
+
+
+def test_golden_trajectories(pkg, torch_cuda, golden):
+    for c in golden:
+        km = pkg.KMeans(layout=c["layout"], layout_means=c["layout_means"])
+        km.initialize(c["d"], c["k"], c["n"], c["iters"], c["data"], c["means"])
+        km.run()
+        means, asg = km.getMeans(), km.getAssignment()
+        assert km.iterations_done() == c["iters"]
+        km.cleanup()
+        ok, err = means_close(means, c["out_means"])
+        assert ok, (c["name"], err)
+        assert (asg != c["out_assignment"]).mean() <= 1e-3, c["name"]
+
+
+def test_golden_stepwise_every_iteration(pkg, torch_cuda, oracle_mod, golden):
+    for c in golden:
+        _stepwise(pkg, oracle_mod, c["data"], c["means"], c["n"], c["k"], c["d"], c["iters"],
+                  c["layout"], c["layout_means"])
+
+
+def test_run_is_resumable(pkg, torch_cuda, golden):
+    c = golden[1]
+    a = pkg.KMeans(layout=c["layout"], layout_means=c["layout_means"])
+    a.initialize(c["d"], c["k"], c["n"], 4, c["data"], c["means"])
+    a.run(4)
+    b = pkg.KMeans(layout=c["layout"], layout_means=c["layout_means"])
+    b.initialize(c["d"], c["k"], c["n"], 4, c["data"], c["means"])
+    b.run(1)
+    b.run(3)
+    assert np.array_equal(a.getAssignment(), b.getAssignment())
+    ok, _ = means_close(a.getMeans(), b.getMeans(), rtol=1e-6)
+    assert ok
+    # resume from saved means in a fresh handle
+    saved = a.getMeans()
+    a.run(1)
+    r = pkg.KMeans(layout=c["layout"], layout_means=c["layout_means"])
+    r.initialize(c["d"], c["k"], c["n"], 1, c["data"], c["means"])
+    r.set_means(saved)
+    r.run(1)
+    assert np.array_equal(a.getAssignment(), r.getAssignment())
+    for km in (a, b, r):
+        km.cleanup()
+
+
+def test_kmeans_host_entry_point(pkg, torch_cuda, golden):
+    c = golden[4]
+    means, asg = pkg.kmeans_host(c["data"], c["means"], c["n"], c["k"], c["d"], c["iters"], c["layout"], c["layout_means"])
+    ok, err = means_close(means, c["out_means"])
+    assert ok, err
+    assert (asg != c["out_assignment"]).mean() <= 1e-3
+
+
+@pytest.mark.parametrize("name,n,iters", [("c1", 1 << 16, 10), ("c2", 1 << 15, 3), ("c3", 1 << 18, 4), ("c5", 1 << 17, 3)])
+def test_benchmark_configs_stepwise(pkg, torch_cuda, oracle_mod, workloads, name, n, iters):
+    data, means, spec = workloads.make(name, n=n)
+    _stepwise(pkg, oracle_mod, data, means, n, spec["k"], spec["dim"], iters, spec["layout"], spec["layout_means"])
+
+
+def test_c4_shape_reduced(pkg, torch_cuda, oracle_mod, workloads):
+    """dim 512: dense-contraction regime at a size the oracle finishes quickly."""
+    n, k, d = 2048, 256, 512
+    rows = workloads.generate_rows("sphere", n, d, k, seed=5)
+    data, means = workloads.to_layout(rows, 0), workloads.to_layout(rows[:k], 0)
+    _stepwise(pkg, oracle_mod, data, means, n, k, d, 2, 0, 0)
+
+
+def test_variants_agree(pkg, torch_cuda, oracle_mod, workloads):
+    data, means, spec = workloads.make("c1", n=1 << 14)
+    outs = []
+    for va in (pkg.ASSIGN_EXACT, pkg.ASSIGN_SIMT, pkg.ASSIGN_TC):
+        for vu in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL):
+            km = pkg.KMeans(layout=spec["layout"], variant_assign=va, variant_update=vu)
+            km.initialize(spec["dim"], spec["k"], 1 << 14, 3, data, means)
+            km.run()
+            outs.append((km.getAssignment(), km.getMeans()))
+            km.cleanup()
+    for asg, mns in outs[1:]:
+        assert (asg != outs[0][0]).mean() <= 1e-3
+        ok, err = means_close(mns, outs[0][1])
+        assert ok, err
+
+
+def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
+    """Headline configuration at full size: conservation laws + a sampled oracle check."""
+    data, means, spec = workloads.make("c2")
+    n, k, d, lay = spec["n"], spec["k"], spec["dim"], spec["layout"]
+    km = pkg.KMeans(layout=lay)
+    km.initialize(d, k, n, 3, data, means)
+    km.run(2)
+    prev = km.getMeans()
+    km.run(1)
+    asg, cur, sizes = km.getAssignment(), km.getMeans(), km.getSizes()
+    info = km.counters()
+    km.cleanup()
+    assert info["assign_variant"] == "tc"
+    assert asg.max() < k
+    assert int(sizes.astype(np.int64).sum()) == n
+    assert np.array_equal(np.bincount(asg, minlength=k).astype(np.uint32), sizes)
+    # sum_c size_c * mean_c == sum of all points (per dimension)
+    rows = workloads.from_layout(data, n, d, lay)
+    total = rows.astype(np.float64).sum(axis=0)
+    got_total = (cur.reshape(d, k).T.astype(np.float64) * sizes[:, None]).sum(axis=0)
+    assert np.allclose(got_total, total, rtol=1e-5)
+    # sampled points: the oracle on a random subset (sub-sampled SoA columns)
+    rng = np.random.default_rng(0)
+    pick = np.sort(rng.choice(n, 8192, replace=False))
+    sub = workloads.to_layout(rows[pick], lay)
+    exact, bad = assignment_mismatches(oracle_mod, asg[pick], sub, prev, pick.size, k, d, lay, lay)
+    assert bad == 0, (exact, bad)
+    # idempotence of the update: recomputing the means from the returned assignment
+    want64, _ = oracle_mod.update_f64(data, asg, n, k, d, lay, lay)
+    ok, err = means_close(cur, want64)
+    assert ok, err
