@@ -221,7 +221,8 @@ def main():
     va = {"auto": 0, "exact": 1, "simt": 2, "tc": 3}[args.assign]
     vu = {"auto": 0, "shared": 1, "global": 2}[args.update]
     km = pkg.KMeans(layout=lay, layout_means=laym, device=local_rank, variant_assign=va, variant_update=vu)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     km.set_stream(stream.cuda_stream)
     km.initialize_device(dim, k, count, args.steps, dev_points.data_ptr(), dev_means.data_ptr())
     if world > 1:

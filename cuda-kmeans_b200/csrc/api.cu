@@ -122,6 +122,7 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 	w.tm.b_hi = reinterpret_cast<float*>(take(plane));
 	w.tm.b_lo = reinterpret_cast<float*>(take(plane));
 	w.tm.cnorm = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * sizeof(float)));
+	w.tm.b_aug = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * 8 * sizeof(float)));
 	w.flag_list = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
 	w.asg_scratch = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
 	if (with_tc_points) {
@@ -465,7 +466,7 @@ int bkm_set_stream(bkm_handle_t h, void* stream)
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
-	h->stream = stream ? static_cast<cudaStream_t>(stream) : h->own_stream;
+	h->stream = static_cast<cudaStream_t>(stream);   // NULL is the legacy default stream
 	return BKM_OK;
 }
 

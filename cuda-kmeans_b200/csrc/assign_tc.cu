@@ -3,9 +3,10 @@
 //   |x - c|^2 = |x|^2 + ( |c|^2 - 2 x.c )          argmin over c ignores |x|^2
 //
 // The x.c contraction runs as split-TF32 ("3xTF32"): every fp32 operand is split once into a
-// tf32 high part and a tf32 low part (x = xh + xl), and xh*ch + xh*cl + xl*ch is accumulated in
-// fp32 in tensor memory, which restores fp32-level accuracy of the products.  The argmin over
-// the centroids is taken in the epilogue straight out of tensor memory; the N x k distance
+// tf32 high part and a tf32 low part (x = xh + xl), and xl*ch + xh*cl + xh*ch is accumulated in
+// fp32 in tensor memory, which restores fp32-level accuracy of the products.  |c|^2 enters the
+// same accumulator through one more K step whose A operand is a constant tile of ones, so the
+// accumulator holds |c|^2 - 2 x.c and the epilogue is a pure arg-min.  The N x k distance
 // matrix never exists in HBM.  Because the GEMM form cancels, a point whose best and
 // second-best values are closer than the error band of this formulation is queued for the
 // exact CUDA-core kernel, so the final assignment equals the reference arithmetic
@@ -15,12 +16,18 @@
 // Kernel organisation (one persistent CTA per SM, 10 warps):
 //   warp 0     : TMA producer.  Point tiles (128 points x 32 dims, hi and lo plane) are loaded
 //                once per block of 4 tiles and stay in shared memory; centroid tiles (up to 128
-//                centroids x 32 dims, hi and lo) stream through a 2-stage ring.
-//   warp 1     : allocates the 512 TMEM columns, issues 12 tcgen05.mma (kind::tf32, M=128,
-//                N<=128, K=8) per (point tile, centroid tile) into one of 4 accumulators.
-//   warps 2..9 : epilogue.  Two warps per 32-lane TMEM quarter (each takes half of the columns)
-//                read the accumulator with tcgen05.ld, add |c|^2, and keep (best, second, index)
-//                per point in registers across all centroid tiles.
+//                centroids x 32 dims, hi and lo, plus their |c|^2 K step) stream through a
+//                2-stage ring.
+//   warp 1     : allocates the 512 TMEM columns and issues the tcgen05.mma instructions
+//                (kind::tf32, M=128, N<=128, K=8).  Back-to-back MMAs into ONE accumulator are
+//                bound by the accumulate latency, not by the tensor work, so the K steps of two
+//                accumulators are issued interleaved.
+//   warps 2..9 : epilogue.  Two warps per 32-lane TMEM quarter; the pair alternates over the
+//                point tiles, so that one computes while the other waits for tensor memory.
+//                Each reads its accumulator rows with tcgen05.ld, packs the column position
+//                into the low mantissa bits, and reduces 32 columns at a time to (best, second)
+//                with a min/max tournament; (best, second, chunk of best) per point stay in
+//                registers across all centroid tiles.
 // All mbarrier waits are bounded; a wait that runs out sets STATUS_WAIT_TIMEOUT and lets every
 // role fall through to the end, where TMEM is released.
 #include <cuda.h>
@@ -30,26 +37,30 @@
 #include "ptx.cuh"
 
 #include <cmath>
+#include <cstdlib>
 #include <new>
 
 namespace bkm {
 
-constexpr uint32_t TC_MA = 4;            // point tiles per block (= TMEM accumulators)
+constexpr uint32_t TC_MA = 2;            // point tiles per block (= TMEM accumulators)
 constexpr uint32_t TC_NB = 2;            // centroid-tile stages
-constexpr uint32_t TC_NT_MAX = 128;      // centroids per tile
+constexpr uint32_t TC_NT_MAX = 256;      // centroids per tile (the widest MMA: N = 256)
 constexpr uint32_t TC_EPI_WARPS = 8;
 constexpr uint32_t TC_THREADS = (2 + TC_EPI_WARPS) * 32;
-constexpr uint32_t TC_MAX_KPAD = 4096;   // |c|^2 of all centroids is kept in shared memory
+constexpr uint32_t TC_MAX_KPAD = 1u << 20;
 constexpr uint32_t TC_TMEM_COLS = 512;
 
-constexpr uint32_t PLANE_BYTES = TC_MTILE * TC_KCHUNK * 4;       // 16 KiB: 128 rows x 128 B
-constexpr uint32_t A_TILE_BYTES = 2 * PLANE_BYTES;               // hi + lo
-constexpr uint32_t B_STAGE_BYTES = 2 * PLANE_BYTES;
+constexpr uint32_t A_PLANE_BYTES = TC_MTILE * TC_KCHUNK * 4;     // 16 KiB: 128 rows x 128 B
+constexpr uint32_t B_PLANE_BYTES = TC_NT_MAX * TC_KCHUNK * 4;    // 32 KiB: 256 rows x 128 B
+constexpr uint32_t A_TILE_BYTES = 2 * A_PLANE_BYTES;             // hi + lo
+constexpr uint32_t B_STAGE_BYTES = 2 * B_PLANE_BYTES;
+constexpr uint32_t AUG_BYTES = TC_NT_MAX * 8 * 4;                // 8 KiB: 256 rows x one K step of 8
 constexpr uint32_t SM_A_OFF = 0;
-constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;   // 131072
-constexpr uint32_t SM_CN_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // 196608
-constexpr uint32_t SM_MERGE_OFF = SM_CN_OFF + TC_MAX_KPAD * 4;   // 212992
-constexpr uint32_t MERGE_BYTES = 3 * TC_MA * TC_MTILE * 4;       // second half's (best, second, idx)
+constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;
+constexpr uint32_t SM_BAUG_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // |c|^2 K step per stage
+constexpr uint32_t SM_AAUG_OFF = SM_BAUG_OFF + TC_NB * AUG_BYTES;  // constant ones tile (128 rows)
+constexpr uint32_t SM_MERGE_OFF = SM_AAUG_OFF + TC_MTILE * 8 * 4;
+constexpr uint32_t MERGE_BYTES = 3 * TC_MA * TC_MTILE * 4;       // second column half's (best, second, idx)
 constexpr uint32_t SM_BAR_OFF = SM_MERGE_OFF + MERGE_BYTES;
 constexpr uint32_t SM_TOTAL = SM_BAR_OFF + 256;
 constexpr uint32_t SM_ALLOC = SM_TOTAL + 1024;                   // slack for 1024-byte alignment
@@ -163,25 +174,67 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr)
 	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__device__ __forceinline__ void track(float v, uint32_t col, float& best, float& second, uint32_t& idx)
+// K-major operand without swizzle, one K step (8 tf32 = two 16-byte chunks) wide: 8x16-byte core
+// matrices; the two chunks of a row group are 128 B apart, row groups 256 B apart.
+__device__ __forceinline__ uint64_t make_desc_aug(uint32_t smem_addr)
 {
-	const bool lt = v < best;
-	second = fminf(second, fmaxf(best, v));
-	best = fminf(best, v);
-	idx = lt ? col : idx;
+	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (8ull << 16) | (16ull << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ float fmin3(float a, float b, float c)
+{
+	float r;
+	asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+	return r;
+}
+
+// Smallest and second-smallest of 32 values by a tournament: 16 (min,max) pairs, then 15 merges
+// (b,s) x (b',s') -> (min(b,b'), min(max(b,b'), s, s')).  77 instructions, log depth.
+__device__ __forceinline__ void top2_of_32(const float (&p)[32], float& b, float& s)
+{
+	float lo[16], hi[16];
+	#pragma unroll
+	for (int i = 0; i < 16; ++i) { lo[i] = fminf(p[2 * i], p[2 * i + 1]); hi[i] = fmaxf(p[2 * i], p[2 * i + 1]); }
+	#pragma unroll
+	for (int n = 16; n > 1; n >>= 1) {
+		#pragma unroll
+		for (int i = 0; i < n / 2; ++i) {
+			const float nb = fminf(lo[2 * i], lo[2 * i + 1]);
+			const float ns = fmin3(fmaxf(lo[2 * i], lo[2 * i + 1]), hi[2 * i], hi[2 * i + 1]);
+			lo[i] = nb;
+			hi[i] = ns;
+		}
+	}
+	b = lo[0];
+	s = hi[0];
+}
+
+// One 32-column chunk of an accumulator row: put the column's position in the chunk into the
+// 5 low mantissa bits (so that the minimum carries its own index), reduce to the two smallest,
+// and merge them into the running (best, second, chunk of best).
+__device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t chunk_id,
+	float& best, float& second, uint32_t& best_chunk)
+{
+	float p[32];
+	#pragma unroll
+	for (int t = 0; t < 32; ++t) p[t] = __uint_as_float((v[t] & 0xFFFFFFE0u) | (uint32_t)t);
+	float b, s2;
+	top2_of_32(p, b, s2);
+	second = fmin3(second, fmaxf(best, b), s2);
+	best_chunk = b < best ? chunk_id : best_chunk;
+	best = fminf(best, b);
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
-	const float* __restrict__ cnorm, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
-	uint64_t n, uint32_t n_tiles, uint32_t k_pad, uint32_t nt_cols, uint32_t idesc,
-	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef)
+	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
+	uint64_t n, uint32_t n_tiles, uint32_t k_pad, uint32_t nt_cols, uint32_t ksteps, uint32_t idesc,
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef, uint32_t dbg)
 {
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 	TcBars* bars = reinterpret_cast<TcBars*>(smem + SM_BAR_OFF);
-	float* cn_s = reinterpret_cast<float*>(smem + SM_CN_OFF);
 	float* mg_best = reinterpret_cast<float*>(smem + SM_MERGE_OFF);
 	float* mg_second = mg_best + TC_MA * TC_MTILE;
 	uint32_t* mg_idx = reinterpret_cast<uint32_t*>(mg_second + TC_MA * TC_MTILE);
@@ -209,7 +262,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		ptx::tmem_alloc(&bars->tmem_slot, TC_TMEM_COLS);
 		ptx::tmem_relinquish();
 	}
-	for (uint32_t i = threadIdx.x; i < k_pad; i += TC_THREADS) cn_s[i] = cnorm[i];
+	{
+		// the constant A operand of the |c|^2 K step: columns 0 and 1 are one (they meet the
+		// high and the low part of |c|^2), the rest zero
+		float* a_aug = reinterpret_cast<float*>(smem + SM_AAUG_OFF);
+		for (uint32_t e = threadIdx.x; e < TC_MTILE * 8; e += TC_THREADS) {
+			const uint32_t row = e >> 3, k = e & 7u;
+			a_aug[aug_offset(row, k)] = k < 2 ? 1.0f : 0.0f;
+		}
+		ptx::fence_proxy_async();
+	}
 	ptx::tc_fence_before();
 	__syncthreads();
 	ptx::tc_fence_after();
@@ -220,7 +282,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		if (lane == 0) {
 			ptx::prefetch_tmap(&tm_a_hi); ptx::prefetch_tmap(&tm_a_lo);
 			ptx::prefetch_tmap(&tm_b_hi); ptx::prefetch_tmap(&tm_b_lo);
-			uint32_t a_use[TC_MA] = {0, 0, 0, 0};
+			uint32_t a_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
 			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
@@ -232,7 +294,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE);
 					ptx::mbar_arrive_expect_tx(&bars->a_full[i], A_TILE_BYTES);
 					ptx::tma_load_2d(dst, &tm_a_hi, 0, row, &bars->a_full[i]);
-					ptx::tma_load_2d(dst + PLANE_BYTES, &tm_a_lo, 0, row, &bars->a_full[i]);
+					ptx::tma_load_2d(dst + A_PLANE_BYTES, &tm_a_lo, 0, row, &bars->a_full[i]);
 					++a_use[i];
 				}
 				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
@@ -240,9 +302,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
 					if (!ok) break;
 					uint8_t* dst = smem + SM_B_OFF + s * B_STAGE_BYTES;
-					ptx::mbar_arrive_expect_tx(&bars->b_full[s], 2 * nt_cols * TC_KCHUNK * 4);
+					const uint32_t aug_bytes = nt_cols * 8 * 4;
+					ptx::mbar_arrive_expect_tx(&bars->b_full[s], 2 * nt_cols * TC_KCHUNK * 4 + aug_bytes);
 					ptx::tma_load_2d(dst, &tm_b_hi, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
-					ptx::tma_load_2d(dst + PLANE_BYTES, &tm_b_lo, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
+					ptx::tma_load_2d(dst + B_PLANE_BYTES, &tm_b_lo, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
+					ptx::bulk_g2s(smem + SM_BAUG_OFF + s * AUG_BYTES, b_aug + (size_t)j * nt_cols * 8, aug_bytes, &bars->b_full[s]);
 					++b_count;
 				}
 			}
@@ -257,10 +321,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	} else if (warp == 1) {
 		// ---------------- MMA issuer ----------------
 		if (lane == 0) {
-			uint32_t a_use[TC_MA] = {0, 0, 0, 0};
-			uint32_t acc_use[TC_MA] = {0, 0, 0, 0};
+			uint32_t a_use[TC_MA] = {0, 0};
+			uint32_t acc_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
+			const uint64_t a_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_AAUG_OFF));
 			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
 				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
@@ -268,7 +333,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
 					if (!ok) break;
 					const uint32_t b_addr = ptx::smem_u32(smem + SM_B_OFF + s * B_STAGE_BYTES);
-					const uint64_t b_hi = make_desc(b_addr), b_lo = make_desc(b_addr + PLANE_BYTES);
+					const uint64_t b_hi = make_desc(b_addr), b_lo = make_desc(b_addr + B_PLANE_BYTES);
+					const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_BAUG_OFF + s * AUG_BYTES));
 					for (uint32_t i = 0; i < tiles; ++i) {
 						if (j == 0) {
 							ok = wait_or_abort(&bars->a_full[i], a_use[i] & 1u, abort_flag);
@@ -278,16 +344,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						if (!ok) break;
 						ptx::tc_fence_after();
 						const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + i * A_TILE_BYTES);
-						const uint64_t a_hi = make_desc(a_addr), a_lo = make_desc(a_addr + PLANE_BYTES);
+						const uint64_t a_hi = make_desc(a_addr), a_lo = make_desc(a_addr + A_PLANE_BYTES);
 						const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
-						// small cross terms first, the dominant hi*hi term last; +2 in the
-						// descriptor's address field = 32 bytes = one K step of 8 tf32 values
-						#pragma unroll
-						for (uint32_t ks = 0; ks < 4; ++ks) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
-						#pragma unroll
-						for (uint32_t ks = 0; ks < 4; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
-						#pragma unroll
-						for (uint32_t ks = 0; ks < 4; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
+						if (!(dbg & 1u)) {
+							// small cross terms first, then the dominant hi*hi term, then |c|^2;
+							// +2 in the descriptor's address field = 32 bytes = one K step
+							for (uint32_t ks = 0; ks < ksteps; ++ks) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
+							for (uint32_t ks = 0; ks < ksteps; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
+							for (uint32_t ks = 0; ks < ksteps; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
+							ptx::mma_tf32(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
+						}
 						ptx::mma_commit(&bars->acc_full[i]);
 						++acc_use[i];
 						if (j == n_ctiles - 1) {
@@ -306,50 +372,48 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		const uint32_t q = warp & 3u;              // TMEM lane quarter this warp may read
 		const uint32_t h = (warp - 2) >> 2;        // which half of the tile's columns
 		const uint32_t row = q * 32 + lane;
-		const uint32_t colbase = h * 64;
 		const float cmax2 = ctl->cmax2[slot];
-		uint32_t acc_use[TC_MA] = {0, 0, 0, 0};
+		const uint32_t half_cols = ((nt_cols >> 5) + 1) / 2 * 32;      // columns of the first half (whole chunks)
+		const uint32_t colbase = h * half_cols;
+		const uint32_t nchunks = h == 0 ? (half_cols >> 5) : ((nt_cols - half_cols) >> 5);   // 0..4
+		uint32_t acc_use[TC_MA] = {0, 0};
 		bool ok = true;
 		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 			float best[TC_MA], second[TC_MA];
-			uint32_t idx[TC_MA];
+			uint32_t bchunk[TC_MA];
 			#pragma unroll
-			for (uint32_t i = 0; i < TC_MA; ++i) { best[i] = INFINITY; second[i] = INFINITY; idx[i] = 0; }
+			for (uint32_t i = 0; i < TC_MA; ++i) { best[i] = INFINITY; second[i] = INFINITY; bchunk[i] = 0; }
 			for (uint32_t j = 0; j < n_ctiles; ++j) {
 				#pragma unroll
 				for (uint32_t i = 0; i < TC_MA; ++i) {
 					if (i < tiles) {
-						if (ok) ok = __all_sync(0xffffffffu, wait_or_abort(&bars->acc_full[i], acc_use[i] & 1u, abort_flag));
+						if (ok) {
+							// one lane polls the barrier, the warp follows
+							bool w = true;
+							if (lane == 0) w = wait_or_abort(&bars->acc_full[i], acc_use[i] & 1u, abort_flag);
+							ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
+						}
 						++acc_use[i];
-						if (ok && colbase < nt_cols) {
+						if (ok && nchunks > 0 && !(dbg & 4u)) {
 							ptx::tc_fence_after();
 							const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
-							const uint32_t gcol = j * nt_cols + colbase;
-							const bool two = colbase + 32 < nt_cols;
+							const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
 							uint32_t v0[32], v1[32];
+							// chunks 0 and 1 in flight together, then 2 and 3 while 1 is reduced
 							ptx::tmem_ld32(taddr, v0);
-							if (two) ptx::tmem_ld32(taddr + 32, v1);
+							if (nchunks > 1) ptx::tmem_ld32(taddr + 32, v1);
 							ptx::tmem_ld_wait();
-							const float4* c4 = reinterpret_cast<const float4*>(cn_s + gcol);
-							#pragma unroll
-							for (uint32_t t = 0; t < 8; ++t) {
-								const float4 c = c4[t];
-								track(__uint_as_float(v0[4 * t + 0]) + c.x, gcol + 4 * t + 0, best[i], second[i], idx[i]);
-								track(__uint_as_float(v0[4 * t + 1]) + c.y, gcol + 4 * t + 1, best[i], second[i], idx[i]);
-								track(__uint_as_float(v0[4 * t + 2]) + c.z, gcol + 4 * t + 2, best[i], second[i], idx[i]);
-								track(__uint_as_float(v0[4 * t + 3]) + c.w, gcol + 4 * t + 3, best[i], second[i], idx[i]);
+							if (!(dbg & 2u)) chunk_update(v0, chunk0, best[i], second[i], bchunk[i]);
+							if (nchunks > 2) ptx::tmem_ld32(taddr + 64, v0);
+							if (nchunks > 1 && !(dbg & 2u)) chunk_update(v1, chunk0 + 1, best[i], second[i], bchunk[i]);
+							if (nchunks > 3) ptx::tmem_ld32(taddr + 96, v1);
+							if (nchunks > 2) {
+								ptx::tmem_ld_wait();
+								if (!(dbg & 2u)) chunk_update(v0, chunk0 + 2, best[i], second[i], bchunk[i]);
+								if (nchunks > 3 && !(dbg & 2u)) chunk_update(v1, chunk0 + 3, best[i], second[i], bchunk[i]);
 							}
-							if (two) {
-								#pragma unroll
-								for (uint32_t t = 0; t < 8; ++t) {
-									const float4 c = c4[8 + t];
-									track(__uint_as_float(v1[4 * t + 0]) + c.x, gcol + 32 + 4 * t + 0, best[i], second[i], idx[i]);
-									track(__uint_as_float(v1[4 * t + 1]) + c.y, gcol + 32 + 4 * t + 1, best[i], second[i], idx[i]);
-									track(__uint_as_float(v1[4 * t + 2]) + c.z, gcol + 32 + 4 * t + 2, best[i], second[i], idx[i]);
-									track(__uint_as_float(v1[4 * t + 3]) + c.w, gcol + 32 + 4 * t + 3, best[i], second[i], idx[i]);
-								}
-							}
+							if (dbg & 2u) best[i] = fminf(best[i], __uint_as_float(v0[0] ^ v0[31] ^ v1[7]));
 							ptx::tc_fence_before();
 						}
 						__syncwarp();
@@ -363,28 +427,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				for (uint32_t i = 0; i < TC_MA; ++i) {
 					mg_best[i * TC_MTILE + row] = best[i];
 					mg_second[i * TC_MTILE + row] = second[i];
-					mg_idx[i * TC_MTILE + row] = idx[i];
+					mg_idx[i * TC_MTILE + row] = bchunk[i] * 32u + (__float_as_uint(best[i]) & 31u);
 				}
 			}
 			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
 			if (h == 0) {
 				#pragma unroll
 				for (uint32_t i = 0; i < TC_MA; ++i) {
-					if (i < tiles) {
+					const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
+					if (i < tiles && p < n && ok && !dbg) {
 						const float ob = mg_best[i * TC_MTILE + row], os = mg_second[i * TC_MTILE + row];
 						const uint32_t oi = mg_idx[i * TC_MTILE + row];
+						const uint32_t mi = bchunk[i] * 32u + (__float_as_uint(best[i]) & 31u);
 						const float b = fminf(best[i], ob);
-						const float s2 = fminf(fminf(second[i], os), fmaxf(best[i], ob));
-						const uint32_t bi = (ob < best[i] || (ob == best[i] && oi < idx[i])) ? oi : idx[i];
-						const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
-						if (p < n && ok) {
-							asg[p] = bi;
-							const float margin = margin_coef * (xnorm[p] + cmax2);
-							if (s2 - b <= margin) {
-								const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-								if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
-								else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
-							}
+						const float s2 = fmin3(second[i], os, fmaxf(best[i], ob));
+						asg[p] = (ob < best[i] || (ob == best[i] && oi < mi)) ? oi : mi;
+						const float margin = margin_coef * (xnorm[p] + cmax2);
+						if (s2 - b <= margin) {
+							const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
+							if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
+							else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
 						}
 					}
 				}
@@ -487,10 +549,15 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
 	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
-	const float margin_coef = margin_scale * (40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
+	// (the 5 index bits packed into the mantissa perturb a value by < 2^-18 of its magnitude)
+	const float margin_coef = margin_scale * ((40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f + 2.0f * 3.8146973e-06f);
+	static const uint32_t dbg = getenv("BKM_TC_DEBUG") ? (uint32_t)atoi(getenv("BKM_TC_DEBUG")) : 0u;
+	uint32_t idesc = p->idesc;
+	if (dbg & 8u) idesc = (idesc & ~(0x3Fu << 17)) | ((64u >> 3) << 17);    // N = 64: half the tensor work per instruction
+	if (dbg & 16u) idesc = (idesc & ~(0x3Fu << 17)) | ((32u >> 3) << 17);   // N = 32
 	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
-		p->tm.cnorm, p->tp.xnorm, asg, p->s.n, n_tiles, p->tm.k_pad, p->nt_cols, p->idesc,
-		ctl, slot, flag_list, margin_coef);
+		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->tm.k_pad, p->nt_cols, (p->s.dim + 7) / 8, idesc,
+		ctl, slot, flag_list, margin_coef, dbg);
 	return cudaGetLastError();
 }
 

@@ -54,4 +54,12 @@ constexpr uint32_t TC_KCHUNK = 32;
 constexpr uint32_t TC_MTILE = 128;
 __host__ __device__ __forceinline__ uint32_t tc_dpad(uint32_t dim) { return round_up(dim, TC_KCHUNK); }
 
+// The |c|^2 operand of the tensor-core assignment is one K step (8 tf32) wide and stored
+// K-major without swizzle: 8-row x 16-byte core matrices, the two 16-byte chunks of a row group
+// 128 B apart, row groups 256 B apart.  Float offset of element (row, k):
+__host__ __device__ __forceinline__ uint32_t aug_offset(uint32_t row, uint32_t k)
+{
+	return (row >> 3) * 64 + (k >> 2) * 32 + (row & 7) * 4 + (k & 3);
+}
+
 } // namespace bkm

@@ -18,6 +18,8 @@ struct TcMeans {
 	float* b_hi;     // [k_pad][d_pad] tf32 high part of -2*mean, K-major
 	float* b_lo;     // [k_pad][d_pad] tf32 low part
 	float* cnorm;    // [k_pad] |mean|^2, +inf for padding rows
+	float* b_aug;    // [k_pad x 8] tf32 (hi, lo) of |mean|^2 in columns 0,1 of one K step (aug_offset layout);
+	                 // padding rows hold a huge finite value so that they never win
 	uint32_t k_pad;  // k rounded up to the centroid tile
 	uint32_t d_pad;  // dim rounded up to TC_KCHUNK
 };

@@ -41,8 +41,8 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 	const float* __restrict__ means_in, float* __restrict__ means_out, uint32_t* __restrict__ sizes_out,
 	uint32_t k, uint32_t d, int soa_means,
 	float* __restrict__ cprep, uint32_t rs, uint32_t srows,
-	float* __restrict__ b_hi, float* __restrict__ b_lo, float* __restrict__ cnorm, uint32_t k_pad, uint32_t d_pad,
-	Control* __restrict__ ctl, int slot)
+	float* __restrict__ b_hi, float* __restrict__ b_lo, float* __restrict__ cnorm, float* __restrict__ b_aug,
+	uint32_t k_pad, uint32_t d_pad, Control* __restrict__ ctl, int slot)
 {
 	const uint32_t lane = threadIdx.x & 31u;
 	const uint32_t wpb = blockDim.x >> 5;
@@ -83,6 +83,13 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 			if (lane == 0) {
 				if (cprep) cprep[(size_t)c * rs] = s2;
 				if (cnorm) cnorm[c] = s2;
+				if (b_aug) {
+					const float hi = tf32_rna(s2);
+					const float lo = tf32_rna(s2 - hi);
+					float4* dst = reinterpret_cast<float4*>(b_aug + aug_offset(c, 0));
+					dst[0] = make_float4(hi, lo, 0.0f, 0.0f);
+					dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);    // columns 4..7 sit 32 floats further
+				}
 				atomicMax(reinterpret_cast<int*>(&ctl->cmax2[slot]), __float_as_int(s2));
 				if (FINALIZE) { sizes_out[c] = cnt; counts[c] = 0; }
 			}
@@ -90,6 +97,11 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 			// padding rows can never win: their |c|^2 is +inf (the -2c part stays zero)
 			if (cprep && c < srows) cprep[(size_t)c * rs] = INFINITY;
 			if (cnorm && c < k_pad) cnorm[c] = INFINITY;
+			if (b_aug && c < k_pad) {
+				float4* dst = reinterpret_cast<float4*>(b_aug + aug_offset(c, 0));
+				dst[0] = make_float4(tf32_rna(1.0e30f), 0.0f, 0.0f, 0.0f);
+				dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+			}
 		}
 	}
 	if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -113,13 +125,14 @@ static void launch_fp(bool finalize, float* acc, uint32_t* counts, const float* 
 	float* bh = tc ? tc->b_hi : nullptr;
 	float* bl = tc ? tc->b_lo : nullptr;
 	float* cn = tc ? tc->cnorm : nullptr;
+	float* ba = tc ? tc->b_aug : nullptr;
 	uint32_t kp = tc ? tc->k_pad : 0, dp = tc ? tc->d_pad : 0;
 	if (finalize)
 		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, means_in, means_out, sizes_out,
-			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, kp, dp, ctl, slot);
+			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, kp, dp, ctl, slot);
 	else
 		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, means_in, means_out, sizes_out,
-			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, kp, dp, ctl, slot);
+			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, kp, dp, ctl, slot);
 }
 
 void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,

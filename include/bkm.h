@@ -132,7 +132,8 @@ int bkm_create(const bkm_config_t* config, bkm_handle_t* out);
 int bkm_destroy(bkm_handle_t h);
 
 /* Makes all work of the handle run on `stream` (a cudaStream_t of the handle's device)
- * instead of the stream the handle created for itself. */
+ * instead of the non-blocking stream the handle created for itself.  NULL selects the legacy
+ * default stream, the one the reference's drivers use (headers/cuda.hpp:70-88). */
 int bkm_set_stream(bkm_handle_t h, void* stream);
 
 /* Tunables: "margin_scale" (float multiplier on the near-tie band, default 1),
