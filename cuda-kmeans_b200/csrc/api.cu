@@ -84,8 +84,10 @@ Nccl* nccl()
 
 struct Workspace {
 	bkm::Control* ctl = nullptr;
-	float* acc = nullptr;          // k*dim sums
-	uint32_t* counts = nullptr;    // k sizes (directly behind acc)
+	float* acc = nullptr;          // k*dim sums (replica 0; further replicas acc_replica_stride words apart)
+	uint32_t* counts = nullptr;    // k sizes (directly behind the sums of each replica)
+	uint32_t replicas = 1;
+	size_t acc_bytes = 0;
 	float* cprep = nullptr;        // CUDA-core rows
 	size_t cprep_bytes = 0;
 	bkm::TcMeans tm{};
@@ -110,7 +112,9 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 	};
 	w.ctl = reinterpret_cast<bkm::Control*>(take(sizeof(bkm::Control)));
 	const size_t kd = (size_t)k * dim;
-	char* accp = take(kd * sizeof(float) + (size_t)k * sizeof(uint32_t));
+	w.replicas = bkm::acc_replicas(k, dim);
+	w.acc_bytes = (size_t)w.replicas * bkm::acc_replica_stride(k, dim) * sizeof(float);
+	char* accp = take(w.acc_bytes);
 	w.acc = reinterpret_cast<float*>(accp);
 	w.counts = accp ? reinterpret_cast<uint32_t*>(accp + kd * sizeof(float)) : nullptr;
 	w.cprep_bytes = (size_t)bkm::simt_rows(k) * bkm::simt_row_stride(dim) * sizeof(float);
@@ -172,7 +176,12 @@ int resolve_update(int variant, const bkm::Shape& s, int device, int* out)
 {
 	switch (variant) {
 	case BKM_UPDATE_AUTO:
-		*out = bkm::update_shared_fits(s, device) ? BKM_UPDATE_SHARED : BKM_UPDATE_GLOBAL;
+		// rows of at least 16 floats and enough of them that the L2 reductions rarely collide
+		if (s.dim >= 16 && (uint64_t)s.k * s.dim >= 8192) *out = BKM_UPDATE_ROWS;
+		else *out = bkm::update_shared_fits(s, device) ? BKM_UPDATE_SHARED : BKM_UPDATE_GLOBAL;
+		return BKM_OK;
+	case BKM_UPDATE_ROWS:
+		*out = variant;
 		return BKM_OK;
 	case BKM_UPDATE_SHARED:
 		if (!bkm::update_shared_fits(s, device)) return fail(BKM_ERR_UNSUPPORTED, "k*dim = %llu floats do not fit shared memory",
@@ -330,9 +339,9 @@ static int stateless_update(const float* points, const uint32_t* assignment, flo
 	int rc = resolve_update(variant, s, device, &v);
 	if (rc) return rc;
 	if (clear_ctl) CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
-	CUDA_TRY(cudaMemsetAsync(w.acc, 0, (size_t)s.k * s.dim * sizeof(float) + (size_t)s.k * sizeof(uint32_t), st));
-	bkm::launch_update(points, assignment, w.acc, w.counts, s, v, w.ctl, sm_count, st);
-	bkm::launch_finalize(w.acc, w.counts, means, sizes, s, nullptr, nullptr, w.ctl, 1, st);
+	CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
+	bkm::launch_update(points, assignment, w.acc, w.counts, w.replicas, s, v, w.ctl, sm_count, st);
+	bkm::launch_finalize(w.acc, w.counts, w.replicas, means, sizes, s, nullptr, nullptr, w.ctl, 1, st);
 	CUDA_TRY(cudaGetLastError());
 	return BKM_OK;
 }
@@ -563,9 +572,10 @@ int bkm_run_async(bkm_handle_t h, uint32_t iters)
 			h->plan, h->margin_scale, h->sm_count, st, timed ? ev[1] : nullptr);
 		if (rc) return rc;
 		if (timed) CUDA_TRY(cudaEventRecord(ev[2], st));
-		bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, s, h->update_variant, h->ws.ctl, h->sm_count, st);
+		bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, h->ws.replicas, s, h->update_variant, h->ws.ctl, h->sm_count, st);
 		if (timed) CUDA_TRY(cudaEventRecord(ev[3], st));
 		if (h->comm) {
+			bkm::launch_merge_replicas(h->ws.acc, h->ws.counts, h->ws.replicas, s, st);
 			Nccl* nc = nccl();
 			NCCL_TRY(nc->GroupStart());
 			NCCL_TRY(nc->AllReduce(h->ws.acc, h->ws.acc, kd, NCCL_FLOAT32, NCCL_SUM, h->comm, st));
@@ -573,7 +583,7 @@ int bkm_run_async(bkm_handle_t h, uint32_t iters)
 			NCCL_TRY(nc->GroupEnd());
 		}
 		if (timed) CUDA_TRY(cudaEventRecord(ev[4], st));
-		bkm::launch_finalize(h->ws.acc, h->ws.counts, h->d_means[next], h->d_sizes, s,
+		bkm::launch_finalize(h->ws.acc, h->ws.counts, h->comm ? 1u : h->ws.replicas, h->d_means[next], h->d_sizes, s,
 			h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
 			h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st);
 		if (timed) { CUDA_TRY(cudaEventRecord(ev[5], st)); ++h->ev_count; }

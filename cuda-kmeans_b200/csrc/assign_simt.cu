@@ -64,9 +64,89 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
 	}
 }
 
+
+// The same arithmetic for a list of queued points: one block per point, the means spread over
+// all threads (four independent distance chains per thread), so that a short list still fills
+// the machine and a single point does not serialise k*dim dependent additions in one warp.
+constexpr int LIST_THREADS = 256;
+
+template<bool SOA, bool SOAM>
+__global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const float* __restrict__ pts,
+	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
+	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
+{
+	extern __shared__ float sx[];
+	__shared__ float sbest[LIST_THREADS / 32];
+	__shared__ uint32_t sidx[LIST_THREADS / 32];
+	const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+	uint64_t total = *list_count;
+	if (total > n) total = n;
+	for (uint64_t w = blockIdx.x; w < total; w += gridDim.x) {
+		const uint64_t i = list[w];
+		__syncthreads();
+		for (uint32_t j = tid; j < d; j += LIST_THREADS) sx[j] = pts[at<SOA>(i, j, n, d)];
+		__syncthreads();
+		float best = INFINITY;
+		uint32_t bidx = 0xffffffffu;
+		for (uint32_t m0 = tid; m0 < k; m0 += LIST_THREADS * 4) {
+			uint32_t m[4];
+			float sum[4];
+			#pragma unroll
+			for (int u = 0; u < 4; ++u) { m[u] = m0 + u * LIST_THREADS; sum[u] = 0.0f; if (m[u] >= k) m[u] = k - 1; }
+			for (uint32_t j = 0; j < d; ++j) {
+				const float xj = sx[j];
+				#pragma unroll
+				for (int u = 0; u < 4; ++u) {
+					const float diff = __fsub_rn(xj, means[at<SOAM>(m[u], j, k, d)]);
+					sum[u] = __fadd_rn(sum[u], __fmul_rn(diff, diff));
+				}
+			}
+			#pragma unroll
+			for (int u = 0; u < 4; ++u) {
+				if (m0 + u * LIST_THREADS < k) {
+					const float dist = __fsqrt_rn(sum[u]);
+					if (bidx == 0xffffffffu || dist < best) { best = dist; bidx = m[u]; }
+				}
+			}
+		}
+		#pragma unroll
+		for (int off = 16; off > 0; off >>= 1) {
+			const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+			const uint32_t oi = __shfl_xor_sync(0xffffffffu, bidx, off);
+			if (oi != 0xffffffffu && (bidx == 0xffffffffu || ob < best || (ob == best && oi < bidx))) { best = ob; bidx = oi; }
+		}
+		if (lane == 0) { sbest[warp] = best; sidx[warp] = bidx; }
+		__syncthreads();
+		if (tid == 0) {
+			for (uint32_t v = 1; v < LIST_THREADS / 32; ++v) {
+				const float ob = sbest[v];
+				const uint32_t oi = sidx[v];
+				if (oi != 0xffffffffu && (bidx == 0xffffffffu || ob < best || (ob == best && oi < bidx))) { best = ob; bidx = oi; }
+			}
+			asg[i] = bidx;
+		}
+	}
+}
+
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
 	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
 {
+	if (list != nullptr && (size_t)s.dim * sizeof(float) <= 160 * 1024) {
+		const size_t lsmem = (size_t)s.dim * sizeof(float);
+		const uint32_t lgrid = (uint32_t)sm_count * 8;
+#define BKM_LAUNCH_LIST(SOA, SOAM) do { \
+		auto kern = assign_exact_list_kernel<SOA, SOAM>; \
+		if (lsmem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lsmem); if (e != cudaSuccess) return e; } \
+		kern<<<lgrid, LIST_THREADS, lsmem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count); \
+	} while (0)
+		if (s.soa && s.soa_means) BKM_LAUNCH_LIST(true, true);
+		else if (s.soa && !s.soa_means) BKM_LAUNCH_LIST(true, false);
+		else if (!s.soa && s.soa_means) BKM_LAUNCH_LIST(false, true);
+		else BKM_LAUNCH_LIST(false, false);
+#undef BKM_LAUNCH_LIST
+		return cudaGetLastError();
+	}
+
 	// shared memory: one copy of the point per warp
 	uint32_t warps = 8;
 	while (warps > 1 && (size_t)warps * s.dim * sizeof(float) > 96 * 1024) warps >>= 1;

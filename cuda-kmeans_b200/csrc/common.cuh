@@ -54,6 +54,20 @@ constexpr uint32_t TC_KCHUNK = 32;
 constexpr uint32_t TC_MTILE = 128;
 __host__ __device__ __forceinline__ uint32_t tc_dpad(uint32_t dim) { return round_up(dim, TC_KCHUNK); }
 
+// The per-iteration accumulators (k*dim float sums directly followed by k integer sizes) exist in
+// `acc_replicas` copies so that concurrent global reductions spread over more cache lines; a
+// copy starts every acc_replica_stride 32-bit words.
+__host__ __device__ __forceinline__ size_t acc_replica_stride(uint32_t k, uint32_t dim)
+{
+	return ((size_t)k * dim + k + 63) / 64 * 64;
+}
+__host__ __device__ __forceinline__ uint32_t acc_replicas(uint32_t k, uint32_t dim)
+{
+	const size_t lines = ((size_t)k * dim + 31) / 32;
+	size_t r = (16384 + lines - 1) / lines;
+	return (uint32_t)(r < 1 ? 1 : (r > 16 ? 16 : r));
+}
+
 // The |c|^2 operand of the tensor-core assignment is one K step (8 tf32) wide and stored
 // K-major without swizzle: 8-row x 16-byte core matrices, the two 16-byte chunks of a row group
 // 128 B apart, row groups 256 B apart.  Float offset of element (row, k):

@@ -43,15 +43,17 @@ void launch_prepare_means(const float* means, const Shape& s, float* cprep, cons
 
 // acc/counts -> means_out (given layout), sizes_out, then the same preparation as above from
 // the fresh means; clears acc, counts and flag_count for the next iteration.
-void launch_finalize(float* acc, uint32_t* counts, float* means_out, uint32_t* sizes_out, const Shape& s,
+void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* means_out, uint32_t* sizes_out, const Shape& s,
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
 
 // ---- update (update.cu) ----
 // variant: BKM_UPDATE_SHARED or BKM_UPDATE_GLOBAL (already resolved).  acc/counts must be zero.
 // Returns false when the shared variant cannot hold k*dim in shared memory.
 bool update_shared_fits(const Shape& s, int device);
-void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, const Shape& s,
+void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, uint32_t replicas, const Shape& s,
 	int variant, Control* ctl, int sm_count, cudaStream_t stream);
+// Folds accumulator replicas 1.. into replica 0 (before an all-reduce of replica 0).
+void launch_merge_replicas(float* acc, uint32_t* counts, uint32_t replicas, const Shape& s, cudaStream_t stream);
 
 // ---- assignment on CUDA cores (assign_simt.cu) ----
 // Exact reference arithmetic.  With list != null only the points list[0..*list_count) are done.

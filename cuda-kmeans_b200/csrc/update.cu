@@ -36,8 +36,10 @@ __device__ __forceinline__ float tf32_rna(float x)
 // finalize / prepare
 // ------------------------------------------------------------------------------------------
 
+// `replicas` copies of (sums, sizes) lie `rep_stride` 32-bit words apart; all are added up and cleared.
 template<bool FINALIZE>
 __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict__ acc, uint32_t* __restrict__ counts,
+	uint32_t replicas, size_t rep_stride,
 	const float* __restrict__ means_in, float* __restrict__ means_out, uint32_t* __restrict__ sizes_out,
 	uint32_t k, uint32_t d, int soa_means,
 	float* __restrict__ cprep, uint32_t rs, uint32_t srows,
@@ -53,15 +55,27 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 	for (uint32_t c = blockIdx.x * wpb + (threadIdx.x >> 5); c < rows_total; c += gridDim.x * wpb) {
 		if (c < k) {
 			uint32_t cnt = 0;
-			if (FINALIZE) cnt = counts[c];
+			if (FINALIZE) {
+				for (uint32_t r = 0; r < replicas; ++r) cnt += counts[c + r * rep_stride];
+			}
 			const float divisor = (float)cnt;
 			float s2 = 0.0f;
 			for (uint32_t j = lane; j < d; j += 32) {
 				float mean;
 				const size_t mi = at_rt(soa_means, c, j, k, d);
 				if (FINALIZE) {
-					const float sum = acc[(size_t)c * d + j];
-					acc[(size_t)c * d + j] = 0.0f;
+					float sum = 0.0f;
+					float* src = acc + (size_t)c * d + j;
+					uint32_t r = 0;
+					for (; r + 4 <= replicas; r += 4) {
+						// four independent loads in flight
+						const float s0 = src[(r + 0) * rep_stride], s1 = src[(r + 1) * rep_stride];
+						const float s2b = src[(r + 2) * rep_stride], s3 = src[(r + 3) * rep_stride];
+						src[(r + 0) * rep_stride] = 0.0f; src[(r + 1) * rep_stride] = 0.0f;
+						src[(r + 2) * rep_stride] = 0.0f; src[(r + 3) * rep_stride] = 0.0f;
+						sum += (s0 + s1) + (s2b + s3);
+					}
+					for (; r < replicas; ++r) { sum += src[r * rep_stride]; src[r * rep_stride] = 0.0f; }
 					mean = cnt ? __fdiv_rn(sum, divisor) : 0.0f;
 					means_out[mi] = mean;
 				} else {
@@ -91,7 +105,10 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 					dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);    // columns 4..7 sit 32 floats further
 				}
 				atomicMax(reinterpret_cast<int*>(&ctl->cmax2[slot]), __float_as_int(s2));
-				if (FINALIZE) { sizes_out[c] = cnt; counts[c] = 0; }
+				if (FINALIZE) {
+					sizes_out[c] = cnt;
+					for (uint32_t r = 0; r < replicas; ++r) counts[c + r * rep_stride] = 0;
+				}
 			}
 		} else if (lane == 0) {
 			// padding rows can never win: their |c|^2 is +inf (the -2c part stays zero)
@@ -111,9 +128,10 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 	}
 }
 
-static void launch_fp(bool finalize, float* acc, uint32_t* counts, const float* means_in, float* means_out,
+static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t replicas, const float* means_in, float* means_out,
 	uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
+	const size_t rep_stride = acc_replica_stride(s.k, s.dim);
 	const uint32_t rs = simt_row_stride(s.dim);
 	const uint32_t srows = simt_rows(s.k);
 	uint32_t rows_total = s.k;
@@ -128,23 +146,49 @@ static void launch_fp(bool finalize, float* acc, uint32_t* counts, const float* 
 	float* ba = tc ? tc->b_aug : nullptr;
 	uint32_t kp = tc ? tc->k_pad : 0, dp = tc ? tc->d_pad : 0;
 	if (finalize)
-		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, means_in, means_out, sizes_out,
+		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, means_out, sizes_out,
 			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, kp, dp, ctl, slot);
 	else
-		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, means_in, means_out, sizes_out,
+		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, means_out, sizes_out,
 			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, kp, dp, ctl, slot);
 }
 
 void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,
 	Control* ctl, int slot, cudaStream_t stream)
 {
-	launch_fp(false, nullptr, nullptr, means, nullptr, nullptr, s, cprep, tc, ctl, slot, stream);
+	launch_fp(false, nullptr, nullptr, 1, means, nullptr, nullptr, s, cprep, tc, ctl, slot, stream);
 }
 
-void launch_finalize(float* acc, uint32_t* counts, float* means_out, uint32_t* sizes_out, const Shape& s,
+void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* means_out, uint32_t* sizes_out, const Shape& s,
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
-	launch_fp(true, acc, counts, nullptr, means_out, sizes_out, s, cprep, tc, ctl, slot, stream);
+	launch_fp(true, acc, counts, replicas, nullptr, means_out, sizes_out, s, cprep, tc, ctl, slot, stream);
+}
+
+// Adds replicas 1.. into replica 0 and clears them (needed before the sums leave the GPU).
+__global__ void __launch_bounds__(256) merge_replicas_kernel(float* __restrict__ acc, uint32_t* __restrict__ counts,
+	uint32_t replicas, size_t rep_stride, size_t kd, uint32_t k)
+{
+	for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < kd + k; e += (size_t)gridDim.x * blockDim.x) {
+		if (e < kd) {
+			float sum = acc[e];
+			for (uint32_t r = 1; r < replicas; ++r) { sum += acc[r * rep_stride + e]; acc[r * rep_stride + e] = 0.0f; }
+			acc[e] = sum;
+		} else {
+			const size_t c = e - kd;
+			uint32_t sum = counts[c];
+			for (uint32_t r = 1; r < replicas; ++r) { sum += counts[r * rep_stride + c]; counts[r * rep_stride + c] = 0; }
+			counts[c] = sum;
+		}
+	}
+}
+
+void launch_merge_replicas(float* acc, uint32_t* counts, uint32_t replicas, const Shape& s, cudaStream_t stream)
+{
+	if (replicas <= 1) return;
+	const size_t kd = (size_t)s.k * s.dim;
+	const uint32_t grid = (uint32_t)std::min<size_t>((kd + s.k + 255) / 256, 148 * 8);
+	merge_replicas_kernel<<<grid, 256, 0, stream>>>(acc, counts, replicas, acc_replica_stride(s.k, s.dim), kd, s.k);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -251,6 +295,94 @@ __global__ void __launch_bounds__(UPD_THREADS) update_kernel(const float* __rest
 	}
 }
 
+
+// Row-wise variant: one warp adds one point's 32-dimension slice to its cluster's row with a
+// single coalesced reduction (32 lanes = 32 consecutive floats = one 128-byte line, which the L2
+// atomic unit takes in one operation).  For SoA points a 32x32 tile is transposed through
+// shared memory first so that the loads stay coalesced too.  Best when k*dim is large enough
+// that the rows rarely collide; the per-cluster sizes go to global integer atomics.
+constexpr int ROWS_THREADS = 256;
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d)
+{
+	asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// VEC: dim is a multiple of 4 and the buffers are 16-byte aligned, so that 8 lanes cover a
+// 32-dimension slice with one 128-bit vector reduction each and a warp handles 4 points per
+// instruction.
+template<bool SOA, bool VEC>
+__global__ void __launch_bounds__(ROWS_THREADS) update_rows_kernel(const float* __restrict__ pts,
+	const uint32_t* __restrict__ asg, float* __restrict__ acc, uint32_t* __restrict__ counts,
+	uint64_t n, uint32_t k, uint32_t d, uint32_t replicas, size_t rep_stride, Control* __restrict__ ctl)
+{
+	// blocks spread over `replicas` copies of the accumulators so that fewer reductions meet on a line
+	acc += (blockIdx.x % replicas) * rep_stride;
+	counts += (blockIdx.x % replicas) * rep_stride;
+	// every warp works on its own group of 32 points, with a private transpose tile
+	__shared__ float tiles[ROWS_THREADS / 32][32][33];
+	const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+	constexpr uint32_t WARPS = ROWS_THREADS / 32;
+	float (*tile)[33] = tiles[warp];
+	const uint64_t groups = (n + 31) / 32;
+	bool bad = false;
+	for (uint64_t grp = (uint64_t)blockIdx.x * WARPS + warp; grp < groups; grp += (uint64_t)gridDim.x * WARPS) {
+		const uint64_t p0 = grp * 32;
+		const uint64_t pmine = p0 + lane;
+		uint32_t amine = pmine < n ? asg[pmine] : 0xffffffffu;      // lane i holds the cluster of point p0+i
+		if (pmine < n && amine >= k) { bad = true; amine = 0xffffffffu; }
+		if (amine != 0xffffffffu) atomicAdd(&counts[amine], 1u);
+		for (uint32_t c0 = 0; c0 < d; c0 += 32) {
+			if (SOA) {
+				// 32 independent coalesced loads per lane (dimension-major), then transpose
+				float v[32];
+				#pragma unroll
+				for (uint32_t dl = 0; dl < 32; ++dl)
+					v[dl] = (c0 + dl < d && pmine < n) ? pts[(size_t)(c0 + dl) * n + pmine] : 0.0f;
+				__syncwarp();
+				#pragma unroll
+				for (uint32_t dl = 0; dl < 32; ++dl) tile[dl][lane] = v[dl];
+				__syncwarp();
+				if (VEC) {
+					const uint32_t sub = lane >> 3, q4 = (lane & 7u) * 4;     // point within a group of 4, first of 4 dims
+					#pragma unroll
+					for (uint32_t it = 0; it < 8; ++it) {
+						const uint32_t pl = it * 4 + sub;
+						const uint32_t a = __shfl_sync(0xffffffffu, amine, pl);
+						if (a != 0xffffffffu && c0 + q4 < d)
+							red_add_v4(&acc[(size_t)a * d + c0 + q4], tile[q4 + 0][pl], tile[q4 + 1][pl], tile[q4 + 2][pl], tile[q4 + 3][pl]);
+					}
+				} else {
+					#pragma unroll 8
+					for (uint32_t pl = 0; pl < 32; ++pl) {
+						const uint32_t a = __shfl_sync(0xffffffffu, amine, pl);
+						if (a != 0xffffffffu && c0 + lane < d) atomicAdd(&acc[(size_t)a * d + c0 + lane], tile[lane][pl]);
+					}
+				}
+			} else if (VEC) {
+				const uint32_t sub = lane >> 3, q4 = (lane & 7u) * 4;
+				#pragma unroll
+				for (uint32_t it = 0; it < 8; ++it) {
+					const uint32_t pl = it * 4 + sub;
+					const uint32_t a = __shfl_sync(0xffffffffu, amine, pl);
+					if (a != 0xffffffffu && c0 + q4 < d) {
+						const float4 v = *reinterpret_cast<const float4*>(&pts[(size_t)(p0 + pl) * d + c0 + q4]);
+						red_add_v4(&acc[(size_t)a * d + c0 + q4], v.x, v.y, v.z, v.w);
+					}
+				}
+			} else {
+				#pragma unroll 8
+				for (uint32_t pl = 0; pl < 32; ++pl) {
+					const uint32_t a = __shfl_sync(0xffffffffu, amine, pl);
+					if (a != 0xffffffffu && c0 + lane < d)
+						atomicAdd(&acc[(size_t)a * d + c0 + lane], pts[(size_t)(p0 + pl) * d + c0 + lane]);
+				}
+			}
+		}
+	}
+	if (bad) atomicOr(&ctl->status, (uint32_t)STATUS_BAD_INDEX);
+}
+
 static size_t update_replica_bytes(const Shape& s)
 {
 	const uint32_t dstride = s.dim | 1u;
@@ -262,19 +394,31 @@ bool update_shared_fits(const Shape& s, int /*device*/)
 	return update_replica_bytes(s) <= SMEM_LIMIT - 1024 && (uint64_t)s.k * s.dim < (1ull << 31);
 }
 
-void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, const Shape& s,
+void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, uint32_t replicas, const Shape& s,
 	int variant, Control* ctl, int sm_count, cudaStream_t stream)
 {
+	if (variant == BKM_UPDATE_ROWS) {
+		const uint64_t groups = (s.n + 31) / 32;
+		const uint64_t blocks = (groups + ROWS_THREADS / 32 - 1) / (ROWS_THREADS / 32);
+		const uint32_t grid = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(blocks, 1), (uint64_t)sm_count * 6);
+		const size_t rep_stride = acc_replica_stride(s.k, s.dim);
+		const bool vec = s.dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(pts) | reinterpret_cast<uintptr_t>(acc)) & 15u) == 0;
+		if (s.soa && vec) update_rows_kernel<true, true><<<grid, ROWS_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, replicas, rep_stride, ctl);
+		else if (s.soa) update_rows_kernel<true, false><<<grid, ROWS_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, replicas, rep_stride, ctl);
+		else if (vec) update_rows_kernel<false, true><<<grid, ROWS_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, replicas, rep_stride, ctl);
+		else update_rows_kernel<false, false><<<grid, ROWS_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, replicas, rep_stride, ctl);
+		return;
+	}
 	const uint32_t dstride = s.dim | 1u;
 	const bool shared = variant == BKM_UPDATE_SHARED;
-	uint32_t replicas = 1;
+	uint32_t smem_replicas = 1;
 	size_t smem = 0;
 	if (shared) {
 		const size_t per = update_replica_bytes(s);
 		// aim at two resident blocks per SM when one replica is small enough, and at most 4 replicas
 		const size_t budget = per <= 100 * 1024 ? 100 * 1024 : SMEM_LIMIT - 1024;
-		replicas = (uint32_t)std::min<size_t>(4, std::max<size_t>(1, budget / per));
-		smem = per * replicas;
+		smem_replicas = (uint32_t)std::min<size_t>(4, std::max<size_t>(1, budget / per));
+		smem = per * smem_replicas;
 	}
 	int per_sm = 1;
 #define BKM_LAUNCH_UPD(SOA, SH) do { \
@@ -285,7 +429,7 @@ void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* 
 		if (per_sm > 4) per_sm = 4; \
 		uint64_t want = (s.n + 1023) / 1024; \
 		uint32_t grid = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(want, 1), (uint64_t)sm_count * per_sm); \
-		kern<<<grid, UPD_THREADS, smem, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dstride, replicas, ctl); \
+		kern<<<grid, UPD_THREADS, smem, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dstride, smem_replicas, ctl); \
 	} while (0)
 	if (s.soa) { if (shared) BKM_LAUNCH_UPD(true, true); else BKM_LAUNCH_UPD(true, false); }
 	else       { if (shared) BKM_LAUNCH_UPD(false, true); else BKM_LAUNCH_UPD(false, false); }

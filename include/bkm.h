@@ -52,6 +52,7 @@ extern "C" {
 #define BKM_UPDATE_AUTO 0
 #define BKM_UPDATE_SHARED 1  /* shared-memory privatised buckets + one global merge */
 #define BKM_UPDATE_GLOBAL 2  /* global atomics only (any k*dim) */
+#define BKM_UPDATE_ROWS 3    /* one coalesced 128-byte global reduction per point and 32 dimensions */
 
 const char* bkm_last_error(void);
 

@@ -102,7 +102,7 @@ def test_variants_agree(pkg, torch_cuda, oracle_mod, workloads):
     data, means, spec = workloads.make("c1", n=1 << 14)
     outs = []
     for va in (pkg.ASSIGN_EXACT, pkg.ASSIGN_SIMT, pkg.ASSIGN_TC):
-        for vu in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL):
+        for vu in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL, pkg.UPDATE_ROWS):
             km = pkg.KMeans(layout=spec["layout"], variant_assign=va, variant_update=vu)
             km.initialize(spec["dim"], spec["k"], 1 << 14, 3, data, means)
             km.run()
