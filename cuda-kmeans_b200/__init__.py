@@ -125,8 +125,28 @@ def shard_range(n_total, world_size, rank):
     return b.value, c.value
 
 
+def _preload_nccl():
+    """Loads the NCCL that ships as a Python wheel (the one PyTorch links) before libbkm looks for
+    one, so that a process that imports torch later does not end up with the system copy bound
+    under the same soname.  No effect when that wheel is absent or NCCL is already loaded."""
+    import importlib.util
+    try:
+        spec = importlib.util.find_spec("nvidia")
+    except (ImportError, ValueError):
+        spec = None
+    for base in (list(spec.submodule_search_locations) if spec and spec.submodule_search_locations else []):
+        path = os.path.join(base, "nccl", "lib", "libnccl.so.2")
+        if os.path.exists(path):
+            try:
+                ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+            except OSError:
+                pass
+            return
+
+
 def comm_unique_id():
     """128 bytes identifying a new NCCL communicator (rank 0 creates, all ranks receive)."""
+    _preload_nccl()
     buf = ctypes.create_string_buffer(128)
     check(lib().bkm_comm_unique_id(buf, 128))
     return buf.raw
@@ -256,6 +276,7 @@ class KMeans:
             check(lib().bkm_set_stream(self._h, stream_ptr))
 
     def comm_init(self, unique_id, world_size, rank):
+        _preload_nccl()
         buf = ctypes.create_string_buffer(bytes(unique_id), 128)
         check(lib().bkm_comm_init(self._need(), buf, 128, world_size, rank))
 

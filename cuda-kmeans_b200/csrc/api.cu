@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -29,6 +30,22 @@ int fail(int code, const char* fmt, ...)
 	g_error = buf;
 	return code;
 }
+
+} // namespace
+
+// Same as fail() for the other translation units of the library.
+int bkm_internal_fail(int code, const char* fmt, ...)
+{
+	char buf[512];
+	va_list ap;
+	va_start(ap, fmt);
+	vsnprintf(buf, sizeof(buf), fmt, ap);
+	va_end(ap);
+	g_error = buf;
+	return code;
+}
+
+namespace {
 
 #define CUDA_TRY(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) \
 	return fail(BKM_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
@@ -57,10 +74,14 @@ Nccl* nccl()
 	static bool tried = false;
 	if (!tried) {
 		tried = true;
-		// RTLD_NOLOAD first: reuse the copy a host application (e.g. PyTorch) already loaded.
-		void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
-		if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-		if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+		// RTLD_NOLOAD first: reuse the copy a host application (e.g. PyTorch) already loaded, so
+		// that one process never holds two NCCL versions under the same soname.  Otherwise the
+		// file named by BKM_NCCL_LIBRARY, then the system default.
+		void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+		const char* named = getenv("BKM_NCCL_LIBRARY");
+		if (!lib && named && *named) lib = dlopen(named, RTLD_NOW | RTLD_LOCAL);
+		if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+		if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
 		if (lib) {
 			inst.lib = lib;
 			inst.GetUniqueId = reinterpret_cast<decltype(inst.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
