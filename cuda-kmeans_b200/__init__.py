@@ -32,7 +32,7 @@ SYMBOLS = [
     "bkm_run_async", "bkm_synchronize", "bkm_get_means", "bkm_get_assignment", "bkm_get_sizes",
     "bkm_device_means", "bkm_device_assignment", "bkm_set_means", "bkm_iterations_done",
     "bkm_phase_ms", "bkm_counters", "bkm_comm_unique_id", "bkm_comm_init", "bkm_shard_range",
-    "bkm_kmeans_host_f32",
+    "bkm_kmeans_host_f32", "bkm_update_noalloc_f32",
 ]
 
 
@@ -97,6 +97,7 @@ def lib():
     L.bkm_comm_init.argtypes = [vp, vp, sz, ci, ci]
     L.bkm_shard_range.argtypes = [u64, ci, ci, ctypes.POINTER(u64), ctypes.POINTER(u64)]
     L.bkm_kmeans_host_f32.argtypes = [vp, vp, vp, u64, u32, u32, u32, ci, ci, ci]
+    L.bkm_update_noalloc_f32.argtypes = [vp, vp, vp, vp, u64, u32, u32, ci, ci, vp]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("bkm_last_error", "bkm_workspace_bytes"):
@@ -164,6 +165,15 @@ def update(points, assignment, means, sizes, n, k, dim, layout, layout_means, wo
            variant=UPDATE_AUTO, stream=0):
     check(lib().bkm_update_f32(points, assignment, means, sizes, n, k, dim, layout, layout_means, variant,
                                workspace, workspace_size, stream))
+
+
+def update_noalloc(points, assignment, means, sizes, n, k, dim, layout, layout_means, stream=0):
+    """bkm_update_noalloc_f32: the update step on the library's built-in scratch (no workspace, no
+    allocation); k*dim + k is limited to NOALLOC_MAX_WORDS and calls on one device must not overlap."""
+    check(lib().bkm_update_noalloc_f32(points, assignment, means, sizes, n, k, dim, layout, layout_means, stream))
+
+
+NOALLOC_MAX_WORDS = 512 * 1024 - 128
 
 
 def iterate(points, means_in, means_out, sizes, assignment, n, k, dim, layout, layout_means,

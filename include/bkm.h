@@ -98,6 +98,33 @@ int bkm_iterate_f32(const float* points, const float* means_in, float* means_out
                     int layout_means, int variant_assign, int variant_update,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The update step without any scratch from the caller and without any allocation inside.
+ * (No counterpart in the reference: its update runners get their extra copies from the
+ * algorithm class that owns all buffers, headers/cuda.hpp:25-28, 161.)
+ *
+ * Who needs it: a runner plugged into the reference's harness is handed only the problem
+ * instance - data, assignment, means, clusterSizes - with no room for a workspace pointer, and
+ * it runs inside the timed iteration loop, where a cudaMalloc would stall the whole device;
+ * likewise an application that has already given all device memory to its own pool, or that
+ * has filled the GPU with point data, has nothing left for cudaMalloc to return.  For such
+ * callers the accumulators of this entry point live in a fixed array inside the library
+ * image: BKM_NOALLOC_SCRATCH_WORDS 32-bit words (2 MiB) on every GPU that loads the library,
+ * held until the process exits whether or not the call is ever used.
+ *
+ * Limit: k*dim + k <= BKM_NOALLOC_MAX_WORDS, otherwise BKM_ERR_UNSUPPORTED (use
+ * bkm_update_f32 with a workspace of your own).  Results are those of bkm_update_f32.
+ *
+ * The first call on each device looks up the device address of the array (a host-side
+ * set-up step, done with that device current); make that first call outside any stream
+ * capture.  All calls on a device share the one array and each call clears what it
+ * accumulates into, so two calls whose kernels overlap on the GPU (different streams, or
+ * different host threads on different streams) race on it: keep calls on one device ordered.
+ * Nothing else of the library touches the array. */
+#define BKM_NOALLOC_SCRATCH_WORDS (512u * 1024u)
+#define BKM_NOALLOC_MAX_WORDS (BKM_NOALLOC_SCRATCH_WORDS - 128u)
+int bkm_update_noalloc_f32(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
+                           uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means, void* stream);
+
 /* Waits for `stream` and returns BKM_ERR_DEVICE if a kernel of the calls issued on this
  * workspace since its last check recorded an error (a bounded wait that ran out, an assignment
  * value >= k fed to the update).  The counterpart of the reference's CUCH(cudaGetLastError())
