@@ -342,7 +342,7 @@ static int stateless_assign(const float* points, const float* means, uint32_t* a
 	} else if (v == BKM_ASSIGN_TC) {
 		CUDA_TRY(cudaMemsetAsync(w.tm.b_hi, 0, w.tm_bytes, st));
 		bkm::launch_prepare_means(means, s, nullptr, &w.tm, w.ctl, 0, st);
-		CUDA_TRY(bkm::launch_split_points(points, s, w.tp, st));
+		CUDA_TRY(bkm::launch_split_points(points, s, w.tp, w.ctl, st));
 		const char* err = nullptr;
 		plan = bkm::tc_plan_create(s, w.tp, w.tm, device, &err);
 		if (!plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
@@ -523,7 +523,7 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 	CUDA_TRY(cudaMemsetAsync(h->d_asg, 0, s.n * sizeof(uint32_t), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_sizes, 0, (size_t)s.k * sizeof(uint32_t), st));
 	if (h->assign_variant == BKM_ASSIGN_TC) {
-		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, st));
+		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.ctl, st));
 		if (h->plan) { bkm::tc_plan_destroy(h->plan); h->plan = nullptr; }
 		const char* err = nullptr;
 		h->plan = bkm::tc_plan_create(s, h->ws.tp, h->ws.tm, h->cfg.device, &err);

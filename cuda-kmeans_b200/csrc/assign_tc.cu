@@ -37,6 +37,7 @@
 #include "ptx.cuh"
 
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <new>
 
@@ -45,7 +46,7 @@ namespace bkm {
 constexpr uint32_t TC_MA = 2;            // point tiles per block (= TMEM accumulators)
 constexpr uint32_t TC_NB = 2;            // centroid-tile stages
 constexpr uint32_t TC_NT_MAX = 256;      // centroids per tile (the widest MMA: N = 256)
-constexpr uint32_t TC_EPI_WARPS = 8;
+constexpr uint32_t TC_EPI_WARPS = 16;          // four per TMEM lane quarter, each a quarter of the columns
 constexpr uint32_t TC_THREADS = (2 + TC_EPI_WARPS) * 32;
 constexpr uint32_t TC_MAX_KPAD = 1u << 20;
 constexpr uint32_t TC_TMEM_COLS = 512;
@@ -60,7 +61,7 @@ constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;
 constexpr uint32_t SM_BAUG_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // |c|^2 K step per stage
 constexpr uint32_t SM_AAUG_OFF = SM_BAUG_OFF + TC_NB * AUG_BYTES;  // constant ones tile (128 rows)
 constexpr uint32_t SM_MERGE_OFF = SM_AAUG_OFF + TC_MTILE * 8 * 4;
-constexpr uint32_t MERGE_BYTES = 3 * TC_MA * TC_MTILE * 4;       // second column half's (best, second, idx)
+constexpr uint32_t MERGE_BYTES = 3 * 3 * TC_MA * TC_MTILE * 4;   // (best, second, chunk) of column parts 1..3
 constexpr uint32_t SM_BAR_OFF = SM_MERGE_OFF + MERGE_BYTES;
 constexpr uint32_t SM_TOTAL = SM_BAR_OFF + 256;
 constexpr uint32_t SM_ALLOC = SM_TOTAL + 1024;                   // slack for 1024-byte alignment
@@ -88,8 +89,10 @@ __device__ __forceinline__ float to_tf32(float x)
 // points for SoA, along dims for AoS) and the write (along dims) are coalesced.
 template<bool SOA>
 __global__ void __launch_bounds__(256) split_points_kernel(const float* __restrict__ pts, float* __restrict__ a_hi,
-	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t n_pad, uint32_t d, uint32_t d_pad)
+	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t n_pad, uint32_t d, uint32_t d_pad,
+	Control* __restrict__ ctl)
 {
+	float local_max = 0.0f;
 	__shared__ float tile[32][33];
 	const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
 	for (uint64_t p0 = (uint64_t)blockIdx.x * 32; p0 < n_pad; p0 += (uint64_t)gridDim.x * 32) {
@@ -128,16 +131,19 @@ __global__ void __launch_bounds__(256) split_points_kernel(const float* __restri
 			#pragma unroll
 			for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
 			if (tx == 0) xnorm[p0 + ty + r * 8] = s;
+			local_max = fmaxf(local_max, s);
 		}
 	}
+	// non-negative floats order like their bit patterns
+	if (tx == 0) atomicMax(reinterpret_cast<int*>(&ctl->xmax2), __float_as_int(local_max));
 }
 
-cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, cudaStream_t stream)
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, Control* ctl, cudaStream_t stream)
 {
 	const uint64_t groups = tp.n_pad / 32;
 	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148 * 16);
-	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad);
-	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad);
+	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, ctl);
+	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, ctl);
 	return cudaGetLastError();
 }
 
@@ -156,13 +162,17 @@ struct TcBars {
 	uint32_t abort_flag;
 };
 static_assert(sizeof(TcBars) <= 256, "barrier block too large");
+static_assert(SM_ALLOC <= 227 * 1024, "shared memory budget exceeded");
 
 // Bounded wait that also gives up when another role already failed.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
 {
-	for (uint32_t i = 0; i < ptx::WAIT_LIMIT; ++i) {
+	if (ptx::mbar_try_wait(bar, parity)) return true;
+	const uint64_t t0 = ptx::globaltimer_ns();
+	while (true) {
 		if (ptx::mbar_try_wait(bar, parity)) return true;
-		if ((i & 255u) == 255u && *abort_flag) return false;
+		if (*abort_flag) return false;
+		if (ptx::globaltimer_ns() - t0 > ptx::WAIT_LIMIT_NS) break;
 	}
 	*abort_flag = 1;
 	return false;
@@ -181,26 +191,21 @@ __device__ __forceinline__ uint64_t make_desc_aug(uint32_t smem_addr)
 	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (8ull << 16) | (16ull << 32) | (1ull << 46);
 }
 
-__device__ __forceinline__ float fmin3(float a, float b, float c)
-{
-	float r;
-	asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-	return r;
-}
+__device__ __forceinline__ uint32_t umin3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_u32(a, b, c); }
 
-// Smallest and second-smallest of 32 values by a tournament: 16 (min,max) pairs, then 15 merges
+// Smallest and second-smallest of 32 keys by a tournament: 16 (min,max) pairs, then 15 merges
 // (b,s) x (b',s') -> (min(b,b'), min(max(b,b'), s, s')).  77 instructions, log depth.
-__device__ __forceinline__ void top2_of_32(const float (&p)[32], float& b, float& s)
+__device__ __forceinline__ void top2_of_32(const uint32_t (&p)[32], uint32_t& b, uint32_t& s)
 {
-	float lo[16], hi[16];
+	uint32_t lo[16], hi[16];
 	#pragma unroll
-	for (int i = 0; i < 16; ++i) { lo[i] = fminf(p[2 * i], p[2 * i + 1]); hi[i] = fmaxf(p[2 * i], p[2 * i + 1]); }
+	for (int i = 0; i < 16; ++i) { lo[i] = min(p[2 * i], p[2 * i + 1]); hi[i] = max(p[2 * i], p[2 * i + 1]); }
 	#pragma unroll
 	for (int n = 16; n > 1; n >>= 1) {
 		#pragma unroll
 		for (int i = 0; i < n / 2; ++i) {
-			const float nb = fminf(lo[2 * i], lo[2 * i + 1]);
-			const float ns = fmin3(fmaxf(lo[2 * i], lo[2 * i + 1]), hi[2 * i], hi[2 * i + 1]);
+			const uint32_t nb = min(lo[2 * i], lo[2 * i + 1]);
+			const uint32_t ns = umin3(max(lo[2 * i], lo[2 * i + 1]), hi[2 * i], hi[2 * i + 1]);
 			lo[i] = nb;
 			hi[i] = ns;
 		}
@@ -209,35 +214,41 @@ __device__ __forceinline__ void top2_of_32(const float (&p)[32], float& b, float
 	s = hi[0];
 }
 
-// One 32-column chunk of an accumulator row: put the column's position in the chunk into the
-// 5 low mantissa bits (so that the minimum carries its own index), reduce to the two smallest,
-// and merge them into the running (best, second, chunk of best).
-__device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t chunk_id,
-	float& best, float& second, uint32_t& best_chunk)
+// One 32-column chunk of an accumulator row.  The kernel adds a constant to every value so that
+// all of them are positive floats with the SAME exponent; their bit patterns then order like the
+// values, the upper exponent bits carry no information, and bits*32 + column (one integer
+// multiply-add, off the min/max pipe) is a key that keeps the full 23-bit mantissa and carries
+// the column position.  The keys are reduced to the two smallest and merged into the running
+// (best, second, chunk of best).  `nvalid` < 32 masks the padding columns behind the last mean.
+template<bool MASKED>
+__device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t chunk_id, uint32_t nvalid,
+	uint32_t& best, uint32_t& second, uint32_t& best_chunk)
 {
-	float p[32];
+	uint32_t p[32];
 	#pragma unroll
-	for (int t = 0; t < 32; ++t) p[t] = __uint_as_float((v[t] & 0xFFFFFFE0u) | (uint32_t)t);
-	float b, s2;
+	for (uint32_t t = 0; t < 32; ++t) p[t] = v[t] * 32u + t;
+	if (MASKED && nvalid < 32) {
+		#pragma unroll
+		for (uint32_t t = 0; t < 32; ++t) p[t] = t < nvalid ? p[t] : 0xFFFFFFFFu;
+	}
+	uint32_t b, s2;
 	top2_of_32(p, b, s2);
-	second = fmin3(second, fmaxf(best, b), s2);
+	second = umin3(second, max(best, b), s2);
 	best_chunk = b < best ? chunk_id : best_chunk;
-	best = fminf(best, b);
+	best = min(best, b);
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
 	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
-	uint64_t n, uint32_t n_tiles, uint32_t k_pad, uint32_t nt_cols, uint32_t ksteps, uint32_t idesc,
+	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t nt_cols, uint32_t ksteps, uint32_t idesc,
 	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef, uint32_t dbg)
 {
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 	TcBars* bars = reinterpret_cast<TcBars*>(smem + SM_BAR_OFF);
-	float* mg_best = reinterpret_cast<float*>(smem + SM_MERGE_OFF);
-	float* mg_second = mg_best + TC_MA * TC_MTILE;
-	uint32_t* mg_idx = reinterpret_cast<uint32_t*>(mg_second + TC_MA * TC_MTILE);
+	uint32_t* mg_state = reinterpret_cast<uint32_t*>(smem + SM_MERGE_OFF);
 	volatile uint32_t* abort_flag = &bars->abort_flag;
 
 	const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -262,13 +273,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		ptx::tmem_alloc(&bars->tmem_slot, TC_TMEM_COLS);
 		ptx::tmem_relinquish();
 	}
+	// Offset constant: every value |c|^2 - 2 x.c lies in [-X2, X2 + 2*C2] (X2, C2 = largest |x|^2,
+	// |c|^2); with P a power of two >= four times that span, value + P + X2 + P/1024 stays
+	// inside [P, 2P): one exponent for all, with head-room for the rounding of the pass.
+	const float x2max = ctl->xmax2, c2max = ctl->cmax2[slot];
+	float pow2 = 1.0f;
 	{
-		// the constant A operand of the |c|^2 K step: columns 0 and 1 are one (they meet the
-		// high and the low part of |c|^2), the rest zero
+		const float span = 4.0f * (2.0f * (x2max + c2max)) + 1.0e-30f;
+		int e;
+		frexpf(span, &e);                       // span = m * 2^e, m in [0.5, 1)
+		pow2 = ldexpf(1.0f, e);                 // >= span
+	}
+	const float offset_c = pow2 + x2max + pow2 * (1.0f / 1024.0f);
+	{
+		// the constant A operand of the extra K step: columns 0 and 1 are one (they meet the high
+		// and the low part of |c|^2), columns 2 and 3 hold the offset constant as tf32 hi/lo
+		// (they meet ones on the B side), the rest is zero
+		const float c_hi = to_tf32(offset_c), c_lo = to_tf32(offset_c - c_hi);
 		float* a_aug = reinterpret_cast<float*>(smem + SM_AAUG_OFF);
 		for (uint32_t e = threadIdx.x; e < TC_MTILE * 8; e += TC_THREADS) {
-			const uint32_t row = e >> 3, k = e & 7u;
-			a_aug[aug_offset(row, k)] = k < 2 ? 1.0f : 0.0f;
+			const uint32_t row = e >> 3, kk = e & 7u;
+			a_aug[aug_offset(row, kk)] = kk < 2 ? 1.0f : (kk == 2 ? c_hi : (kk == 3 ? c_lo : 0.0f));
 		}
 		ptx::fence_proxy_async();
 	}
@@ -320,130 +345,181 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		}
 	} else if (warp == 1) {
 		// ---------------- MMA issuer ----------------
-		if (lane == 0) {
+		// The whole warp walks the loop (so that the address arithmetic is warp-uniform and stays
+		// off the vector ALU, which the epilogue warps of the same scheduler keep busy); one
+		// elected lane issues the tensor-core instructions.
+		{
 			uint32_t a_use[TC_MA] = {0, 0};
 			uint32_t acc_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
+			long long t_b = 0, t_a = 0, t_acc = 0, t_issue = 0, t_start = clock64();
 			const uint64_t a_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_AAUG_OFF));
 			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
 				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
 					const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
+					long long c0 = clock64();
 					ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
+					t_b += clock64() - c0;
 					if (!ok) break;
 					const uint32_t b_addr = ptx::smem_u32(smem + SM_B_OFF + s * B_STAGE_BYTES);
 					const uint64_t b_hi = make_desc(b_addr), b_lo = make_desc(b_addr + B_PLANE_BYTES);
 					const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_BAUG_OFF + s * AUG_BYTES));
 					for (uint32_t i = 0; i < tiles; ++i) {
+						long long c1 = clock64();
 						if (j == 0) {
 							ok = wait_or_abort(&bars->a_full[i], a_use[i] & 1u, abort_flag);
 							if (!ok) break;
 						}
+						long long c2 = clock64();
 						ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
 						if (!ok) break;
+						long long c3 = clock64();
+						t_a += c2 - c1; t_acc += c3 - c2;
 						ptx::tc_fence_after();
 						const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + i * A_TILE_BYTES);
 						const uint64_t a_hi = make_desc(a_addr), a_lo = make_desc(a_addr + A_PLANE_BYTES);
 						const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
-						if (!(dbg & 1u)) {
-							// small cross terms first, then the dominant hi*hi term, then |c|^2;
-							// +2 in the descriptor's address field = 32 bytes = one K step
-							for (uint32_t ks = 0; ks < ksteps; ++ks) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
-							for (uint32_t ks = 0; ks < ksteps; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
-							for (uint32_t ks = 0; ks < ksteps; ++ks) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
-							ptx::mma_tf32(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
+						if (ptx::elect_one()) {
+							if (!(dbg & 1u)) {
+								// small cross terms first, then the dominant hi*hi term, then |c|^2;
+								// +2 in the descriptor's address field = 32 bytes = one K step
+								#pragma unroll
+								for (uint32_t ks = 0; ks < 4; ++ks)
+									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
+								#pragma unroll
+								for (uint32_t ks = 0; ks < 4; ++ks)
+									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
+								#pragma unroll
+								for (uint32_t ks = 0; ks < 4; ++ks)
+									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
+								ptx::mma_tf32(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
+							}
+							ptx::mma_commit(&bars->acc_full[i]);
+							if (j == n_ctiles - 1) ptx::mma_commit(&bars->a_empty[i]);
 						}
-						ptx::mma_commit(&bars->acc_full[i]);
+						__syncwarp();
+						t_issue += clock64() - c3;
 						++acc_use[i];
-						if (j == n_ctiles - 1) {
-							ptx::mma_commit(&bars->a_empty[i]);
-							++a_use[i];
-						}
+						if (j == n_ctiles - 1) ++a_use[i];
 					}
 					if (!ok) break;
-					ptx::mma_commit(&bars->b_empty[s]);
+					if (ptx::elect_one()) ptx::mma_commit(&bars->b_empty[s]);
+					__syncwarp();
 					++b_count;
 				}
 			}
+			if ((dbg & 32u) && blockIdx.x == 3 && lane == 0)
+				printf("mma warp: total %lld  wait_b %lld  wait_a %lld  wait_acc %lld  issue %lld  (tiles %u)\n",
+					clock64() - t_start, t_b, t_a, t_acc, t_issue, b_count * TC_MA);
 		}
 	} else {
 		// ---------------- epilogue ----------------
+		// The loops over tiles and chunks are kept rolled on purpose: unrolled, the arg-min code
+		// of one block outgrows the instruction cache and the warps starve on instruction fetch.
 		const uint32_t q = warp & 3u;              // TMEM lane quarter this warp may read
-		const uint32_t h = (warp - 2) >> 2;        // which half of the tile's columns
+		const uint32_t part = (warp - 2) >> 2;     // which quarter of the tile's columns (0..3)
 		const uint32_t row = q * 32 + lane;
-		const float cmax2 = ctl->cmax2[slot];
-		const uint32_t half_cols = ((nt_cols >> 5) + 1) / 2 * 32;      // columns of the first half (whole chunks)
-		const uint32_t colbase = h * half_cols;
-		const uint32_t nchunks = h == 0 ? (half_cols >> 5) : ((nt_cols - half_cols) >> 5);   // 0..4
+		const float ulp = pow2 * 1.1920929e-07f;   // spacing of the values inside [P, 2P)
+		const uint32_t chunks_total = nt_cols >> 5;                    // 1..8
+		const uint32_t per_part = (chunks_total + 3) / 4;              // 1..2
+		const uint32_t first_chunk = part * per_part;
+		const uint32_t nchunks = first_chunk >= chunks_total ? 0u : min(per_part, chunks_total - first_chunk);
+		const uint32_t colbase = first_chunk * 32;
 		uint32_t acc_use[TC_MA] = {0, 0};
 		bool ok = true;
+		long long e_wait = 0, e_ld = 0, e_cmp = 0, e_merge = 0, e_start = clock64();
 		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-			float best[TC_MA], second[TC_MA];
-			uint32_t bchunk[TC_MA];
-			#pragma unroll
-			for (uint32_t i = 0; i < TC_MA; ++i) { best[i] = INFINITY; second[i] = INFINITY; bchunk[i] = 0; }
+			uint32_t best0 = 0xFFFFFFFFu, second0 = 0xFFFFFFFFu, bchunk0 = 0;
+			uint32_t best1 = 0xFFFFFFFFu, second1 = 0xFFFFFFFFu, bchunk1 = 0;
+			// |x|^2 of this thread's two points is only needed at the end of the block: fetch it now
+			float xn0 = 0.0f, xn1 = 0.0f;
+			if (part == 0) {
+				const uint64_t p0 = (uint64_t)(blk * TC_MA) * TC_MTILE + row;
+				if (p0 < n) xn0 = xnorm[p0];
+				if (p0 + TC_MTILE < n) xn1 = xnorm[p0 + TC_MTILE];
+			}
 			for (uint32_t j = 0; j < n_ctiles; ++j) {
-				#pragma unroll
-				for (uint32_t i = 0; i < TC_MA; ++i) {
-					if (i < tiles) {
-						if (ok) {
-							// one lane polls the barrier, the warp follows
-							bool w = true;
-							if (lane == 0) w = wait_or_abort(&bars->acc_full[i], acc_use[i] & 1u, abort_flag);
-							ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
+				#pragma unroll 1
+				for (uint32_t i = 0; i < tiles; ++i) {
+					const uint32_t use = i ? acc_use[1] : acc_use[0];
+					long long e0 = clock64();
+					if (ok) {
+						// one lane polls the barrier, the warp follows
+						bool w = true;
+						if (lane == 0) w = wait_or_abort(&bars->acc_full[i], use & 1u, abort_flag);
+						ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
+					}
+					if (i) ++acc_use[1]; else ++acc_use[0];
+					long long e1 = clock64();
+					e_wait += e1 - e0;
+					if (ok && nchunks > 0 && !(dbg & 4u)) {
+						ptx::tc_fence_after();
+						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
+						const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
+						// This warp's columns go to registers first and the accumulator is handed back
+						// to the MMA warp right away; the arg-min then runs from registers while the
+						// tensor cores already fill the accumulator again.
+						uint32_t v0[32], v1[32];
+						ptx::tmem_ld32(taddr, v0);
+						if (nchunks > 1) ptx::tmem_ld32(taddr + 32, v1);
+						ptx::tmem_ld_wait();
+						ptx::tc_fence_before();
+						__syncwarp();
+						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
+						long long e2 = clock64();
+						e_ld += e2 - e1;
+						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
+						// columns at or behind k are padding
+						const uint32_t col0 = chunk0 * 32u;
+						const uint32_t left = k > col0 ? k - col0 : 0u;
+						if (dbg & 2u) {
+							b = min(b, v0[0] ^ v0[31] ^ v1[7]);
+						} else if (left >= 64 || (nchunks == 1 && left >= 32)) {
+							chunk_update<false>(v0, chunk0, 32, b, s2, bc);
+							if (nchunks > 1) chunk_update<false>(v1, chunk0 + 1, 32, b, s2, bc);
+						} else {
+							if (left > 0) chunk_update<true>(v0, chunk0, left, b, s2, bc);
+							if (nchunks > 1 && left > 32) chunk_update<true>(v1, chunk0 + 1, left - 32, b, s2, bc);
 						}
-						++acc_use[i];
-						if (ok && nchunks > 0 && !(dbg & 4u)) {
-							ptx::tc_fence_after();
-							const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
-							const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
-							uint32_t v0[32], v1[32];
-							// chunks 0 and 1 in flight together, then 2 and 3 while 1 is reduced
-							ptx::tmem_ld32(taddr, v0);
-							if (nchunks > 1) ptx::tmem_ld32(taddr + 32, v1);
-							ptx::tmem_ld_wait();
-							if (!(dbg & 2u)) chunk_update(v0, chunk0, best[i], second[i], bchunk[i]);
-							if (nchunks > 2) ptx::tmem_ld32(taddr + 64, v0);
-							if (nchunks > 1 && !(dbg & 2u)) chunk_update(v1, chunk0 + 1, best[i], second[i], bchunk[i]);
-							if (nchunks > 3) ptx::tmem_ld32(taddr + 96, v1);
-							if (nchunks > 2) {
-								ptx::tmem_ld_wait();
-								if (!(dbg & 2u)) chunk_update(v0, chunk0 + 2, best[i], second[i], bchunk[i]);
-								if (nchunks > 3 && !(dbg & 2u)) chunk_update(v1, chunk0 + 3, best[i], second[i], bchunk[i]);
-							}
-							if (dbg & 2u) best[i] = fminf(best[i], __uint_as_float(v0[0] ^ v0[31] ^ v1[7]));
-							ptx::tc_fence_before();
-						}
+						if (i) { best1 = b; second1 = s2; bchunk1 = bc; } else { best0 = b; second0 = s2; bchunk0 = bc; }
+						e_cmp += clock64() - e2;
+					} else {
 						__syncwarp();
 						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
 					}
 				}
 			}
-			// merge the two column halves: half 1 hands its state over through shared memory
-			if (h == 1) {
-				#pragma unroll
-				for (uint32_t i = 0; i < TC_MA; ++i) {
-					mg_best[i * TC_MTILE + row] = best[i];
-					mg_second[i * TC_MTILE + row] = second[i];
-					mg_idx[i * TC_MTILE + row] = bchunk[i] * 32u + (__float_as_uint(best[i]) & 31u);
-				}
+			long long e3 = clock64();
+			// merge the four column parts: parts 1..3 hand their state over through shared memory
+			uint32_t* mg = mg_state;
+			if (part > 0) {
+				uint32_t* dst = mg + (part - 1) * (3 * TC_MA * TC_MTILE);
+				dst[0 * TC_MTILE + row] = best0; dst[1 * TC_MTILE + row] = second0; dst[2 * TC_MTILE + row] = bchunk0;
+				dst[3 * TC_MTILE + row] = best1; dst[4 * TC_MTILE + row] = second1; dst[5 * TC_MTILE + row] = bchunk1;
 			}
 			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
-			if (h == 0) {
+			if (part == 0) {
 				#pragma unroll
 				for (uint32_t i = 0; i < TC_MA; ++i) {
 					const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
 					if (i < tiles && p < n && ok && !dbg) {
-						const float ob = mg_best[i * TC_MTILE + row], os = mg_second[i * TC_MTILE + row];
-						const uint32_t oi = mg_idx[i * TC_MTILE + row];
-						const uint32_t mi = bchunk[i] * 32u + (__float_as_uint(best[i]) & 31u);
-						const float b = fminf(best[i], ob);
-						const float s2 = fmin3(second[i], os, fmaxf(best[i], ob));
-						asg[p] = (ob < best[i] || (ob == best[i] && oi < mi)) ? oi : mi;
-						const float margin = margin_coef * (xnorm[p] + cmax2);
-						if (s2 - b <= margin) {
+						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
+						#pragma unroll
+						for (uint32_t o = 0; o < 3; ++o) {
+							const uint32_t* src = mg + o * (3 * TC_MA * TC_MTILE) + i * 3 * TC_MTILE;
+							const uint32_t ob = src[row], os = src[TC_MTILE + row], oc = src[2 * TC_MTILE + row];
+							s2 = umin3(s2, os, max(b, ob));
+							bc = ob < b ? oc : bc;
+							b = min(b, ob);
+						}
+						asg[p] = bc * 32u + (b & 31u);
+						// keys are (mantissa bits << 5 | column): their difference >> 5 counts value spacings
+						const float gap = s2 == 0xFFFFFFFFu ? INFINITY : (float)((s2 >> 5) - (b >> 5)) * ulp;
+						const float margin = margin_coef * ((i ? xn1 : xn0) + c2max) + 4.0f * ulp;
+						if (gap <= margin) {
 							const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
 							if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
 							else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
@@ -452,7 +528,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				}
 			}
 			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+			e_merge += clock64() - e3;
 		}
+		if ((dbg & 32u) && blockIdx.x == 3 && lane == 0 && (warp == 2 || warp == 7 || warp == 17))
+			printf("epi warp %u: total %lld  wait %lld  ld %lld  compute %lld  merge %lld\n", warp, clock64() - e_start, e_wait, e_ld, e_cmp, e_merge);
 	}
 
 	ptx::tc_fence_before();
@@ -549,14 +628,13 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
 	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
-	// (the 5 index bits packed into the mantissa perturb a value by < 2^-18 of its magnitude)
-	const float margin_coef = margin_scale * ((40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f + 2.0f * 3.8146973e-06f);
+	const float margin_coef = margin_scale * (40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
 	static const uint32_t dbg = getenv("BKM_TC_DEBUG") ? (uint32_t)atoi(getenv("BKM_TC_DEBUG")) : 0u;
 	uint32_t idesc = p->idesc;
 	if (dbg & 8u) idesc = (idesc & ~(0x3Fu << 17)) | ((64u >> 3) << 17);    // N = 64: half the tensor work per instruction
 	if (dbg & 16u) idesc = (idesc & ~(0x3Fu << 17)) | ((32u >> 3) << 17);   // N = 32
 	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
-		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->tm.k_pad, p->nt_cols, (p->s.dim + 7) / 8, idesc,
+		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, (p->s.dim + 7) / 8, idesc,
 		ctl, slot, flag_list, margin_coef, dbg);
 	return cudaGetLastError();
 }

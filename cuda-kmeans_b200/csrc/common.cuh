@@ -22,7 +22,8 @@ struct Control {
 	float cmax2[2];        // max over clusters of |mean|^2; the preparation of iteration t
 	                       // writes slot (t+1)&1 with atomicMax and clears slot t&1
 	uint32_t last_flag_count; // flag_count of the last finished iteration (for reporting)
-	uint32_t pad[3];
+	float xmax2;           // max over the points of |x|^2 (written by the one-off split of the points)
+	uint32_t pad[2];
 };
 
 // Element offset of (item, dim) in a buffer of `items` vectors of `dims` floats.

@@ -18,8 +18,8 @@ struct TcMeans {
 	float* b_hi;     // [k_pad][d_pad] tf32 high part of -2*mean, K-major
 	float* b_lo;     // [k_pad][d_pad] tf32 low part
 	float* cnorm;    // [k_pad] |mean|^2, +inf for padding rows
-	float* b_aug;    // [k_pad x 8] tf32 (hi, lo) of |mean|^2 in columns 0,1 of one K step (aug_offset layout);
-	                 // padding rows hold a huge finite value so that they never win
+	float* b_aug;    // [k_pad x 8] one K step (aug_offset layout): columns 0,1 = tf32 (hi, lo) of |mean|^2,
+	                 // columns 2,3 = 1 (they meet the kernel's offset constant), rest 0; padding rows 0,0,1,1
 	uint32_t k_pad;  // k rounded up to the centroid tile
 	uint32_t d_pad;  // dim rounded up to TC_KCHUNK
 };
@@ -69,7 +69,7 @@ cudaError_t launch_assign_simt(const float* pts, const float* cprep, uint32_t* a
 bool assign_tc_supported(const Shape& s);
 uint32_t tc_kpad(uint32_t k);
 // One-off split of the points into tf32 hi/lo K-major planes + |x|^2.
-cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, cudaStream_t stream);
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, Control* ctl, cudaStream_t stream);
 // Opaque per-handle state (tensor maps).  Created once the operand buffers exist.
 struct TcPlan;
 TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err);

@@ -8,9 +8,19 @@
 
 namespace bkm { namespace ptx {
 
-// Polls before a wait gives up.  try_wait itself blocks for a hardware-defined slice, so this
-// is many milliseconds at least - far beyond any legitimate wait in these kernels.
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+// A wait gives up after this many nanoseconds (read from %globaltimer) - far beyond any
+// legitimate wait in these kernels, short enough that a broken pipeline ends by itself.
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+// How long one try_wait may keep the thread suspended before it returns to be polled again.
+// A long slice keeps waiting threads from burning issue slots that the working warps need.
+constexpr uint32_t WAIT_SLICE_NS = 20000u;
+
+__device__ __forceinline__ uint64_t globaltimer_ns()
+{
+	uint64_t t;
+	asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+	return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
@@ -49,20 +59,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 	asm volatile(
 		"{\n"
 		".reg .pred p;\n"
-		"mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+		"mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
 		"selp.u32 %0, 1, 0, p;\n"
 		"}\n"
-		: "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+		: "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_SLICE_NS) : "memory");
 	return ok != 0;
 }
 
-// Bounded wait.  Returns false if the phase did not complete within WAIT_LIMIT polls.
+// Bounded wait.  Returns false if the phase did not complete within WAIT_LIMIT_NS.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {
-	for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+	if (mbar_try_wait(bar, parity)) return true;
+	const uint64_t t0 = globaltimer_ns();
+	while (true) {
 		if (mbar_try_wait(bar, parity)) return true;
+		if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
 	}
-	return false;
 }
 
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
@@ -112,6 +124,20 @@ __device__ __forceinline__ void tc_fence_before()
 __device__ __forceinline__ void tc_fence_after()
 {
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one()
+{
+	uint32_t pred;
+	asm volatile(
+		"{\n"
+		".reg .pred p;\n"
+		"elect.sync _|p, 0xffffffff;\n"
+		"selp.u32 %0, 1, 0, p;\n"
+		"}\n"
+		: "=r"(pred));
+	return pred != 0;
 }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc], kind::tf32, issued by one thread.

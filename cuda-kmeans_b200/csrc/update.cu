@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 					const float hi = tf32_rna(s2);
 					const float lo = tf32_rna(s2 - hi);
 					float4* dst = reinterpret_cast<float4*>(b_aug + aug_offset(c, 0));
-					dst[0] = make_float4(hi, lo, 0.0f, 0.0f);
+					dst[0] = make_float4(hi, lo, 1.0f, 1.0f);
 					dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);    // columns 4..7 sit 32 floats further
 				}
 				atomicMax(reinterpret_cast<int*>(&ctl->cmax2[slot]), __float_as_int(s2));
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 			if (cnorm && c < k_pad) cnorm[c] = INFINITY;
 			if (b_aug && c < k_pad) {
 				float4* dst = reinterpret_cast<float4*>(b_aug + aug_offset(c, 0));
-				dst[0] = make_float4(tf32_rna(1.0e30f), 0.0f, 0.0f, 0.0f);
+				dst[0] = make_float4(0.0f, 0.0f, 1.0f, 1.0f);
 				dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 			}
 		}
