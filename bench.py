@@ -35,6 +35,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 V100_PUBLISHED_GEVALS = 84.4  # reference's best variant, N=2M d=32 k=1024, V100 (results/README.md:20)
+# dram__bytes_read.sum + dram__bytes_write.sum of one assign_tc_kernel launch on workload c2, from the ncu
+# capture summarised in profiles/assign_tc_kernel_c2.md (546.99 MB + 12.44 MB).
+C2_ASSIGN_TC_DRAM_BYTES = 559.4e6
 
 
 def parse_args():
@@ -315,8 +318,10 @@ def main():
         if counters["assign_variant"] == "tc" or flops_iter / (peaks["bf16_tflops"] * 0.5e12) > bytes_iter / (peaks["hbm_gbs"] * 1e9):
             tf32_peak = peaks["bf16_tflops"] * 0.5
             ach = flops_iter / (assign_ms * 1e-3) / 1e12
+            traffic = C2_ASSIGN_TC_DRAM_BYTES if (args.workload == "c2" and not args.n and counters["assign_variant"] == "tc") else None
             roofline = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
-                        "traffic": None, "kernel": "assignment (%s)" % counters["assign_variant"],
+                        "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write)",
+                        "kernel": "assignment (%s)" % counters["assign_variant"],
                         "kernel_ms": assign_ms,
                         "peak_note": "TF32 dense taken as half the %s bf16 burst peak; 3xTF32 issues 3 tensor "
                                      "flops per algorithmic flop, so 1/3 is the ceiling of this fraction" % peaks["source"]}

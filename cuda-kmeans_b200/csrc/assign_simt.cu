@@ -6,12 +6,13 @@
 //    for the queued near-ties of the fast passes.  Replaces baseAssignmentKernel
 //    (kernels/kernels.cu:182-199 of the reference) and follows serial.hpp:21-35.
 //
-//  * assign_simt_kernel<D>: small-d fast pass.  The prepared means ([|c|^2, -2c...] rows)
-//    are staged into shared memory with a bulk TMA copy; every thread keeps P points in
-//    registers and evaluates |c|^2 - 2 x.c with D fused multiply-adds per mean, tracking the
-//    best and second-best value.  A point whose two best values are closer than the rounding
-//    band of this formulation is queued for the exact kernel, so the final result equals the
-//    reference's for every point.  Covers the shape range of cachedFixedAssignmentKernel
+//  * assign_simt_kernel<D>: small-d fast pass.  The means are staged into shared memory with a
+//    bulk TMA copy; every thread keeps P points in registers and evaluates sum (x-c)^2 with a
+//    subtract and a fused multiply-add per dimension (the difference form keeps its relative
+//    accuracy for tight clusters far from the origin, where |c|^2 - 2 x.c would cancel),
+//    tracking the best and second-best value.  A point whose two best values are closer than
+//    the rounding band (of this pass, of the reference's own sum, and of its square root) is
+//    queued for the exact kernel, so the final result equals the reference's for every point.  Covers the shape range of cachedFixedAssignmentKernel
 //    (kernels/kernels.cu:218-273) and cachedAllMeansAssignmentKernel (:330-374).
 #include "kernels.cuh"
 #include "ptx.cuh"
@@ -65,9 +66,11 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
 }
 
 
-// The same arithmetic for a list of queued points: one block per point, the means spread over
-// all threads (four independent distance chains per thread), so that a short list still fills
-// the machine and a single point does not serialise k*dim dependent additions in one warp.
+// The same arithmetic for a list of queued points: one block per point, one mean per thread at a
+// time, so that a short list still fills the machine.  Each distance is still summed in
+// dimension order by a single thread.  AoS means are staged through a shared tile (32 dimensions
+// of 256 means at a time, loaded along the dimensions) so that the global loads stay coalesced;
+// SoA means are read directly (consecutive threads = consecutive means).
 constexpr int LIST_THREADS = 256;
 
 template<bool SOA, bool SOAM>
@@ -75,7 +78,8 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
 	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
 {
-	extern __shared__ float sx[];
+	extern __shared__ float sx[];                       // the point (d floats), then the means tile
+	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + ((d + 3) & ~3u));
 	__shared__ float sbest[LIST_THREADS / 32];
 	__shared__ uint32_t sidx[LIST_THREADS / 32];
 	const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -88,25 +92,35 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 		__syncthreads();
 		float best = INFINITY;
 		uint32_t bidx = 0xffffffffu;
-		for (uint32_t m0 = tid; m0 < k; m0 += LIST_THREADS * 4) {
-			uint32_t m[4];
-			float sum[4];
-			#pragma unroll
-			for (int u = 0; u < 4; ++u) { m[u] = m0 + u * LIST_THREADS; sum[u] = 0.0f; if (m[u] >= k) m[u] = k - 1; }
-			for (uint32_t j = 0; j < d; ++j) {
-				const float xj = sx[j];
-				#pragma unroll
-				for (int u = 0; u < 4; ++u) {
-					const float diff = __fsub_rn(xj, means[at<SOAM>(m[u], j, k, d)]);
-					sum[u] = __fadd_rn(sum[u], __fmul_rn(diff, diff));
+		for (uint32_t m0 = 0; m0 < k; m0 += LIST_THREADS) {
+			const uint32_t m = m0 + tid;
+			float sum = 0.0f;
+			if (SOAM) {
+				if (m < k) {
+					for (uint32_t j = 0; j < d; ++j) {
+						const float diff = __fsub_rn(sx[j], means[(size_t)j * k + m]);
+						sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+					}
+				}
+			} else {
+				for (uint32_t j0 = 0; j0 < d; j0 += 32) {
+					__syncthreads();
+					#pragma unroll 4
+					for (uint32_t r = 0; r < 32; ++r) {
+						const uint32_t row = warp * 32 + r;
+						tile[row][lane] = (m0 + row < k && j0 + lane < d) ? means[(size_t)(m0 + row) * d + j0 + lane] : 0.0f;
+					}
+					__syncthreads();
+					const uint32_t jn = d - j0 < 32 ? d - j0 : 32;
+					for (uint32_t jj = 0; jj < jn; ++jj) {
+						const float diff = __fsub_rn(sx[j0 + jj], tile[tid][jj]);
+						sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+					}
 				}
 			}
-			#pragma unroll
-			for (int u = 0; u < 4; ++u) {
-				if (m0 + u * LIST_THREADS < k) {
-					const float dist = __fsqrt_rn(sum[u]);
-					if (bidx == 0xffffffffu || dist < best) { best = dist; bidx = m[u]; }
-				}
+			if (m < k) {
+				const float dist = __fsqrt_rn(sum);
+				if (bidx == 0xffffffffu || dist < best) { best = dist; bidx = m; }
 			}
 		}
 		#pragma unroll
@@ -131,8 +145,8 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
 	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
 {
-	if (list != nullptr && (size_t)s.dim * sizeof(float) <= 160 * 1024) {
-		const size_t lsmem = (size_t)s.dim * sizeof(float);
+	if (list != nullptr && (size_t)s.dim * sizeof(float) <= 120 * 1024) {
+		const size_t lsmem = (size_t)((s.dim + 3) & ~3u) * sizeof(float) + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
 		const uint32_t lgrid = (uint32_t)sm_count * 8;
 #define BKM_LAUNCH_LIST(SOA, SOAM) do { \
 		auto kern = assign_exact_list_kernel<SOA, SOAM>; \
@@ -208,12 +222,10 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 		ok = ptx::mbar_wait(&bar, phase);
 		phase ^= 1;
 	}
-	const float cmax2 = ctl->cmax2[slot];
 
 	for (uint64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
 		float x[P][D];
 		uint64_t idx[P];
-		float xn[P];
 		const uint64_t base = blk * per_block;
 		if (SOA) {
 			#pragma unroll
@@ -250,10 +262,6 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 		#pragma unroll
 		for (int p = 0; p < P; ++p) {
 			best[p] = INFINITY; second[p] = INFINITY; bidx[p] = 0;
-			float s2 = 0.0f;
-			#pragma unroll
-			for (int j = 0; j < D; ++j) s2 = fmaf(x[p][j], x[p][j], s2);
-			xn[p] = s2;
 		}
 
 		for (uint32_t t = 0; t < ntiles; ++t) {
@@ -283,7 +291,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 				for (int p = 0; p < P; ++p) {
 					float v = r[0];
 					#pragma unroll
-					for (int j = 0; j < D; ++j) v = fmaf(x[p][j], r[1 + j], v);
+					for (int j = 0; j < D; ++j) { const float diff = x[p][j] - r[1 + j]; v = fmaf(diff, diff, v); }
 					const bool lt = v < best[p];
 					second[p] = fminf(second[p], fmaxf(best[p], v));
 					best[p] = fminf(best[p], v);
@@ -296,8 +304,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 		for (int p = 0; p < P; ++p) {
 			if (idx[p] < n) {
 				asg[idx[p]] = bidx[p];
-				const float margin = margin_coef * (xn[p] + cmax2);
-				if (second[p] - best[p] <= margin) {
+				if (second[p] - best[p] <= margin_coef * second[p]) {
 					uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
 					if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)idx[p];
 					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
@@ -325,7 +332,7 @@ static cudaError_t launch_simt_d(const float* pts, const float* cprep, uint32_t*
 	const uint64_t nblocks = (s.n + per_block - 1) / per_block;
 	// persistent grid: a whole number of resident blocks per SM
 	int per_sm = 1;
-	const float margin_coef = margin_scale * (float)(D + 8) * 2.384185791015625e-07f; // (D+8) * 2^-22
+	const float margin_coef = margin_scale * (float)(2 * D + 8) * 1.1920929e-07f;    // (2D+8) * 2^-23, relative
 	const int vec_ok = ((reinterpret_cast<uintptr_t>(pts) & 15u) == 0) ? 1 : 0;
 #define BKM_LAUNCH_SIMT(SOA) do { \
 		auto kern = assign_simt_kernel<D, SOA>; \

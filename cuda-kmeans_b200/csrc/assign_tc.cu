@@ -37,7 +37,6 @@
 #include "ptx.cuh"
 
 #include <cmath>
-#include <cstdio>
 #include <cstdlib>
 #include <new>
 
@@ -56,6 +55,12 @@ constexpr uint32_t B_PLANE_BYTES = TC_NT_MAX * TC_KCHUNK * 4;    // 32 KiB: 256 
 constexpr uint32_t A_TILE_BYTES = 2 * A_PLANE_BYTES;             // hi + lo
 constexpr uint32_t B_STAGE_BYTES = 2 * B_PLANE_BYTES;
 constexpr uint32_t AUG_BYTES = TC_NT_MAX * 8 * 4;                // 8 KiB: 256 rows x one K step of 8
+// K-loop mode (dim > 32): both operands stream, one 32-dimension slice per stage:
+// [A hi | A lo | B hi | B lo | B's |c|^2 step]; two such stages fill the same bytes as the
+// resident-points layout below.
+constexpr uint32_t KSTAGE_BYTES = A_TILE_BYTES + B_STAGE_BYTES + AUG_BYTES;
+constexpr uint32_t KS_ALO_OFF = A_PLANE_BYTES, KS_BHI_OFF = A_TILE_BYTES, KS_BLO_OFF = A_TILE_BYTES + B_PLANE_BYTES,
+	KS_AUG_OFF = A_TILE_BYTES + B_STAGE_BYTES;
 constexpr uint32_t SM_A_OFF = 0;
 constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;
 constexpr uint32_t SM_BAUG_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // |c|^2 K step per stage
@@ -71,7 +76,7 @@ uint32_t tc_kpad(uint32_t k) { return round_up(k, tc_nt_cols(k)); }
 
 bool assign_tc_supported(const Shape& s)
 {
-	return s.dim <= TC_KCHUNK && tc_kpad(s.k) <= TC_MAX_KPAD && s.n < (1ull << 32) - 1024;
+	return s.dim <= 4096 && tc_kpad(s.k) <= TC_MAX_KPAD && s.n < (1ull << 32) - 1024;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -163,6 +168,7 @@ struct TcBars {
 };
 static_assert(sizeof(TcBars) <= 256, "barrier block too large");
 static_assert(SM_ALLOC <= 227 * 1024, "shared memory budget exceeded");
+static_assert(TC_NB * KSTAGE_BYTES <= SM_AAUG_OFF, "K-loop stages overlap the constant tile");
 
 // Bounded wait that also gives up when another role already failed.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
@@ -242,8 +248,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
 	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
-	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t nt_cols, uint32_t ksteps, uint32_t idesc,
-	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef, uint32_t dbg)
+	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t nt_cols, uint32_t kchunks, uint32_t ksteps, uint32_t idesc,
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef)
 {
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -310,6 +316,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			uint32_t a_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
+			if (kchunks > 1) {
+				// K-loop mode: one (point tile, centroid tile, 32-dimension slice) per stage
+				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+					for (uint32_t j = 0; j < n_ctiles && ok; ++j)
+						for (uint32_t i = 0; i < tiles && ok; ++i)
+							for (uint32_t kc = 0; kc < kchunks; ++kc) {
+								const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
+								ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
+								if (!ok) break;
+								uint8_t* dst = smem + s * KSTAGE_BYTES;
+								const bool last = kc == kchunks - 1;
+								const uint32_t aug_bytes = last ? nt_cols * 8 * 4 : 0u;
+								const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE), x = (int32_t)(kc * TC_KCHUNK);
+								ptx::mbar_arrive_expect_tx(&bars->b_full[s], A_TILE_BYTES + 2 * nt_cols * TC_KCHUNK * 4 + aug_bytes);
+								ptx::tma_load_2d(dst, &tm_a_hi, x, row, &bars->b_full[s]);
+								ptx::tma_load_2d(dst + KS_ALO_OFF, &tm_a_lo, x, row, &bars->b_full[s]);
+								ptx::tma_load_2d(dst + KS_BHI_OFF, &tm_b_hi, x, (int32_t)(j * nt_cols), &bars->b_full[s]);
+								ptx::tma_load_2d(dst + KS_BLO_OFF, &tm_b_lo, x, (int32_t)(j * nt_cols), &bars->b_full[s]);
+								if (last) ptx::bulk_g2s(dst + KS_AUG_OFF, b_aug + (size_t)j * nt_cols * 8, aug_bytes, &bars->b_full[s]);
+								++b_count;
+							}
+				}
+			} else
 			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
 				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 				for (uint32_t i = 0; i < tiles && ok; ++i) {
@@ -353,36 +383,70 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			uint32_t acc_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
-			long long t_b = 0, t_a = 0, t_acc = 0, t_issue = 0, t_start = clock64();
 			const uint64_t a_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_AAUG_OFF));
+			if (kchunks > 1) {
+				// K-loop mode: the accumulator of a (point tile, centroid tile) pair collects all slices
+				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+					for (uint32_t j = 0; j < n_ctiles && ok; ++j)
+						for (uint32_t i = 0; i < tiles && ok; ++i) {
+							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
+							if (!ok) break;
+							ptx::tc_fence_after();
+							const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
+							for (uint32_t kc = 0; kc < kchunks; ++kc) {
+								const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
+								ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
+								if (!ok) break;
+								ptx::tc_fence_after();
+								const uint32_t base = ptx::smem_u32(smem + s * KSTAGE_BYTES);
+								const uint64_t a_hi = make_desc(base), a_lo = make_desc(base + KS_ALO_OFF);
+								const uint64_t b_hi = make_desc(base + KS_BHI_OFF), b_lo = make_desc(base + KS_BLO_OFF);
+								const bool last = kc == kchunks - 1;
+								const uint32_t steps = last ? ksteps : 4u;
+								if (ptx::elect_one()) {
+									#pragma unroll
+									for (uint32_t ks = 0; ks < 4; ++ks)
+										if (ks < steps) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, (kc | ks) > 0);
+									#pragma unroll
+									for (uint32_t ks = 0; ks < 4; ++ks)
+										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
+									#pragma unroll
+									for (uint32_t ks = 0; ks < 4; ++ks)
+										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
+									if (last) ptx::mma_tf32(d_tmem, a_aug_desc, make_desc_aug(base + KS_AUG_OFF), idesc, 1);
+									ptx::mma_commit(&bars->b_empty[s]);
+									if (last) ptx::mma_commit(&bars->acc_full[i]);
+								}
+								__syncwarp();
+								++b_count;
+							}
+							++acc_use[i];
+						}
+				}
+			} else
 			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
 				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
 					const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
-					long long c0 = clock64();
 					ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
-					t_b += clock64() - c0;
 					if (!ok) break;
 					const uint32_t b_addr = ptx::smem_u32(smem + SM_B_OFF + s * B_STAGE_BYTES);
 					const uint64_t b_hi = make_desc(b_addr), b_lo = make_desc(b_addr + B_PLANE_BYTES);
 					const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_BAUG_OFF + s * AUG_BYTES));
 					for (uint32_t i = 0; i < tiles; ++i) {
-						long long c1 = clock64();
 						if (j == 0) {
 							ok = wait_or_abort(&bars->a_full[i], a_use[i] & 1u, abort_flag);
 							if (!ok) break;
 						}
-						long long c2 = clock64();
 						ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
 						if (!ok) break;
-						long long c3 = clock64();
-						t_a += c2 - c1; t_acc += c3 - c2;
 						ptx::tc_fence_after();
 						const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + i * A_TILE_BYTES);
 						const uint64_t a_hi = make_desc(a_addr), a_lo = make_desc(a_addr + A_PLANE_BYTES);
 						const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
 						if (ptx::elect_one()) {
-							if (!(dbg & 1u)) {
+							{
 								// small cross terms first, then the dominant hi*hi term, then |c|^2;
 								// +2 in the descriptor's address field = 32 bytes = one K step
 								#pragma unroll
@@ -400,7 +464,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							if (j == n_ctiles - 1) ptx::mma_commit(&bars->a_empty[i]);
 						}
 						__syncwarp();
-						t_issue += clock64() - c3;
 						++acc_use[i];
 						if (j == n_ctiles - 1) ++a_use[i];
 					}
@@ -410,9 +473,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					++b_count;
 				}
 			}
-			if ((dbg & 32u) && blockIdx.x == 3 && lane == 0)
-				printf("mma warp: total %lld  wait_b %lld  wait_a %lld  wait_acc %lld  issue %lld  (tiles %u)\n",
-					clock64() - t_start, t_b, t_a, t_acc, t_issue, b_count * TC_MA);
 		}
 	} else {
 		// ---------------- epilogue ----------------
@@ -429,7 +489,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		const uint32_t colbase = first_chunk * 32;
 		uint32_t acc_use[TC_MA] = {0, 0};
 		bool ok = true;
-		long long e_wait = 0, e_ld = 0, e_cmp = 0, e_merge = 0, e_start = clock64();
 		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 			uint32_t best0 = 0xFFFFFFFFu, second0 = 0xFFFFFFFFu, bchunk0 = 0;
@@ -445,7 +504,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				#pragma unroll 1
 				for (uint32_t i = 0; i < tiles; ++i) {
 					const uint32_t use = i ? acc_use[1] : acc_use[0];
-					long long e0 = clock64();
 					if (ok) {
 						// one lane polls the barrier, the warp follows
 						bool w = true;
@@ -453,9 +511,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
 					}
 					if (i) ++acc_use[1]; else ++acc_use[0];
-					long long e1 = clock64();
-					e_wait += e1 - e0;
-					if (ok && nchunks > 0 && !(dbg & 4u)) {
+					if (ok && nchunks > 0) {
 						ptx::tc_fence_after();
 						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
 						const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
@@ -469,15 +525,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						ptx::tc_fence_before();
 						__syncwarp();
 						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
-						long long e2 = clock64();
-						e_ld += e2 - e1;
 						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
 						// columns at or behind k are padding
 						const uint32_t col0 = chunk0 * 32u;
 						const uint32_t left = k > col0 ? k - col0 : 0u;
-						if (dbg & 2u) {
-							b = min(b, v0[0] ^ v0[31] ^ v1[7]);
-						} else if (left >= 64 || (nchunks == 1 && left >= 32)) {
+						if (left >= 64 || (nchunks == 1 && left >= 32)) {
 							chunk_update<false>(v0, chunk0, 32, b, s2, bc);
 							if (nchunks > 1) chunk_update<false>(v1, chunk0 + 1, 32, b, s2, bc);
 						} else {
@@ -485,14 +537,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							if (nchunks > 1 && left > 32) chunk_update<true>(v1, chunk0 + 1, left - 32, b, s2, bc);
 						}
 						if (i) { best1 = b; second1 = s2; bchunk1 = bc; } else { best0 = b; second0 = s2; bchunk0 = bc; }
-						e_cmp += clock64() - e2;
 					} else {
 						__syncwarp();
 						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
 					}
 				}
 			}
-			long long e3 = clock64();
 			// merge the four column parts: parts 1..3 hand their state over through shared memory
 			uint32_t* mg = mg_state;
 			if (part > 0) {
@@ -505,7 +555,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				#pragma unroll
 				for (uint32_t i = 0; i < TC_MA; ++i) {
 					const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
-					if (i < tiles && p < n && ok && !dbg) {
+					if (i < tiles && p < n && ok) {
 						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
 						#pragma unroll
 						for (uint32_t o = 0; o < 3; ++o) {
@@ -528,10 +578,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				}
 			}
 			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
-			e_merge += clock64() - e3;
 		}
-		if ((dbg & 32u) && blockIdx.x == 3 && lane == 0 && (warp == 2 || warp == 7 || warp == 17))
-			printf("epi warp %u: total %lld  wait %lld  ld %lld  compute %lld  merge %lld\n", warp, clock64() - e_start, e_wait, e_ld, e_cmp, e_merge);
 	}
 
 	ptx::tc_fence_before();
@@ -593,7 +640,7 @@ TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, in
 	static const char* e_sup = "shape not supported by the tensor-core assignment";
 	static const char* e_map = "cuTensorMapEncodeTiled failed or is unavailable";
 	static const char* e_attr = "cannot set the shared-memory size of the tensor-core kernel";
-	if (!assign_tc_supported(s) || tp.d_pad != TC_KCHUNK || tm.d_pad != TC_KCHUNK) { if (err) *err = e_sup; return nullptr; }
+	if (!assign_tc_supported(s) || tp.d_pad != tm.d_pad || tp.d_pad % TC_KCHUNK != 0) { if (err) *err = e_sup; return nullptr; }
 	TcPlan* p = new (std::nothrow) TcPlan();
 	if (!p) return nullptr;
 	p->s = s; p->tp = tp; p->tm = tm;
@@ -629,13 +676,12 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
 	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
 	const float margin_coef = margin_scale * (40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
-	static const uint32_t dbg = getenv("BKM_TC_DEBUG") ? (uint32_t)atoi(getenv("BKM_TC_DEBUG")) : 0u;
-	uint32_t idesc = p->idesc;
-	if (dbg & 8u) idesc = (idesc & ~(0x3Fu << 17)) | ((64u >> 3) << 17);    // N = 64: half the tensor work per instruction
-	if (dbg & 16u) idesc = (idesc & ~(0x3Fu << 17)) | ((32u >> 3) << 17);   // N = 32
+	const uint32_t kchunks = p->tp.d_pad / TC_KCHUNK;
+	const uint32_t ksteps_last = (p->s.dim - (kchunks - 1) * TC_KCHUNK + 7) / 8;    // K steps of the last 32-dimension slice
+	const uint32_t idesc = p->idesc;
 	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
-		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, (p->s.dim + 7) / 8, idesc,
-		ctl, slot, flag_list, margin_coef, dbg);
+		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kchunks, ksteps_last, idesc,
+		ctl, slot, flag_list, margin_coef);
 	return cudaGetLastError();
 }
 

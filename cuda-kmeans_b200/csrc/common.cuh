@@ -43,10 +43,11 @@ __host__ __device__ __forceinline__ uint32_t round_up(uint32_t x, uint32_t m) { 
 __host__ __device__ __forceinline__ uint64_t round_up64(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
 // Row stride (floats) of the prepared means used by the CUDA-core assignment:
-// [ |c|^2, -2*c_0 ... -2*c_{d-1}, 0-padding ] rounded to a multiple of 4 floats.
+// [ t, c_0 ... c_{d-1}, 0-padding ] rounded to a multiple of 4 floats, where the additive term t
+// is 0 for a real mean and +inf for a padding row.
 __host__ __device__ __forceinline__ uint32_t simt_row_stride(uint32_t dim) { return round_up(dim + 1, 4); }
 
-// Rows of the prepared means: k rounded to a multiple of 4; padding rows have |c|^2 = +inf.
+// Rows of the prepared means: k rounded to a multiple of 4.
 __host__ __device__ __forceinline__ uint32_t simt_rows(uint32_t k) { return round_up(k, 4); }
 
 // Geometry of the tensor-core operands: K (dimension) padded to 32 floats (one 128-byte

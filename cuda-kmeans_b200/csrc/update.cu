@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 				}
 				s2 = fmaf(mean, mean, s2);
 				const float b = -2.0f * mean;
-				if (cprep) cprep[(size_t)c * rs + 1 + j] = b;
+				if (cprep) cprep[(size_t)c * rs + 1 + j] = mean;
 				if (b_hi) {
 					const float hi = tf32_rna(b);
 					const float lo = tf32_rna(b - hi);
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 			for (int off = 16; off > 0; off >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, off);
 			__syncwarp();
 			if (lane == 0) {
-				if (cprep) cprep[(size_t)c * rs] = s2;
+				if (cprep) cprep[(size_t)c * rs] = 0.0f;
 				if (cnorm) cnorm[c] = s2;
 				if (b_aug) {
 					const float hi = tf32_rna(s2);
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 				}
 			}
 		} else if (lane == 0) {
-			// padding rows can never win: their |c|^2 is +inf (the -2c part stays zero)
+			// padding rows can never win: their additive term is +inf (the coordinates stay zero)
 			if (cprep && c < srows) cprep[(size_t)c * rs] = INFINITY;
 			if (cnorm && c < k_pad) cnorm[c] = INFINITY;
 			if (b_aug && c < k_pad) {

@@ -11,7 +11,7 @@ def _variants(pkg, d):
     v = [pkg.ASSIGN_EXACT, pkg.ASSIGN_AUTO]
     if d <= 8:
         v.append(pkg.ASSIGN_SIMT)
-    if d <= 32:
+    if d <= 4096:
         v.append(pkg.ASSIGN_TC)
     return v
 
@@ -64,7 +64,7 @@ def test_tight_clusters_far_from_origin(pkg, torch_cuda, oracle_mod):
 
 def test_duplicate_means_pick_lowest_index(pkg, torch_cuda):
     rng = np.random.default_rng(9)
-    for d, variants in ((4, (1, 2, 3)), (32, (1, 3))):
+    for d, variants in ((4, (1, 2, 3)), (32, (1, 3)), (80, (1, 3))):
         n, k = 3000, 40
         centres = rng.random((k, d), dtype=np.float32)
         centres[20:] = centres[:20]          # every mean exists twice

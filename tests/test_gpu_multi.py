@@ -1,0 +1,90 @@
+"""GPU, 2 ranks (needs two devices): the sharded driver - contiguous point shards, per-iteration
+NCCL all-reduce of sums and sizes inside libbkm - against the single-GPU run and the oracle."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out_dir, name, n_total, iters):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load()
+    import importlib
+    wl = importlib.import_module("cuda_kmeans_b200.workloads")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        spec = dict(wl.CONFIGS[name])
+        k, d, lay = spec["k"], spec["dim"], spec["layout"]
+        begin, count = pkg.shard_range(n_total, world, rank)
+        rows = wl.generate_rows(spec["kind"], n_total, d, k, 5, spec.get("sigma", 0.05), spec.get("zipf"),
+                                begin=begin, count=count, chunk=4096)
+        first = wl.generate_rows(spec["kind"], n_total, d, k, 5, spec.get("sigma", 0.05), spec.get("zipf"),
+                                 begin=0, count=k, chunk=4096)
+        km = pkg.KMeans(layout=lay, device=rank)
+        km.initialize(d, k, count, iters, wl.to_layout(rows, lay), wl.to_layout(first, lay))
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(pkg.comm_unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        km.comm_init(uid.numpy().tobytes(), world, rank)
+        km.run()
+        np.save(os.path.join(out_dir, "means_%d.npy" % rank), km.getMeans())
+        np.save(os.path.join(out_dir, "asg_%d.npy" % rank), km.getAssignment())
+        np.save(os.path.join(out_dir, "sizes_%d.npy" % rank), km.getSizes())
+        km.cleanup()
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name,n_total,iters", [("c1", 50001, 4), ("c2", 40000, 3)])
+def test_two_ranks_match_single_gpu_and_oracle(tmp_path, pkg, torch_cuda, workloads, oracle_mod, name, n_total, iters):
+    if torch_cuda.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), name, n_total, iters), nprocs=world, join=True)
+    spec = dict(workloads.CONFIGS[name])
+    k, d, lay = spec["k"], spec["dim"], spec["layout"]
+    rows = workloads.generate_rows(spec["kind"], n_total, d, k, 5, spec.get("sigma", 0.05), spec.get("zipf"), chunk=4096)
+    data, means0 = workloads.to_layout(rows, lay), workloads.to_layout(rows[:k], lay)
+    m0, m1 = np.load(tmp_path / "means_0.npy"), np.load(tmp_path / "means_1.npy")
+    assert np.array_equal(m0, m1)                                 # identical means on every rank
+    assert np.array_equal(np.load(tmp_path / "sizes_0.npy"), np.load(tmp_path / "sizes_1.npy"))
+    asg = np.concatenate([np.load(tmp_path / "asg_0.npy"), np.load(tmp_path / "asg_1.npy")])
+    # single GPU, same data
+    km = pkg.KMeans(layout=lay)
+    km.initialize(d, k, n_total, iters, data, means0)
+    km.run()
+    single_means, single_asg = km.getMeans(), km.getAssignment()
+    km.cleanup()
+    from helpers import means_close
+    ok, err = means_close(m0, single_means)
+    assert ok, err
+    assert (asg != single_asg).mean() <= 1e-3
+    # the oracle
+    want_means, want_asg = oracle_mod.kmeans(data, means0, n_total, k, d, iters, lay, lay)
+    ok, err = means_close(m0, want_means)
+    assert ok, err
+    assert (asg != want_asg).mean() <= 1e-3
+    assert int(np.load(tmp_path / "sizes_0.npy").astype(np.int64).sum()) == n_total
