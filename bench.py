@@ -131,6 +131,43 @@ def physical_gpu_index(local_index):
     return local_index
 
 
+def device_rows(torch, workloads, spec, n_total, begin, count, seed, chunk=1 << 22):
+    """Rows [begin, begin+count) of a large workload generated on the GPU in chunks seeded by
+    (seed, chunk index), so that every rank count sees the same global data set.  Returns the flat
+    device tensor in the workload's layout and the first k rows (initial means) as a numpy array."""
+    k, dim, lay = spec["k"], spec["dim"], spec["layout"]
+    kind, sigma = spec["kind"], spec.get("sigma", 0.05)
+    out = torch.empty(count * dim, dtype=torch.float32, device="cuda")
+    view = out.view(count, dim) if lay == 0 else out.view(dim, count)
+    centres = torch.from_numpy(workloads.mixture_centres(k, dim, seed)).cuda() if kind == "mixture" else None
+    weights = torch.from_numpy(workloads.mixture_weights(k, spec.get("zipf"))).float().cuda() if kind == "mixture" else None
+    gen = torch.Generator(device="cuda")
+
+    def block(c):
+        c0, c1 = c * chunk, min(n_total, (c + 1) * chunk)
+        gen.manual_seed(seed * 1000003 + c)
+        if kind == "uniform":
+            return torch.rand((c1 - c0, dim), generator=gen, device="cuda")
+        if kind == "mixture":
+            which = torch.multinomial(weights, c1 - c0, replacement=True, generator=gen)
+            return centres[which] + sigma * torch.randn((c1 - c0, dim), generator=gen, device="cuda")
+        x = torch.randn((c1 - c0, dim), generator=gen, device="cuda")
+        return x / x.norm(dim=1, keepdim=True)
+
+    for c in range(begin // chunk, (begin + count - 1) // chunk + 1):
+        c0 = c * chunk
+        rows = block(c)
+        lo, hi = max(begin, c0), min(begin + count, c0 + rows.shape[0])
+        part = rows[lo - c0:hi - c0]
+        if lay == 0:
+            view[lo - begin:hi - begin] = part
+        else:
+            view[:, lo - begin:hi - begin] = part.t()
+        del rows, part
+    first = block(0)[:k].cpu().numpy()
+    return out, first
+
+
 def cpu_reference_leg(workloads, spec, seed, sample_n, steps, warmup):
     """Times the reference's serial CPU k-means, one iteration per step, on the first
     `sample_n` points of the workload (same k, dim, layouts, initial means)."""
@@ -211,14 +248,20 @@ def main():
 
     n_total = spec["n"] * world if scaling == "weak" else spec["n"]
     begin, count = pkg.shard_range(n_total, world, rank)
-    rows = workloads.generate_rows(spec["kind"], n_total, dim, k, args.seed, spec.get("sigma", 0.05),
-                                   spec.get("zipf"), begin=begin, count=count)
-    first = rows[:k] if begin == 0 else workloads.generate_rows(
-        spec["kind"], n_total, dim, k, args.seed, spec.get("sigma", 0.05), spec.get("zipf"), begin=0, count=k)
-    host_points = torch.from_numpy(workloads.to_layout(rows, lay)).pin_memory()
+    big = count * dim * 4 > (2 << 30)          # beyond 2 GiB the shard is generated on the device
+    if big:
+        dev_points, first = device_rows(torch, workloads, spec, n_total, begin, count, args.seed)
+        host_points = None
+        args.no_e2e = True                        # no host copy of a shard this large is kept
+    else:
+        rows = workloads.generate_rows(spec["kind"], n_total, dim, k, args.seed, spec.get("sigma", 0.05),
+                                       spec.get("zipf"), begin=begin, count=count)
+        first = rows[:k] if begin == 0 else workloads.generate_rows(
+            spec["kind"], n_total, dim, k, args.seed, spec.get("sigma", 0.05), spec.get("zipf"), begin=0, count=k)
+        host_points = torch.from_numpy(workloads.to_layout(rows, lay)).pin_memory()
+        del rows
+        dev_points = host_points.to("cuda", non_blocking=False)
     host_means = torch.from_numpy(workloads.to_layout(first, laym)).pin_memory()
-    del rows
-    dev_points = host_points.to("cuda", non_blocking=False)
     dev_means = host_means.to("cuda")
 
     va = {"auto": 0, "exact": 1, "simt": 2, "tc": 3}[args.assign]
@@ -263,11 +306,11 @@ def main():
 
     # ---------------- end to end through the host-buffer calls ----------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and host_points is not None:
         e2e_steps = max(3, min(args.steps, 20))
         km2 = pkg.KMeans(layout=lay, layout_means=laym, device=local_rank, variant_assign=va, variant_update=vu)
         km2.set_stream(stream.cuda_stream)
-        hp, hm = host_points.numpy(), host_means.numpy()
+        hp, hm = host_points.numpy(), host_means.numpy()   # (host_points exists: large shards skip this leg)
         out_means = torch.empty(k * dim, dtype=torch.float32).pin_memory()
         out_asg = torch.empty(count, dtype=torch.int32).pin_memory()
         km2.initialize(dim, k, count, 1, hp, hm)
@@ -339,7 +382,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sample_n = min(spec["n"], 1 << 16)
+        sample_n = min(spec["n"], max(1 << 12, (1 << 26) // (k * max(1, dim // 32 + (dim % 32 > 0)))))
         cpu_baseline, _ = cpu_reference_leg(workloads, spec, args.seed, sample_n, 1, 0)
 
     if rank == 0:

@@ -280,9 +280,17 @@ struct bkm_handle_s {
 	bool ev_made = false;
 	uint32_t ev_count = 0;
 	uint32_t launches_per_iter = 0;
+	// CUDA graph of two iterations (launch-bound problem sizes)
+	int use_graph = 2;                 // 0 = never, 1 = always (single GPU), 2 = by problem size
+	cudaGraphExec_t graph_exec = nullptr;
+	int graph_cur = 0, graph_slot = 0;
+	cudaStream_t graph_stream = nullptr;
+	cudaEvent_t ev_run[2] = {};
 };
 
 extern "C" {
+
+static void drop_graph(bkm_handle_t h);
 
 const char* bkm_last_error(void) { return g_error.c_str(); }
 
@@ -466,6 +474,9 @@ int bkm_create(const bkm_config_t* cfg, bkm_handle_t* out)
 			if ((e = cudaEventCreate(&h->ev[i][j])) != cudaSuccess)
 				return bail(fail(BKM_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e)));
 	h->ev_made = true;
+	for (int j = 0; j < 2; ++j)
+		if ((e = cudaEventCreate(&h->ev_run[j])) != cudaSuccess)
+			return bail(fail(BKM_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e)));
 	*out = h;
 	return BKM_OK;
 }
@@ -475,11 +486,13 @@ int bkm_destroy(bkm_handle_t h)
 	if (!h) return BKM_OK;
 	cudaSetDevice(h->cfg.device);
 	if (h->stream) cudaStreamSynchronize(h->stream);
+	drop_graph(h);
 	if (h->comm && nccl()->ok) nccl()->CommDestroy(h->comm);
 	if (h->plan) bkm::tc_plan_destroy(h->plan);
 	for (int i = 0; i < bkm_handle_s::EV_RING; ++i)
 		for (int j = 0; j < bkm_handle_s::EV_PER; ++j)
 			if (h->ev[i][j]) cudaEventDestroy(h->ev[i][j]);
+	for (int j = 0; j < 2; ++j) if (h->ev_run[j]) cudaEventDestroy(h->ev_run[j]);
 	cudaFree(h->d_points_owned);
 	cudaFree(h->d_means[0]);
 	cudaFree(h->d_means[1]);
@@ -509,6 +522,12 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value)
 		return BKM_OK;
 	}
 	if (!strcmp(name, "phase_timing")) { h->phase_timing = value != 0.0; return BKM_OK; }
+	if (!strcmp(name, "use_graph")) {
+		if (value != 0.0 && value != 1.0 && value != 2.0) return fail(BKM_ERR_INVALID, "use_graph is 0 (never), 1 (always) or 2 (by size)");
+		h->use_graph = (int)value;
+		drop_graph(h);
+		return BKM_OK;
+	}
 	return fail(BKM_ERR_INVALID, "unknown option '%s'", name);
 }
 
@@ -518,6 +537,7 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 	const size_t kd = (size_t)s.k * s.dim;
 	cudaStream_t st = h->stream;
 	h->cur = 0; h->slot = 0; h->iters_done = 0; h->ev_count = 0;
+	drop_graph(h);
 	CUDA_TRY(cudaMemcpyAsync(h->d_means[0], means, kd * sizeof(float), kind, st));
 	CUDA_TRY(cudaMemsetAsync(h->d_ws, 0, (size_t)(reinterpret_cast<char*>(h->ws.flag_list) - h->d_ws), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_asg, 0, s.n * sizeof(uint32_t), st));
@@ -575,45 +595,97 @@ int bkm_set_means(bkm_handle_t h, const float* host_means)
 	return BKM_OK;
 }
 
+// Enqueues one iteration on the handle's stream; `ev` (6 events) brackets the phases when given.
+static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
+{
+	const bkm::Shape& s = h->shape;
+	cudaStream_t st = h->stream;
+	const size_t kd = (size_t)s.k * s.dim;
+	const int next = h->cur ^ 1;
+	if (ev) CUDA_TRY(cudaEventRecord(ev[0], st));
+	int rc = enqueue_assign(h->assign_variant, h->d_points, h->d_means[h->cur], h->d_asg, s, h->ws, h->slot,
+		h->plan, h->margin_scale, h->sm_count, st, ev ? ev[1] : nullptr);
+	if (rc) return rc;
+	if (ev) CUDA_TRY(cudaEventRecord(ev[2], st));
+	bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, h->ws.replicas, s, h->update_variant, h->ws.ctl, h->sm_count, st);
+	if (ev) CUDA_TRY(cudaEventRecord(ev[3], st));
+	if (h->comm) {
+		bkm::launch_merge_replicas(h->ws.acc, h->ws.counts, h->ws.replicas, s, st);
+		Nccl* nc = nccl();
+		NCCL_TRY(nc->GroupStart());
+		NCCL_TRY(nc->AllReduce(h->ws.acc, h->ws.acc, kd, NCCL_FLOAT32, NCCL_SUM, h->comm, st));
+		NCCL_TRY(nc->AllReduce(h->ws.counts, h->ws.counts, s.k, NCCL_UINT32, NCCL_SUM, h->comm, st));
+		NCCL_TRY(nc->GroupEnd());
+	}
+	if (ev) CUDA_TRY(cudaEventRecord(ev[4], st));
+	bkm::launch_finalize(h->ws.acc, h->ws.counts, h->comm ? 1u : h->ws.replicas, h->d_means[next], h->d_sizes, s,
+		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st);
+	if (ev) CUDA_TRY(cudaEventRecord(ev[5], st));
+	CUDA_TRY(cudaGetLastError());
+	h->cur = next;
+	h->slot ^= 1;
+	++h->iters_done;
+	return BKM_OK;
+}
+
+static void drop_graph(bkm_handle_t h)
+{
+	if (h->graph_exec) { cudaGraphExecDestroy(h->graph_exec); h->graph_exec = nullptr; }
+}
+
+// Small problems are bound by launch latency: two iterations (after which the double-buffered
+// means and the cmax2 slot are back where they started) are captured once into a CUDA graph and
+// replayed.  The graph is rebuilt when the starting buffers differ from the captured ones.
+static bool graph_wanted(bkm_handle_t h, uint32_t iters)
+{
+	if (h->comm || iters < 4) return false;
+	if (h->use_graph == 0) return false;
+	if (h->use_graph == 1) return true;
+	return (double)h->shape.n * h->shape.k * h->shape.dim <= 1.0e8;     // auto: launch-bound sizes only
+}
+
 int bkm_run_async(bkm_handle_t h, uint32_t iters)
 {
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "run before initialize");
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
-	const bkm::Shape& s = h->shape;
 	cudaStream_t st = h->stream;
-	const size_t kd = (size_t)s.k * s.dim;
 	h->ev_count = 0;
-	for (uint32_t it = 0; it < iters; ++it) {
-		const int next = h->cur ^ 1;
-		const bool timed = h->phase_timing && (iters - it) <= (uint32_t)bkm_handle_s::EV_RING;
-		cudaEvent_t* ev = timed ? h->ev[h->ev_count] : nullptr;
-		if (timed) CUDA_TRY(cudaEventRecord(ev[0], st));
-		int rc = enqueue_assign(h->assign_variant, h->d_points, h->d_means[h->cur], h->d_asg, s, h->ws, h->slot,
-			h->plan, h->margin_scale, h->sm_count, st, timed ? ev[1] : nullptr);
-		if (rc) return rc;
-		if (timed) CUDA_TRY(cudaEventRecord(ev[2], st));
-		bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, h->ws.replicas, s, h->update_variant, h->ws.ctl, h->sm_count, st);
-		if (timed) CUDA_TRY(cudaEventRecord(ev[3], st));
-		if (h->comm) {
-			bkm::launch_merge_replicas(h->ws.acc, h->ws.counts, h->ws.replicas, s, st);
-			Nccl* nc = nccl();
-			NCCL_TRY(nc->GroupStart());
-			NCCL_TRY(nc->AllReduce(h->ws.acc, h->ws.acc, kd, NCCL_FLOAT32, NCCL_SUM, h->comm, st));
-			NCCL_TRY(nc->AllReduce(h->ws.counts, h->ws.counts, s.k, NCCL_UINT32, NCCL_SUM, h->comm, st));
-			NCCL_TRY(nc->GroupEnd());
-		}
-		if (timed) CUDA_TRY(cudaEventRecord(ev[4], st));
-		bkm::launch_finalize(h->ws.acc, h->ws.counts, h->comm ? 1u : h->ws.replicas, h->d_means[next], h->d_sizes, s,
-			h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
-			h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st);
-		if (timed) { CUDA_TRY(cudaEventRecord(ev[5], st)); ++h->ev_count; }
-		CUDA_TRY(cudaGetLastError());
-		h->cur = next;
-		h->slot ^= 1;
-		++h->iters_done;
-	}
 	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + 2u;
+	uint32_t it = 0;
+	if (graph_wanted(h, iters)) {
+		if (!h->graph_exec || h->graph_cur != h->cur || h->graph_slot != h->slot || h->graph_stream != st) {
+			drop_graph(h);
+			const int cur0 = h->cur, slot0 = h->slot;
+			const uint64_t done0 = h->iters_done;
+			cudaGraph_t graph = nullptr;
+			CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
+			int rc = enqueue_iteration(h, nullptr);
+			if (rc == BKM_OK) rc = enqueue_iteration(h, nullptr);
+			cudaError_t e = cudaStreamEndCapture(st, &graph);
+			h->cur = cur0; h->slot = slot0; h->iters_done = done0;     // capturing ran nothing
+			if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+			if (e != cudaSuccess) return fail(BKM_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+			e = cudaGraphInstantiate(&h->graph_exec, graph, 0);
+			cudaGraphDestroy(graph);
+			if (e != cudaSuccess) { h->graph_exec = nullptr; return fail(BKM_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+			h->graph_cur = cur0; h->graph_slot = slot0; h->graph_stream = st;
+		}
+		// the last few iterations run as plain launches so that their phases can be timed
+		const uint32_t tail = h->phase_timing ? 2u : 0u;
+		if (h->phase_timing) CUDA_TRY(cudaEventRecord(h->ev_run[0], st));
+		for (; it + 2 + tail <= iters; it += 2) {
+			CUDA_TRY(cudaGraphLaunch(h->graph_exec, st));
+			h->iters_done += 2;
+		}
+	}
+	for (; it < iters; ++it) {
+		const bool timed = h->phase_timing && (iters - it) <= (uint32_t)bkm_handle_s::EV_RING;
+		int rc = enqueue_iteration(h, timed ? h->ev[h->ev_count] : nullptr);
+		if (rc) return rc;
+		if (timed) ++h->ev_count;
+	}
 	return BKM_OK;
 }
 

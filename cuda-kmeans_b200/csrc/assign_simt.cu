@@ -66,40 +66,54 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
 }
 
 
-// The same arithmetic for a list of queued points: one block per point, one mean per thread at a
-// time, so that a short list still fills the machine.  Each distance is still summed in
-// dimension order by a single thread.  AoS means are staged through a shared tile (32 dimensions
-// of 256 means at a time, loaded along the dimensions) so that the global loads stay coalesced;
-// SoA means are read directly (consecutive threads = consecutive means).
+// The same arithmetic for a list of queued points: one block per LIST_PB points, one mean per
+// thread at a time, so that a short list still fills the machine and every mean that is
+// fetched serves LIST_PB points.  Each distance is still summed in dimension order by a single
+// thread.  AoS means are staged through a shared tile (32 dimensions of 256 means at a time,
+// loaded along the dimensions) so that the global loads stay coalesced; SoA means are read
+// directly (consecutive threads = consecutive means).
 constexpr int LIST_THREADS = 256;
+constexpr int LIST_PB = 4;
 
 template<bool SOA, bool SOAM>
 __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const float* __restrict__ pts,
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
 	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
 {
-	extern __shared__ float sx[];                       // the point (d floats), then the means tile
-	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + ((d + 3) & ~3u));
-	__shared__ float sbest[LIST_THREADS / 32];
-	__shared__ uint32_t sidx[LIST_THREADS / 32];
+	extern __shared__ float sx[];                       // LIST_PB points (dpad floats each), then the means tile
+	const uint32_t dpad = (d + 3) & ~3u;
+	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + (size_t)LIST_PB * dpad);
+	__shared__ float sbest[LIST_PB][LIST_THREADS / 32];
+	__shared__ uint32_t sidx[LIST_PB][LIST_THREADS / 32];
 	const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
 	uint64_t total = *list_count;
 	if (total > n) total = n;
-	for (uint64_t w = blockIdx.x; w < total; w += gridDim.x) {
-		const uint64_t i = list[w];
+	for (uint64_t w0 = (uint64_t)blockIdx.x * LIST_PB; w0 < total; w0 += (uint64_t)gridDim.x * LIST_PB) {
+		const uint32_t np = total - w0 < LIST_PB ? (uint32_t)(total - w0) : LIST_PB;
 		__syncthreads();
-		for (uint32_t j = tid; j < d; j += LIST_THREADS) sx[j] = pts[at<SOA>(i, j, n, d)];
+		for (uint32_t p = 0; p < LIST_PB; ++p) {
+			const uint64_t i = list[w0 + (p < np ? p : 0)];      // unused slots repeat the first point
+			for (uint32_t j = tid; j < d; j += LIST_THREADS) sx[p * dpad + j] = pts[at<SOA>(i, j, n, d)];
+		}
 		__syncthreads();
-		float best = INFINITY;
-		uint32_t bidx = 0xffffffffu;
+		float best[LIST_PB];
+		uint32_t bidx[LIST_PB];
+		#pragma unroll
+		for (int p = 0; p < LIST_PB; ++p) { best[p] = INFINITY; bidx[p] = 0xffffffffu; }
 		for (uint32_t m0 = 0; m0 < k; m0 += LIST_THREADS) {
 			const uint32_t m = m0 + tid;
-			float sum = 0.0f;
+			float sum[LIST_PB];
+			#pragma unroll
+			for (int p = 0; p < LIST_PB; ++p) sum[p] = 0.0f;
 			if (SOAM) {
 				if (m < k) {
 					for (uint32_t j = 0; j < d; ++j) {
-						const float diff = __fsub_rn(sx[j], means[(size_t)j * k + m]);
-						sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+						const float c = means[(size_t)j * k + m];
+						#pragma unroll
+						for (int p = 0; p < LIST_PB; ++p) {
+							const float diff = __fsub_rn(sx[p * dpad + j], c);
+							sum[p] = __fadd_rn(sum[p], __fmul_rn(diff, diff));
+						}
 					}
 				}
 			} else {
@@ -113,31 +127,43 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 					__syncthreads();
 					const uint32_t jn = d - j0 < 32 ? d - j0 : 32;
 					for (uint32_t jj = 0; jj < jn; ++jj) {
-						const float diff = __fsub_rn(sx[j0 + jj], tile[tid][jj]);
-						sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+						const float c = tile[tid][jj];
+						#pragma unroll
+						for (int p = 0; p < LIST_PB; ++p) {
+							const float diff = __fsub_rn(sx[p * dpad + j0 + jj], c);
+							sum[p] = __fadd_rn(sum[p], __fmul_rn(diff, diff));
+						}
 					}
 				}
 			}
 			if (m < k) {
-				const float dist = __fsqrt_rn(sum);
-				if (bidx == 0xffffffffu || dist < best) { best = dist; bidx = m; }
+				#pragma unroll
+				for (int p = 0; p < LIST_PB; ++p) {
+					const float dist = __fsqrt_rn(sum[p]);
+					if (bidx[p] == 0xffffffffu || dist < best[p]) { best[p] = dist; bidx[p] = m; }
+				}
 			}
 		}
 		#pragma unroll
-		for (int off = 16; off > 0; off >>= 1) {
-			const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-			const uint32_t oi = __shfl_xor_sync(0xffffffffu, bidx, off);
-			if (oi != 0xffffffffu && (bidx == 0xffffffffu || ob < best || (ob == best && oi < bidx))) { best = ob; bidx = oi; }
-		}
-		if (lane == 0) { sbest[warp] = best; sidx[warp] = bidx; }
-		__syncthreads();
-		if (tid == 0) {
-			for (uint32_t v = 1; v < LIST_THREADS / 32; ++v) {
-				const float ob = sbest[v];
-				const uint32_t oi = sidx[v];
-				if (oi != 0xffffffffu && (bidx == 0xffffffffu || ob < best || (ob == best && oi < bidx))) { best = ob; bidx = oi; }
+		for (int p = 0; p < LIST_PB; ++p) {
+			#pragma unroll
+			for (int off = 16; off > 0; off >>= 1) {
+				const float ob = __shfl_xor_sync(0xffffffffu, best[p], off);
+				const uint32_t oi = __shfl_xor_sync(0xffffffffu, bidx[p], off);
+				if (oi != 0xffffffffu && (bidx[p] == 0xffffffffu || ob < best[p] || (ob == best[p] && oi < bidx[p]))) { best[p] = ob; bidx[p] = oi; }
 			}
-			asg[i] = bidx;
+			if (lane == 0) { sbest[p][warp] = best[p]; sidx[p][warp] = bidx[p]; }
+		}
+		__syncthreads();
+		if (tid < np) {
+			float b = sbest[tid][0];
+			uint32_t bi = sidx[tid][0];
+			for (uint32_t v = 1; v < LIST_THREADS / 32; ++v) {
+				const float ob = sbest[tid][v];
+				const uint32_t oi = sidx[tid][v];
+				if (oi != 0xffffffffu && (bi == 0xffffffffu || ob < b || (ob == b && oi < bi))) { b = ob; bi = oi; }
+			}
+			asg[list[w0 + tid]] = bi;
 		}
 	}
 }
@@ -145,8 +171,8 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
 	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
 {
-	if (list != nullptr && (size_t)s.dim * sizeof(float) <= 120 * 1024) {
-		const size_t lsmem = (size_t)((s.dim + 3) & ~3u) * sizeof(float) + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
+	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
+		const size_t lsmem = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float) + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
 		const uint32_t lgrid = (uint32_t)sm_count * 8;
 #define BKM_LAUNCH_LIST(SOA, SOAM) do { \
 		auto kern = assign_exact_list_kernel<SOA, SOAM>; \

@@ -164,8 +164,10 @@ int bkm_destroy(bkm_handle_t h);
  * default stream, the one the reference's drivers use (headers/cuda.hpp:70-88). */
 int bkm_set_stream(bkm_handle_t h, void* stream);
 
-/* Tunables: "margin_scale" (float multiplier on the near-tie band, default 1),
- * "blocks_per_sm_update" etc.  Unknown names fail with BKM_ERR_INVALID. */
+/* Tunables: "margin_scale" (multiplier on the near-tie band, default 1), "phase_timing"
+ * (0/1: record per-phase CUDA events, default 1), "use_graph" (0 never, 1 always, 2 = default:
+ * replay a CUDA graph of two iterations when the problem is small enough to be bound by launch
+ * latency; single GPU only).  Unknown names fail with BKM_ERR_INVALID. */
 int bkm_set_option(bkm_handle_t h, const char* name, double value);
 
 /* initialize(): copies points and initial means from HOST memory, runs the one-off
