@@ -148,6 +148,7 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 	w.tm.b_lo = reinterpret_cast<float*>(take(plane));
 	w.tm.cnorm = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * sizeof(float)));
 	w.tm.b_aug = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * 8 * sizeof(float)));
+	w.tm.center = reinterpret_cast<float*>(take((size_t)w.tm.d_pad * sizeof(float)));
 	w.flag_list = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
 	w.asg_scratch = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
 	if (with_tc_points) {
@@ -197,8 +198,8 @@ int resolve_update(int variant, const bkm::Shape& s, int device, int* out)
 {
 	switch (variant) {
 	case BKM_UPDATE_AUTO:
-		// rows of at least 16 floats and enough of them that the L2 reductions rarely collide
-		if (s.dim >= 16 && (uint64_t)s.k * s.dim >= 8192) *out = BKM_UPDATE_ROWS;
+		// rows of at least 16 floats: one coalesced L2 reduction per point beats shared-memory atomics
+		if (s.dim >= 16) *out = BKM_UPDATE_ROWS;
 		else *out = bkm::update_shared_fits(s, device) ? BKM_UPDATE_SHARED : BKM_UPDATE_GLOBAL;
 		return BKM_OK;
 	case BKM_UPDATE_ROWS:
@@ -349,8 +350,9 @@ static int stateless_assign(const float* points, const float* means, uint32_t* a
 		bkm::launch_prepare_means(means, s, w.cprep, nullptr, w.ctl, 0, st);
 	} else if (v == BKM_ASSIGN_TC) {
 		CUDA_TRY(cudaMemsetAsync(w.tm.b_hi, 0, w.tm_bytes, st));
+		CUDA_TRY(bkm::launch_compute_center(points, s, w.tm.center, st));
 		bkm::launch_prepare_means(means, s, nullptr, &w.tm, w.ctl, 0, st);
-		CUDA_TRY(bkm::launch_split_points(points, s, w.tp, w.ctl, st));
+		CUDA_TRY(bkm::launch_split_points(points, s, w.tp, w.tm.center, w.ctl, st));
 		const char* err = nullptr;
 		plan = bkm::tc_plan_create(s, w.tp, w.tm, device, &err);
 		if (!plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
@@ -543,7 +545,8 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 	CUDA_TRY(cudaMemsetAsync(h->d_asg, 0, s.n * sizeof(uint32_t), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_sizes, 0, (size_t)s.k * sizeof(uint32_t), st));
 	if (h->assign_variant == BKM_ASSIGN_TC) {
-		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.ctl, st));
+		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
+		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, st));
 		if (h->plan) { bkm::tc_plan_destroy(h->plan); h->plan = nullptr; }
 		const char* err = nullptr;
 		h->plan = bkm::tc_plan_create(s, h->ws.tp, h->ws.tm, h->cfg.device, &err);

@@ -95,7 +95,7 @@ __device__ __forceinline__ float to_tf32(float x)
 template<bool SOA>
 __global__ void __launch_bounds__(256) split_points_kernel(const float* __restrict__ pts, float* __restrict__ a_hi,
 	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t n_pad, uint32_t d, uint32_t d_pad,
-	Control* __restrict__ ctl)
+	const float* __restrict__ center, Control* __restrict__ ctl)
 {
 	float local_max = 0.0f;
 	__shared__ float tile[32][33];
@@ -110,11 +110,11 @@ __global__ void __launch_bounds__(256) split_points_kernel(const float* __restri
 				if (SOA) {
 					const uint64_t p = p0 + tx;
 					const uint32_t j = c0 + rr;
-					tile[tx][rr] = (p < n && j < d) ? pts[(size_t)j * n + p] : 0.0f;     // tile[point][dim]
+					tile[tx][rr] = (p < n && j < d) ? pts[(size_t)j * n + p] - center[j] : 0.0f;     // tile[point][dim]
 				} else {
 					const uint64_t p = p0 + rr;
 					const uint32_t j = c0 + tx;
-					tile[rr][tx] = (p < n && j < d) ? pts[(size_t)p * d + j] : 0.0f;
+					tile[rr][tx] = (p < n && j < d) ? pts[(size_t)p * d + j] - center[j] : 0.0f;
 				}
 			}
 			__syncthreads();
@@ -143,12 +143,42 @@ __global__ void __launch_bounds__(256) split_points_kernel(const float* __restri
 	if (tx == 0) atomicMax(reinterpret_cast<int*>(&ctl->xmax2), __float_as_int(local_max));
 }
 
-cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, Control* ctl, cudaStream_t stream)
+// One block per dimension: mean of that coordinate over at most 65536 evenly spaced points.
+template<bool SOA>
+__global__ void __launch_bounds__(256) compute_center_kernel(const float* __restrict__ pts, float* __restrict__ center,
+	uint64_t n, uint32_t d)
+{
+	__shared__ float part[256];
+	const uint32_t j = blockIdx.x;
+	const uint64_t samples = n < 65536 ? n : 65536;
+	const uint64_t stride = n / samples;
+	float sum = 0.0f;
+	for (uint64_t t = threadIdx.x; t < samples; t += 256) {
+		const uint64_t i = t * stride;
+		sum += SOA ? pts[(size_t)j * n + i] : pts[(size_t)i * d + j];
+	}
+	part[threadIdx.x] = sum;
+	__syncthreads();
+	for (uint32_t w = 128; w > 0; w >>= 1) {
+		if (threadIdx.x < w) part[threadIdx.x] += part[threadIdx.x + w];
+		__syncthreads();
+	}
+	if (threadIdx.x == 0) center[j] = part[0] / (float)samples;
+}
+
+cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream)
+{
+	if (s.soa) compute_center_kernel<true><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim);
+	else compute_center_kernel<false><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim);
+	return cudaGetLastError();
+}
+
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream)
 {
 	const uint64_t groups = tp.n_pad / 32;
 	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148 * 16);
-	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, ctl);
-	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, ctl);
+	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl);
+	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl);
 	return cudaGetLastError();
 }
 
@@ -280,17 +310,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		ptx::tmem_relinquish();
 	}
 	// Offset constant: every value |c|^2 - 2 x.c lies in [-X2, X2 + 2*C2] (X2, C2 = largest |x|^2,
-	// |c|^2); with P a power of two >= four times that span, value + P + X2 + P/1024 stays
-	// inside [P, 2P): one exponent for all, with head-room for the rounding of the pass.
+	// |c|^2 after centring), an interval of width 2*(X2+C2); with P a power of two >= 1.25 times
+	// that width, value + P + X2 + P/32 stays inside [P, 2P) with P/32 of head-room on both
+	// sides for the rounding of the pass: one exponent for all values.
 	const float x2max = ctl->xmax2, c2max = ctl->cmax2[slot];
 	float pow2 = 1.0f;
 	{
-		const float span = 4.0f * (2.0f * (x2max + c2max)) + 1.0e-30f;
+		const float span = 1.25f * (2.0f * (x2max + c2max)) + 1.0e-30f;
 		int e;
 		frexpf(span, &e);                       // span = m * 2^e, m in [0.5, 1)
 		pow2 = ldexpf(1.0f, e);                 // >= span
 	}
-	const float offset_c = pow2 + x2max + pow2 * (1.0f / 1024.0f);
+	const float offset_c = pow2 + x2max + pow2 * (1.0f / 32.0f);
 	{
 		// the constant A operand of the extra K step: columns 0 and 1 are one (they meet the high
 		// and the low part of |c|^2), columns 2 and 3 hold the offset constant as tf32 hi/lo
@@ -675,7 +706,7 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
 	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
-	const float margin_coef = margin_scale * (40.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
+	const float margin_coef = margin_scale * (48.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
 	const uint32_t kchunks = p->tp.d_pad / TC_KCHUNK;
 	const uint32_t ksteps_last = (p->s.dim - (kchunks - 1) * TC_KCHUNK + 7) / 8;    // K steps of the last 32-dimension slice
 	const uint32_t idesc = p->idesc;

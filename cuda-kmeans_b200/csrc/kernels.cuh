@@ -20,6 +20,8 @@ struct TcMeans {
 	float* cnorm;    // [k_pad] |mean|^2, +inf for padding rows
 	float* b_aug;    // [k_pad x 8] one K step (aug_offset layout): columns 0,1 = tf32 (hi, lo) of |mean|^2,
 	                 // columns 2,3 = 1 (they meet the kernel's offset constant), rest 0; padding rows 0,0,1,1
+	float* center;   // [d_pad] vector subtracted from points and means alike before the split (distances do
+	                 // not change; the norms, and with them the cancellation of the GEMM form, shrink)
 	uint32_t k_pad;  // k rounded up to the centroid tile
 	uint32_t d_pad;  // dim rounded up to TC_KCHUNK
 };
@@ -69,7 +71,10 @@ cudaError_t launch_assign_simt(const float* pts, const float* cprep, uint32_t* a
 bool assign_tc_supported(const Shape& s);
 uint32_t tc_kpad(uint32_t k);
 // One-off split of the points into tf32 hi/lo K-major planes + |x|^2.
-cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, Control* ctl, cudaStream_t stream);
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream);
+// center[j] = mean of dimension j over a strided sample of the points (any vector would do; the
+// sample mean keeps the shifted norms small).
+cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream);
 // Opaque per-handle state (tensor maps).  Created once the operand buffers exist.
 struct TcPlan;
 TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err);

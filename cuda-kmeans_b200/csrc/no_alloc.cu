@@ -75,7 +75,7 @@ extern "C" int bkm_update_noalloc_f32(const float* points, const uint32_t* assig
 	e = cudaMemsetAsync(base, 0, (NOALLOC_HEADER_WORDS + (size_t)replicas * stride) * sizeof(uint32_t), st);
 	if (e != cudaSuccess) return bkm_internal_fail(BKM_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
 	int variant = BKM_UPDATE_GLOBAL;
-	if (dim >= 16 && (uint64_t)k * dim >= 8192) variant = BKM_UPDATE_ROWS;
+	if (dim >= 16) variant = BKM_UPDATE_ROWS;
 	else if (bkm::update_shared_fits(s, device)) variant = BKM_UPDATE_SHARED;
 	bkm::launch_update(points, assignment, acc, counts, replicas, s, variant, ctl, sm_count, st);
 	bkm::launch_finalize(acc, counts, replicas, means, sizes, s, nullptr, nullptr, ctl, 1, st);

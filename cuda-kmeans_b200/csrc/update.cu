@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 	uint32_t k, uint32_t d, int soa_means,
 	float* __restrict__ cprep, uint32_t rs, uint32_t srows,
 	float* __restrict__ b_hi, float* __restrict__ b_lo, float* __restrict__ cnorm, float* __restrict__ b_aug,
-	uint32_t k_pad, uint32_t d_pad, Control* __restrict__ ctl, int slot)
+	const float* __restrict__ center, uint32_t k_pad, uint32_t d_pad, Control* __restrict__ ctl, int slot)
 {
 	const uint32_t lane = threadIdx.x & 31u;
 	const uint32_t wpb = blockDim.x >> 5;
@@ -81,8 +81,10 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 				} else {
 					mean = means_in[mi];
 				}
-				s2 = fmaf(mean, mean, s2);
-				const float b = -2.0f * mean;
+				// the tensor-core operands and the norms use the mean relative to the common centre
+				const float shifted = center ? mean - center[j] : mean;
+				s2 = fmaf(shifted, shifted, s2);
+				const float b = -2.0f * shifted;
 				if (cprep) cprep[(size_t)c * rs + 1 + j] = mean;
 				if (b_hi) {
 					const float hi = tf32_rna(b);
@@ -144,13 +146,14 @@ static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t repl
 	float* bl = tc ? tc->b_lo : nullptr;
 	float* cn = tc ? tc->cnorm : nullptr;
 	float* ba = tc ? tc->b_aug : nullptr;
+	const float* ce = tc ? tc->center : nullptr;
 	uint32_t kp = tc ? tc->k_pad : 0, dp = tc ? tc->d_pad : 0;
 	if (finalize)
 		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, means_out, sizes_out,
-			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, kp, dp, ctl, slot);
+			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, ce, kp, dp, ctl, slot);
 	else
 		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, means_out, sizes_out,
-			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, kp, dp, ctl, slot);
+			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, ce, kp, dp, ctl, slot);
 }
 
 void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,
