@@ -40,6 +40,17 @@
 #include <cstdlib>
 #include <new>
 
+// Optional stage timing for development builds (-DBKM_TC_TIMING): one CTA prints how its MMA warp
+// and three of its epilogue warps spent their cycles.
+#ifdef BKM_TC_TIMING
+#include <cstdio>
+#define TC_T(var) const long long var = clock64()
+#define TC_ACC(sum, from, to) sum += (to) - (from)
+#else
+#define TC_T(var)
+#define TC_ACC(sum, from, to)
+#endif
+
 namespace bkm {
 
 constexpr uint32_t TC_MA = 2;            // point tiles per block (= TMEM accumulators)
@@ -125,8 +136,10 @@ __global__ void __launch_bounds__(256) split_points_kernel(const float* __restri
 				const float hi = to_tf32(x);
 				const float lo = to_tf32(x - hi);
 				const size_t o = (size_t)(p0 + rr) * d_pad + c0 + tx;
-				a_hi[o] = hi;
-				a_lo[o] = lo;
+				if (c0 + tx < d_pad) {          // rows are shorter than the 32-wide step when d_pad = 16
+					a_hi[o] = hi;
+					a_lo[o] = lo;
+				}
 				norm[r] = fmaf(x, x, norm[r]);
 			}
 		}
@@ -186,9 +199,11 @@ cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints
 // the assignment kernel
 // ------------------------------------------------------------------------------------------
 
+constexpr uint32_t TC_NA_MAX = 8;        // most point-tile buffers (single resident centroid tile, 16-float rows)
+
 struct TcBars {
-	uint64_t a_full[TC_MA];
-	uint64_t a_empty[TC_MA];
+	uint64_t a_full[TC_NA_MAX];
+	uint64_t a_empty[TC_NA_MAX];
 	uint64_t b_full[TC_NB];
 	uint64_t b_empty[TC_NB];
 	uint64_t acc_full[TC_MA];
@@ -218,6 +233,14 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr)
 {
 	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Same for rows of `kw` floats: kw = 32 as above, kw = 16 -> 64-byte swizzle, rows of 64 B,
+// 8-row groups 512 B apart.
+__device__ __forceinline__ uint64_t make_desc_kw(uint32_t smem_addr, uint32_t kw)
+{
+	return kw == 32 ? make_desc(smem_addr)
+		: ((uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (32ull << 32) | (1ull << 46) | (4ull << 61));
 }
 
 // K-major operand without swizzle, one K step (8 tf32 = two 16-byte chunks) wide: 8x16-byte core
@@ -278,7 +301,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
 	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
-	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t nt_cols, uint32_t kchunks, uint32_t ksteps, uint32_t idesc,
+	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t nt_cols, uint32_t kw, uint32_t kchunks, uint32_t ksteps, uint32_t idesc,
 	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef)
 {
 	extern __shared__ uint8_t smem_raw[];
@@ -290,11 +313,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 	const uint32_t n_ctiles = k_pad / nt_cols;
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
+	// Resident-points layout (dim <= 32).  With a single centroid tile (k <= 256) that tile is loaded
+	// once and stays, and the space of the second stage holds two more point tiles, so that the
+	// next block's points arrive while this block is still being multiplied.
+	// Rows are kw = 32 floats (128 B) or, for dim <= 16, kw = 16 floats (64 B): half-size tiles.
+	const bool b_resident = n_ctiles == 1;
+	const uint32_t a_plane = TC_MTILE * kw * 4, a_tile = 2 * a_plane;
+	const uint32_t b_plane = TC_NT_MAX * kw * 4, b_stage = 2 * b_plane;
+	const uint32_t n_bstage = b_resident ? 1u : TC_NB;
+	const uint32_t n_abuf = min(TC_NA_MAX, (SM_AAUG_OFF - n_bstage * (b_stage + AUG_BYTES)) / a_tile);
+	const uint32_t sm_b_off = n_abuf * a_tile;
+	const uint32_t sm_baug_off = sm_b_off + n_bstage * b_stage;
 
 	if (threadIdx.x == 0) {
-		for (uint32_t i = 0; i < TC_MA; ++i) {
+		for (uint32_t i = 0; i < TC_NA_MAX; ++i) {
 			ptx::mbar_init(&bars->a_full[i], 1);
 			ptx::mbar_init(&bars->a_empty[i], 1);
+		}
+		for (uint32_t i = 0; i < TC_MA; ++i) {
 			ptx::mbar_init(&bars->acc_full[i], 1);
 			ptx::mbar_init(&bars->acc_empty[i], TC_EPI_WARPS);
 		}
@@ -344,7 +380,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		if (lane == 0) {
 			ptx::prefetch_tmap(&tm_a_hi); ptx::prefetch_tmap(&tm_a_lo);
 			ptx::prefetch_tmap(&tm_b_hi); ptx::prefetch_tmap(&tm_b_lo);
-			uint32_t a_use[TC_MA] = {0, 0};
+			uint32_t a_use[TC_NA_MAX] = {0, 0, 0, 0, 0, 0, 0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
 			if (kchunks > 1) {
@@ -370,34 +406,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 								++b_count;
 							}
 				}
-			} else
-			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
-				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-				for (uint32_t i = 0; i < tiles && ok; ++i) {
-					ok = wait_or_abort(&bars->a_empty[i], (a_use[i] & 1u) ^ 1u, abort_flag);
-					if (!ok) break;
-					uint8_t* dst = smem + SM_A_OFF + i * A_TILE_BYTES;
-					const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE);
-					ptx::mbar_arrive_expect_tx(&bars->a_full[i], A_TILE_BYTES);
-					ptx::tma_load_2d(dst, &tm_a_hi, 0, row, &bars->a_full[i]);
-					ptx::tma_load_2d(dst + A_PLANE_BYTES, &tm_a_lo, 0, row, &bars->a_full[i]);
-					++a_use[i];
-				}
-				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
-					const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
-					ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
-					if (!ok) break;
-					uint8_t* dst = smem + SM_B_OFF + s * B_STAGE_BYTES;
-					const uint32_t aug_bytes = nt_cols * 8 * 4;
-					ptx::mbar_arrive_expect_tx(&bars->b_full[s], 2 * nt_cols * TC_KCHUNK * 4 + aug_bytes);
-					ptx::tma_load_2d(dst, &tm_b_hi, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
-					ptx::tma_load_2d(dst + B_PLANE_BYTES, &tm_b_lo, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
-					ptx::bulk_g2s(smem + SM_BAUG_OFF + s * AUG_BYTES, b_aug + (size_t)j * nt_cols * 8, aug_bytes, &bars->b_full[s]);
-					++b_count;
+			} else {
+				uint32_t g = 0;                       // running count of point tiles = position in the A ring
+				bool b_loaded = false;
+				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+					for (uint32_t i = 0; i < tiles && ok; ++i, ++g) {
+						const uint32_t buf = g % n_abuf, u = g / n_abuf;
+						ok = wait_or_abort(&bars->a_empty[buf], (u & 1u) ^ 1u, abort_flag);
+						if (!ok) break;
+						uint8_t* dst = smem + SM_A_OFF + buf * a_tile;
+						const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE);
+						ptx::mbar_arrive_expect_tx(&bars->a_full[buf], a_tile);
+						ptx::tma_load_2d(dst, &tm_a_hi, 0, row, &bars->a_full[buf]);
+						ptx::tma_load_2d(dst + a_plane, &tm_a_lo, 0, row, &bars->a_full[buf]);
+						++a_use[buf];
+					}
+					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+						if (b_resident && b_loaded) break;
+						const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
+						ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
+						if (!ok) break;
+						uint8_t* dst = smem + sm_b_off + s * b_stage;
+						const uint32_t aug_bytes = nt_cols * 8 * 4;
+						ptx::mbar_arrive_expect_tx(&bars->b_full[s], 2 * nt_cols * kw * 4 + aug_bytes);
+						ptx::tma_load_2d(dst, &tm_b_hi, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
+						ptx::tma_load_2d(dst + b_plane, &tm_b_lo, 0, (int32_t)(j * nt_cols), &bars->b_full[s]);
+						ptx::bulk_g2s(smem + sm_baug_off + s * AUG_BYTES, b_aug + (size_t)j * nt_cols * 8, aug_bytes, &bars->b_full[s]);
+						++b_count;
+						b_loaded = true;
+					}
 				}
 			}
 			// Do not leave while an own copy may still be in flight towards this CTA's shared memory.
-			for (uint32_t i = 0; i < TC_MA; ++i)
+			for (uint32_t i = 0; i < TC_NA_MAX; ++i)
 				if (a_use[i]) ptx::mbar_wait(&bars->a_full[i], (a_use[i] - 1) & 1u);
 			for (uint32_t back = 0; back < TC_NB && back < b_count; ++back) {
 				const uint32_t c = b_count - 1 - back;
@@ -410,7 +452,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		// off the vector ALU, which the epilogue warps of the same scheduler keep busy); one
 		// elected lane issues the tensor-core instructions.
 		{
-			uint32_t a_use[TC_MA] = {0, 0};
 			uint32_t acc_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
@@ -455,29 +496,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							++acc_use[i];
 						}
 				}
-			} else
-			for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
-				const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-				for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
-					const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
-					ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
-					if (!ok) break;
-					const uint32_t b_addr = ptx::smem_u32(smem + SM_B_OFF + s * B_STAGE_BYTES);
-					const uint64_t b_hi = make_desc(b_addr), b_lo = make_desc(b_addr + B_PLANE_BYTES);
-					const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_BAUG_OFF + s * AUG_BYTES));
-					for (uint32_t i = 0; i < tiles; ++i) {
-						if (j == 0) {
-							ok = wait_or_abort(&bars->a_full[i], a_use[i] & 1u, abort_flag);
+			} else {
+#ifdef BKM_TC_TIMING
+				long long t_b = 0, t_a = 0, t_acc = 0, t_issue = 0;
+				const long long t_start = clock64();
+#endif
+				uint32_t g = 0;                       // position of the block's first tile in the A ring
+				bool b_ready = false;
+				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
+					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+						const uint32_t s = b_resident ? 0u : b_count % TC_NB, u = b_count / TC_NB;
+						TC_T(c0);
+						if (!(b_resident && b_ready)) {
+							ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
 							if (!ok) break;
+							b_ready = true;
 						}
-						ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
-						if (!ok) break;
-						ptx::tc_fence_after();
-						const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + i * A_TILE_BYTES);
-						const uint64_t a_hi = make_desc(a_addr), a_lo = make_desc(a_addr + A_PLANE_BYTES);
-						const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
-						if (ptx::elect_one()) {
-							{
+						TC_T(c1);
+						TC_ACC(t_b, c0, c1);
+						const uint32_t b_addr = ptx::smem_u32(smem + sm_b_off + s * b_stage);
+						const uint64_t b_hi = make_desc_kw(b_addr, kw), b_lo = make_desc_kw(b_addr + b_plane, kw);
+						const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + sm_baug_off + s * AUG_BYTES));
+						for (uint32_t i = 0; i < tiles; ++i) {
+							const uint32_t buf = (g + i) % n_abuf, ua = (g + i) / n_abuf;
+							TC_T(c2);
+							if (j == 0) {
+								ok = wait_or_abort(&bars->a_full[buf], ua & 1u, abort_flag);
+								if (!ok) break;
+							}
+							TC_T(c3);
+							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
+							if (!ok) break;
+							TC_T(c4);
+							TC_ACC(t_a, c2, c3);
+							TC_ACC(t_acc, c3, c4);
+							ptx::tc_fence_after();
+							const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + buf * a_tile);
+							const uint64_t a_hi = make_desc_kw(a_addr, kw), a_lo = make_desc_kw(a_addr + a_plane, kw);
+							const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
+							if (ptx::elect_one()) {
 								// small cross terms first, then the dominant hi*hi term, then |c|^2;
 								// +2 in the descriptor's address field = 32 bytes = one K step
 								#pragma unroll
@@ -490,19 +548,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 								for (uint32_t ks = 0; ks < 4; ++ks)
 									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
 								ptx::mma_tf32(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
+								ptx::mma_commit(&bars->acc_full[i]);
+								if (j == n_ctiles - 1) ptx::mma_commit(&bars->a_empty[buf]);
 							}
-							ptx::mma_commit(&bars->acc_full[i]);
-							if (j == n_ctiles - 1) ptx::mma_commit(&bars->a_empty[i]);
+							__syncwarp();
+							TC_T(c5);
+							TC_ACC(t_issue, c4, c5);
+							++acc_use[i];
 						}
-						__syncwarp();
-						++acc_use[i];
-						if (j == n_ctiles - 1) ++a_use[i];
+						if (!ok) break;
+						if (!b_resident) {
+							if (ptx::elect_one()) ptx::mma_commit(&bars->b_empty[s]);
+							__syncwarp();
+							++b_count;
+						}
 					}
-					if (!ok) break;
-					if (ptx::elect_one()) ptx::mma_commit(&bars->b_empty[s]);
-					__syncwarp();
-					++b_count;
+					g += tiles;
 				}
+#ifdef BKM_TC_TIMING
+				if (blockIdx.x == 3 && lane == 0)
+					printf("mma warp: total %lld  wait_b %lld  wait_a %lld  wait_acc %lld  issue %lld  (tiles %u)\n",
+						clock64() - t_start, t_b, t_a, t_acc, t_issue, g);
+#endif
 			}
 		}
 	} else {
@@ -520,6 +587,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		const uint32_t colbase = first_chunk * 32;
 		uint32_t acc_use[TC_MA] = {0, 0};
 		bool ok = true;
+#ifdef BKM_TC_TIMING
+		long long e_wait = 0, e_ld = 0, e_cmp = 0, e_merge = 0;
+		const long long e_start = clock64();
+#endif
 		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 			uint32_t best0 = 0xFFFFFFFFu, second0 = 0xFFFFFFFFu, bchunk0 = 0;
@@ -535,6 +606,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				#pragma unroll 1
 				for (uint32_t i = 0; i < tiles; ++i) {
 					const uint32_t use = i ? acc_use[1] : acc_use[0];
+					TC_T(e0);
 					if (ok) {
 						// one lane polls the barrier, the warp follows
 						bool w = true;
@@ -542,6 +614,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
 					}
 					if (i) ++acc_use[1]; else ++acc_use[0];
+					TC_T(e1);
+					TC_ACC(e_wait, e0, e1);
 					if (ok && nchunks > 0) {
 						ptx::tc_fence_after();
 						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
@@ -556,6 +630,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						ptx::tc_fence_before();
 						__syncwarp();
 						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
+						TC_T(e2);
+						TC_ACC(e_ld, e1, e2);
 						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
 						// columns at or behind k are padding
 						const uint32_t col0 = chunk0 * 32u;
@@ -568,6 +644,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							if (nchunks > 1 && left > 32) chunk_update<true>(v1, chunk0 + 1, left - 32, b, s2, bc);
 						}
 						if (i) { best1 = b; second1 = s2; bchunk1 = bc; } else { best0 = b; second0 = s2; bchunk0 = bc; }
+						TC_T(e3);
+						TC_ACC(e_cmp, e2, e3);
 					} else {
 						__syncwarp();
 						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
@@ -576,12 +654,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			}
 			// merge the four column parts: parts 1..3 hand their state over through shared memory
 			uint32_t* mg = mg_state;
+			TC_T(e4);
 			if (part > 0) {
 				uint32_t* dst = mg + (part - 1) * (3 * TC_MA * TC_MTILE);
 				dst[0 * TC_MTILE + row] = best0; dst[1 * TC_MTILE + row] = second0; dst[2 * TC_MTILE + row] = bchunk0;
 				dst[3 * TC_MTILE + row] = best1; dst[4 * TC_MTILE + row] = second1; dst[5 * TC_MTILE + row] = bchunk1;
 			}
-			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+			asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");   // the four warps that share these 32 rows
 			if (part == 0) {
 				#pragma unroll
 				for (uint32_t i = 0; i < TC_MA; ++i) {
@@ -608,8 +687,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					}
 				}
 			}
-			asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+			asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");   // the four warps that share these 32 rows
+			TC_T(e5);
+			TC_ACC(e_merge, e4, e5);
 		}
+#ifdef BKM_TC_TIMING
+		if (blockIdx.x == 3 && lane == 0 && (warp == 2 || warp == 7 || warp == 17))
+			printf("epi warp %u: total %lld  wait %lld  ld %lld  compute %lld  merge %lld\n", warp, clock64() - e_start, e_wait, e_ld, e_cmp, e_merge);
+#endif
 	}
 
 	ptx::tc_fence_before();
@@ -651,17 +736,19 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode()
 	return fn;
 }
 
-// [rows][cols] fp32 row-major, box = box_rows x 32 columns, 128-byte swizzle.
+// [rows][cols] fp32 row-major, box = box_rows x 32 columns with 128-byte swizzle, or, when the
+// rows are only 16 floats long, box_rows x 16 columns with 64-byte swizzle.
 static bool encode_plane(CUtensorMap* out, const float* base, uint64_t rows, uint32_t cols, uint32_t box_rows)
 {
+	const uint32_t kw = cols == 16 ? 16u : TC_KCHUNK;
 	auto enc = get_encode();
 	if (!enc) return false;
 	cuuint64_t dims[2] = {cols, rows};
 	cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
-	cuuint32_t box[2] = {TC_KCHUNK, box_rows};
+	cuuint32_t box[2] = {kw, box_rows};
 	cuuint32_t estr[2] = {1, 1};
 	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-		CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+		CU_TENSOR_MAP_INTERLEAVE_NONE, kw == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
 		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 	return r == CUDA_SUCCESS;
 }
@@ -671,7 +758,7 @@ TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, in
 	static const char* e_sup = "shape not supported by the tensor-core assignment";
 	static const char* e_map = "cuTensorMapEncodeTiled failed or is unavailable";
 	static const char* e_attr = "cannot set the shared-memory size of the tensor-core kernel";
-	if (!assign_tc_supported(s) || tp.d_pad != tm.d_pad || tp.d_pad % TC_KCHUNK != 0) { if (err) *err = e_sup; return nullptr; }
+	if (!assign_tc_supported(s) || tp.d_pad != tm.d_pad || (tp.d_pad != 16 && tp.d_pad % TC_KCHUNK != 0)) { if (err) *err = e_sup; return nullptr; }
 	TcPlan* p = new (std::nothrow) TcPlan();
 	if (!p) return nullptr;
 	p->s = s; p->tp = tp; p->tm = tm;
@@ -707,11 +794,12 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
 	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
 	const float margin_coef = margin_scale * (48.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
-	const uint32_t kchunks = p->tp.d_pad / TC_KCHUNK;
-	const uint32_t ksteps_last = (p->s.dim - (kchunks - 1) * TC_KCHUNK + 7) / 8;    // K steps of the last 32-dimension slice
+	const uint32_t kw = p->tp.d_pad == 16 ? 16u : TC_KCHUNK;
+	const uint32_t kchunks = p->tp.d_pad / kw;
+	const uint32_t ksteps_last = (p->s.dim - (kchunks - 1) * kw + 7) / 8;    // K steps of the last slice
 	const uint32_t idesc = p->idesc;
 	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
-		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kchunks, ksteps_last, idesc,
+		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,
 		ctl, slot, flag_list, margin_coef);
 	return cudaGetLastError();
 }

@@ -54,7 +54,8 @@ __host__ __device__ __forceinline__ uint32_t simt_rows(uint32_t k) { return roun
 // swizzle row), point rows padded to 128, mean rows padded to 16.
 constexpr uint32_t TC_KCHUNK = 32;
 constexpr uint32_t TC_MTILE = 128;
-__host__ __device__ __forceinline__ uint32_t tc_dpad(uint32_t dim) { return round_up(dim, TC_KCHUNK); }
+// dim <= 16 uses rows of 16 floats (64-byte swizzle): half the operand bytes of a 32-float row
+__host__ __device__ __forceinline__ uint32_t tc_dpad(uint32_t dim) { return dim <= 16 ? 16u : round_up(dim, TC_KCHUNK); }
 
 // The per-iteration accumulators (k*dim float sums directly followed by k integer sizes) exist in
 // `acc_replicas` copies so that concurrent global reductions spread over more cache lines; a
