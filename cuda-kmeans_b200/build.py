@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbkm.so")
-SOURCES = ["api.cu", "assign_simt.cu", "assign_tc.cu", "update.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "assign_simt.cu", "assign_tc.cu", "assign_tc_pair.cu", "update.cu", "no_alloc.cu"]
 HEADERS = ["common.cuh", "kernels.cuh", "ptx.cuh", os.path.join("..", "..", "include", "bkm.h")]
 
 NVCC_FLAGS = [

@@ -283,6 +283,7 @@ struct bkm_handle_s {
 	uint32_t launches_per_iter = 0;
 	// CUDA graph of two iterations (launch-bound problem sizes)
 	int use_graph = 2;                 // 0 = never, 1 = always (single GPU), 2 = by problem size
+	bool tc_pair = true;               // let the tensor-core assignment use its CTA-pair kernel where it applies
 	cudaGraphExec_t graph_exec = nullptr;
 	int graph_cur = 0, graph_slot = 0;
 	cudaStream_t graph_stream = nullptr;
@@ -530,6 +531,12 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value)
 		drop_graph(h);
 		return BKM_OK;
 	}
+	if (!strcmp(name, "tc_pair")) {
+		h->tc_pair = value != 0.0;
+		bkm::tc_plan_allow_pair(h->plan, h->tc_pair);
+		drop_graph(h);
+		return BKM_OK;
+	}
 	return fail(BKM_ERR_INVALID, "unknown option '%s'", name);
 }
 
@@ -551,6 +558,7 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 		const char* err = nullptr;
 		h->plan = bkm::tc_plan_create(s, h->ws.tp, h->ws.tm, h->cfg.device, &err);
 		if (!h->plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
+		bkm::tc_plan_allow_pair(h->plan, h->tc_pair);
 	}
 	bkm::launch_prepare_means(h->d_means[0], s,
 		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,

@@ -4,30 +4,32 @@
 //
 // The x.c contraction runs as split-TF32 ("3xTF32"): every fp32 operand is split once into a
 // tf32 high part and a tf32 low part (x = xh + xl), and xl*ch + xh*cl + xh*ch is accumulated in
-// fp32 in tensor memory, which restores fp32-level accuracy of the products.  |c|^2 enters the
-// same accumulator through one more K step whose A operand is a constant tile of ones, so the
-// accumulator holds |c|^2 - 2 x.c and the epilogue is a pure arg-min.  The N x k distance
+// fp32 in tensor memory, which restores fp32-level accuracy of the products.  |c|^2 and an offset
+// constant enter the same accumulator through one more K step whose A operand is a constant
+// tile, so the accumulator holds |c|^2 - 2 x.c + C, all values positive with one exponent, and
+// the epilogue is a pure arg-min on integer keys.  The N x k distance
 // matrix never exists in HBM.  Because the GEMM form cancels, a point whose best and
 // second-best values are closer than the error band of this formulation is queued for the
 // exact CUDA-core kernel, so the final assignment equals the reference arithmetic
 // (headers/serial.hpp:21-35 of krulis-martin/cuda-kmeans) for every point.  The kernel covers
 // the shape range of the reference's cachedRegsAssignmentKernel (kernels/kernels.cu:548-661).
 //
-// Kernel organisation (one persistent CTA per SM, 10 warps):
-//   warp 0     : TMA producer.  Point tiles (128 points x 32 dims, hi and lo plane) are loaded
-//                once per block of 4 tiles and stay in shared memory; centroid tiles (up to 128
-//                centroids x 32 dims, hi and lo, plus their |c|^2 K step) stream through a
-//                2-stage ring.
-//   warp 1     : allocates the 512 TMEM columns and issues the tcgen05.mma instructions
-//                (kind::tf32, M=128, N<=128, K=8).  Back-to-back MMAs into ONE accumulator are
-//                bound by the accumulate latency, not by the tensor work, so the K steps of two
-//                accumulators are issued interleaved.
-//   warps 2..9 : epilogue.  Two warps per 32-lane TMEM quarter; the pair alternates over the
-//                point tiles, so that one computes while the other waits for tensor memory.
-//                Each reads its accumulator rows with tcgen05.ld, packs the column position
-//                into the low mantissa bits, and reduces 32 columns at a time to (best, second)
-//                with a min/max tournament; (best, second, chunk of best) per point stay in
-//                registers across all centroid tiles.
+// Kernel organisation (one persistent CTA per SM, 18 warps):
+//   warp 0      : TMA producer.  dim <= 32: point tiles (128 points, hi and lo plane) go through a
+//                 ring and stay for all mean tiles; mean tiles (up to 256 means, hi and lo, plus
+//                 their |c|^2 K step) stream through a 2-stage ring, or stay when there is only
+//                 one.  dim > 32: both operands stream in 32-dimension slices.
+//   warp 1      : allocates the 512 TMEM columns and issues the tcgen05.mma instructions
+//                 (kind::tf32, M=128, N<=256, K=8) into two accumulators, one per point tile of
+//                 a block.  The whole warp walks the loop; one elected lane issues.
+//   warps 2..17 : epilogue.  Eight warps per accumulator (TMEM lane quarter x column half), so
+//                 that one accumulator is reduced while the other is being multiplied.  A warp
+//                 reads its columns with tcgen05.ld two 32-column chunks at a time, hands the
+//                 accumulator back after its last load, and reduces each chunk to (best, second)
+//                 on integer keys; (best, second, chunk of best) per point stay in registers
+//                 across all mean tiles and are merged through shared memory at the end.
+// Mean sets of 2..4 tiles of 256 with 17 <= dim <= 32 run on CTA pairs instead, with all means
+// resident in shared memory (assign_tc_pair.cu).
 // All mbarrier waits are bounded; a wait that runs out sets STATUS_WAIT_TIMEOUT and lets every
 // role fall through to the end, where TMEM is released.
 #include <cuda.h>
@@ -35,31 +37,14 @@
 
 #include "kernels.cuh"
 #include "ptx.cuh"
+#include "tc_common.cuh"
 
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <new>
 
-// Optional stage timing for development builds (-DBKM_TC_TIMING): one CTA prints how its MMA warp
-// and three of its epilogue warps spent their cycles.
-#ifdef BKM_TC_TIMING
-#include <cstdio>
-#define TC_T(var) const long long var = clock64()
-#define TC_ACC(sum, from, to) sum += (to) - (from)
-#else
-#define TC_T(var)
-#define TC_ACC(sum, from, to)
-#endif
-
 namespace bkm {
-
-constexpr uint32_t TC_MA = 2;            // point tiles per block (= TMEM accumulators)
-constexpr uint32_t TC_NB = 2;            // centroid-tile stages
-constexpr uint32_t TC_NT_MAX = 256;      // centroids per tile (the widest MMA: N = 256)
-constexpr uint32_t TC_EPI_WARPS = 16;          // four per TMEM lane quarter, each a quarter of the columns
-constexpr uint32_t TC_THREADS = (2 + TC_EPI_WARPS) * 32;
-constexpr uint32_t TC_MAX_KPAD = 1u << 20;
-constexpr uint32_t TC_TMEM_COLS = 512;
 
 constexpr uint32_t A_PLANE_BYTES = TC_MTILE * TC_KCHUNK * 4;     // 16 KiB: 128 rows x 128 B
 constexpr uint32_t B_PLANE_BYTES = TC_NT_MAX * TC_KCHUNK * 4;    // 32 KiB: 256 rows x 128 B
@@ -77,7 +62,7 @@ constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;
 constexpr uint32_t SM_BAUG_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // |c|^2 K step per stage
 constexpr uint32_t SM_AAUG_OFF = SM_BAUG_OFF + TC_NB * AUG_BYTES;  // constant ones tile (128 rows)
 constexpr uint32_t SM_MERGE_OFF = SM_AAUG_OFF + TC_MTILE * 8 * 4;
-constexpr uint32_t MERGE_BYTES = 3 * 3 * TC_MA * TC_MTILE * 4;   // (best, second, chunk) of column parts 1..3
+constexpr uint32_t MERGE_BYTES = 2 * 3 * TC_MA * TC_MTILE * 4;   // (best, second, chunk) of the upper column half, two slots
 constexpr uint32_t SM_BAR_OFF = SM_MERGE_OFF + MERGE_BYTES;
 constexpr uint32_t SM_TOTAL = SM_BAR_OFF + 256;
 constexpr uint32_t SM_ALLOC = SM_TOTAL + 1024;                   // slack for 1024-byte alignment
@@ -93,13 +78,6 @@ bool assign_tc_supported(const Shape& s)
 // ------------------------------------------------------------------------------------------
 // one-off split of the points
 // ------------------------------------------------------------------------------------------
-
-__device__ __forceinline__ float to_tf32(float x)
-{
-	uint32_t u;
-	asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-	return __uint_as_float(u);
-}
 
 // 32 points x 32 dims per step through a padded shared tile, so that both the read (along
 // points for SoA, along dims for AoS) and the write (along dims) are coalesced.
@@ -215,88 +193,6 @@ static_assert(sizeof(TcBars) <= 256, "barrier block too large");
 static_assert(SM_ALLOC <= 227 * 1024, "shared memory budget exceeded");
 static_assert(TC_NB * KSTAGE_BYTES <= SM_AAUG_OFF, "K-loop stages overlap the constant tile");
 
-// Bounded wait that also gives up when another role already failed.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
-{
-	if (ptx::mbar_try_wait(bar, parity)) return true;
-	const uint64_t t0 = ptx::globaltimer_ns();
-	while (true) {
-		if (ptx::mbar_try_wait(bar, parity)) return true;
-		if (*abort_flag) return false;
-		if (ptx::globaltimer_ns() - t0 > ptx::WAIT_LIMIT_NS) break;
-	}
-	*abort_flag = 1;
-	return false;
-}
-
-// K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr)
-{
-	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Same for rows of `kw` floats: kw = 32 as above, kw = 16 -> 64-byte swizzle, rows of 64 B,
-// 8-row groups 512 B apart.
-__device__ __forceinline__ uint64_t make_desc_kw(uint32_t smem_addr, uint32_t kw)
-{
-	return kw == 32 ? make_desc(smem_addr)
-		: ((uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (32ull << 32) | (1ull << 46) | (4ull << 61));
-}
-
-// K-major operand without swizzle, one K step (8 tf32 = two 16-byte chunks) wide: 8x16-byte core
-// matrices; the two chunks of a row group are 128 B apart, row groups 256 B apart.
-__device__ __forceinline__ uint64_t make_desc_aug(uint32_t smem_addr)
-{
-	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (8ull << 16) | (16ull << 32) | (1ull << 46);
-}
-
-__device__ __forceinline__ uint32_t umin3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_u32(a, b, c); }
-
-// Smallest and second-smallest of 32 keys by a tournament: 16 (min,max) pairs, then 15 merges
-// (b,s) x (b',s') -> (min(b,b'), min(max(b,b'), s, s')).  77 instructions, log depth.
-__device__ __forceinline__ void top2_of_32(const uint32_t (&p)[32], uint32_t& b, uint32_t& s)
-{
-	uint32_t lo[16], hi[16];
-	#pragma unroll
-	for (int i = 0; i < 16; ++i) { lo[i] = min(p[2 * i], p[2 * i + 1]); hi[i] = max(p[2 * i], p[2 * i + 1]); }
-	#pragma unroll
-	for (int n = 16; n > 1; n >>= 1) {
-		#pragma unroll
-		for (int i = 0; i < n / 2; ++i) {
-			const uint32_t nb = min(lo[2 * i], lo[2 * i + 1]);
-			const uint32_t ns = umin3(max(lo[2 * i], lo[2 * i + 1]), hi[2 * i], hi[2 * i + 1]);
-			lo[i] = nb;
-			hi[i] = ns;
-		}
-	}
-	b = lo[0];
-	s = hi[0];
-}
-
-// One 32-column chunk of an accumulator row.  The kernel adds a constant to every value so that
-// all of them are positive floats with the SAME exponent; their bit patterns then order like the
-// values, the upper exponent bits carry no information, and bits*32 + column (one integer
-// multiply-add, off the min/max pipe) is a key that keeps the full 23-bit mantissa and carries
-// the column position.  The keys are reduced to the two smallest and merged into the running
-// (best, second, chunk of best).  `nvalid` < 32 masks the padding columns behind the last mean.
-template<bool MASKED>
-__device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t chunk_id, uint32_t nvalid,
-	uint32_t& best, uint32_t& second, uint32_t& best_chunk)
-{
-	uint32_t p[32];
-	#pragma unroll
-	for (uint32_t t = 0; t < 32; ++t) p[t] = v[t] * 32u + t;
-	if (MASKED && nvalid < 32) {
-		#pragma unroll
-		for (uint32_t t = 0; t < 32; ++t) p[t] = t < nvalid ? p[t] : 0xFFFFFFFFu;
-	}
-	uint32_t b, s2;
-	top2_of_32(p, b, s2);
-	second = umin3(second, max(best, b), s2);
-	best_chunk = b < best ? chunk_id : best_chunk;
-	best = min(best, b);
-}
-
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -332,7 +228,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		}
 		for (uint32_t i = 0; i < TC_MA; ++i) {
 			ptx::mbar_init(&bars->acc_full[i], 1);
-			ptx::mbar_init(&bars->acc_empty[i], TC_EPI_WARPS);
+			ptx::mbar_init(&bars->acc_empty[i], TC_EPI_WARPS / TC_MA);
 		}
 		for (uint32_t i = 0; i < TC_NB; ++i) {
 			ptx::mbar_init(&bars->b_full[i], 1);
@@ -345,31 +241,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		ptx::tmem_alloc(&bars->tmem_slot, TC_TMEM_COLS);
 		ptx::tmem_relinquish();
 	}
-	// Offset constant: every value |c|^2 - 2 x.c lies in [-X2, X2 + 2*C2] (X2, C2 = largest |x|^2,
-	// |c|^2 after centring), an interval of width 2*(X2+C2); with P a power of two >= 1.25 times
-	// that width, value + P + X2 + P/32 stays inside [P, 2P) with P/32 of head-room on both
-	// sides for the rounding of the pass: one exponent for all values.
 	const float x2max = ctl->xmax2, c2max = ctl->cmax2[slot];
-	float pow2 = 1.0f;
-	{
-		const float span = 1.25f * (2.0f * (x2max + c2max)) + 1.0e-30f;
-		int e;
-		frexpf(span, &e);                       // span = m * 2^e, m in [0.5, 1)
-		pow2 = ldexpf(1.0f, e);                 // >= span
-	}
-	const float offset_c = pow2 + x2max + pow2 * (1.0f / 32.0f);
-	{
-		// the constant A operand of the extra K step: columns 0 and 1 are one (they meet the high
-		// and the low part of |c|^2), columns 2 and 3 hold the offset constant as tf32 hi/lo
-		// (they meet ones on the B side), the rest is zero
-		const float c_hi = to_tf32(offset_c), c_lo = to_tf32(offset_c - c_hi);
-		float* a_aug = reinterpret_cast<float*>(smem + SM_AAUG_OFF);
-		for (uint32_t e = threadIdx.x; e < TC_MTILE * 8; e += TC_THREADS) {
-			const uint32_t row = e >> 3, kk = e & 7u;
-			a_aug[aug_offset(row, kk)] = kk < 2 ? 1.0f : (kk == 2 ? c_hi : (kk == 3 ? c_lo : 0.0f));
-		}
-		ptx::fence_proxy_async();
-	}
+	const KeyConsts kc = make_key_consts(x2max, c2max);
+	const float pow2 = kc.pow2;
+	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base;
+	fill_a_aug(reinterpret_cast<float*>(smem + SM_AAUG_OFF), kc.offset_c, threadIdx.x, TC_THREADS);
+	ptx::fence_proxy_async();
 	ptx::tc_fence_before();
 	__syncthreads();
 	ptx::tc_fence_after();
@@ -574,122 +451,116 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		}
 	} else {
 		// ---------------- epilogue ----------------
-		// The loops over tiles and chunks are kept rolled on purpose: unrolled, the arg-min code
-		// of one block outgrows the instruction cache and the warps starve on instruction fetch.
-		const uint32_t q = warp & 3u;              // TMEM lane quarter this warp may read
-		const uint32_t part = (warp - 2) >> 2;     // which quarter of the tile's columns (0..3)
+		// Warp (q, half, i): TMEM lane quarter q (the only lanes the warp may read), column half
+		// `half` of accumulator i.  The eight warps of one accumulator work while the other
+		// accumulator is being multiplied, so on every scheduler two warps read tensor memory while
+		// the other two keep the integer pipes busy.  A warp takes its columns two 32-column chunks
+		// at a time into registers and hands the accumulator back after its last load.
+		// The loops are kept rolled on purpose: unrolled, the arg-min code outgrows the instruction
+		// cache and the warps starve on instruction fetch.
+		const uint32_t q = warp & 3u;
+		const uint32_t part = (warp - 2) >> 2;     // 0..3
+		const uint32_t i = part >> 1;              // accumulator = point tile within the block
+		const uint32_t half = part & 1u;
 		const uint32_t row = q * 32 + lane;
 		const float ulp = pow2 * 1.1920929e-07f;   // spacing of the values inside [P, 2P)
 		const uint32_t chunks_total = nt_cols >> 5;                    // 1..8
-		const uint32_t per_part = (chunks_total + 3) / 4;              // 1..2
-		const uint32_t first_chunk = part * per_part;
-		const uint32_t nchunks = first_chunk >= chunks_total ? 0u : min(per_part, chunks_total - first_chunk);
-		const uint32_t colbase = first_chunk * 32;
-		uint32_t acc_use[TC_MA] = {0, 0};
+		const uint32_t per_half = (chunks_total + 1) / 2;              // 1..4
+		const uint32_t first_chunk = half * per_half;
+		const uint32_t nchunks = first_chunk >= chunks_total ? 0u : min(per_half, chunks_total - first_chunk);
+		const uint32_t bar_id = 1u + i * 4u + q;   // named barrier of the two warps that share these rows
+		uint32_t acc_use = 0, blk_count = 0;
 		bool ok = true;
 #ifdef BKM_TC_TIMING
 		long long e_wait = 0, e_ld = 0, e_cmp = 0, e_merge = 0;
 		const long long e_start = clock64();
 #endif
-		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x, ++blk_count) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-			uint32_t best0 = 0xFFFFFFFFu, second0 = 0xFFFFFFFFu, bchunk0 = 0;
-			uint32_t best1 = 0xFFFFFFFFu, second1 = 0xFFFFFFFFu, bchunk1 = 0;
-			// |x|^2 of this thread's two points is only needed at the end of the block: fetch it now
-			float xn0 = 0.0f, xn1 = 0.0f;
-			if (part == 0) {
-				const uint64_t p0 = (uint64_t)(blk * TC_MA) * TC_MTILE + row;
-				if (p0 < n) xn0 = xnorm[p0];
-				if (p0 + TC_MTILE < n) xn1 = xnorm[p0 + TC_MTILE];
-			}
+			if (i >= tiles) continue;              // odd tail: this accumulator is not used in the last block
+			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
+			const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
+			// |x|^2 of this thread's point is only needed at the end of the block: fetch it now
+			float xn = 0.0f;
+			if (half == 0 && p < n) xn = xnorm[p];
+			#pragma unroll 1
 			for (uint32_t j = 0; j < n_ctiles; ++j) {
-				#pragma unroll 1
-				for (uint32_t i = 0; i < tiles; ++i) {
-					const uint32_t use = i ? acc_use[1] : acc_use[0];
-					TC_T(e0);
-					if (ok) {
-						// one lane polls the barrier, the warp follows
-						bool w = true;
-						if (lane == 0) w = wait_or_abort(&bars->acc_full[i], use & 1u, abort_flag);
-						ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
-					}
-					if (i) ++acc_use[1]; else ++acc_use[0];
-					TC_T(e1);
-					TC_ACC(e_wait, e0, e1);
-					if (ok && nchunks > 0) {
-						ptx::tc_fence_after();
+				TC_T(e0);
+				if (ok) {
+					// one lane polls the barrier, the warp follows
+					bool w = true;
+					if (lane == 0) w = wait_or_abort(&bars->acc_full[i], acc_use & 1u, abort_flag);
+					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
+				}
+				++acc_use;
+				TC_T(e1);
+				TC_ACC(e_wait, e0, e1);
+				if (ok && nchunks > 0) {
+					ptx::tc_fence_after();
+					#pragma unroll 1
+					for (uint32_t c = 0; c < nchunks; c += 2) {
+						const uint32_t colbase = (first_chunk + c) * 32u;
 						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
 						const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
-						// This warp's columns go to registers first and the accumulator is handed back
-						// to the MMA warp right away; the arg-min then runs from registers while the
-						// tensor cores already fill the accumulator again.
+						const bool two = c + 1 < nchunks;
+						TC_T(e2);
 						uint32_t v0[32], v1[32];
 						ptx::tmem_ld32(taddr, v0);
-						if (nchunks > 1) ptx::tmem_ld32(taddr + 32, v1);
+						if (two) ptx::tmem_ld32(taddr + 32, v1);
 						ptx::tmem_ld_wait();
-						ptx::tc_fence_before();
-						__syncwarp();
-						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
-						TC_T(e2);
-						TC_ACC(e_ld, e1, e2);
-						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
+						if (c + 2 >= nchunks) {
+							// last load: the tensor cores may fill this accumulator again
+							ptx::tc_fence_before();
+							__syncwarp();
+							if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
+						}
+						TC_T(e3);
+						TC_ACC(e_ld, e2, e3);
 						// columns at or behind k are padding
 						const uint32_t col0 = chunk0 * 32u;
 						const uint32_t left = k > col0 ? k - col0 : 0u;
-						if (left >= 64 || (nchunks == 1 && left >= 32)) {
-							chunk_update<false>(v0, chunk0, 32, b, s2, bc);
-							if (nchunks > 1) chunk_update<false>(v1, chunk0 + 1, 32, b, s2, bc);
+						if (left >= 64 || (!two && left >= 32)) {
+							chunk_update<false>(v0, key_mult, kc.one, chunk0, 32, best, second, bchunk);
+							if (two) chunk_update<false>(v1, key_mult, kc.one, chunk0 + 1, 32, best, second, bchunk);
 						} else {
-							if (left > 0) chunk_update<true>(v0, chunk0, left, b, s2, bc);
-							if (nchunks > 1 && left > 32) chunk_update<true>(v1, chunk0 + 1, left - 32, b, s2, bc);
+							if (left > 0) chunk_update<true>(v0, key_mult, kc.one, chunk0, left, best, second, bchunk);
+							if (two && left > 32) chunk_update<true>(v1, key_mult, kc.one, chunk0 + 1, left - 32, best, second, bchunk);
 						}
-						if (i) { best1 = b; second1 = s2; bchunk1 = bc; } else { best0 = b; second0 = s2; bchunk0 = bc; }
-						TC_T(e3);
-						TC_ACC(e_cmp, e2, e3);
-					} else {
-						__syncwarp();
-						if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
+						TC_T(e4);
+						TC_ACC(e_cmp, e3, e4);
 					}
+				} else {
+					__syncwarp();
+					if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
 				}
 			}
-			// merge the four column parts: parts 1..3 hand their state over through shared memory
-			uint32_t* mg = mg_state;
-			TC_T(e4);
-			if (part > 0) {
-				uint32_t* dst = mg + (part - 1) * (3 * TC_MA * TC_MTILE);
-				dst[0 * TC_MTILE + row] = best0; dst[1 * TC_MTILE + row] = second0; dst[2 * TC_MTILE + row] = bchunk0;
-				dst[3 * TC_MTILE + row] = best1; dst[4 * TC_MTILE + row] = second1; dst[5 * TC_MTILE + row] = bchunk1;
-			}
-			asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");   // the four warps that share these 32 rows
-			if (part == 0) {
-				#pragma unroll
-				for (uint32_t i = 0; i < TC_MA; ++i) {
-					const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
-					if (i < tiles && p < n && ok) {
-						uint32_t b = i ? best1 : best0, s2 = i ? second1 : second0, bc = i ? bchunk1 : bchunk0;
-						#pragma unroll
-						for (uint32_t o = 0; o < 3; ++o) {
-							const uint32_t* src = mg + o * (3 * TC_MA * TC_MTILE) + i * 3 * TC_MTILE;
-							const uint32_t ob = src[row], os = src[TC_MTILE + row], oc = src[2 * TC_MTILE + row];
-							s2 = umin3(s2, os, max(b, ob));
-							bc = ob < b ? oc : bc;
-							b = min(b, ob);
-						}
-						asg[p] = bc * 32u + (b & 31u);
-						// keys are (mantissa bits << 5 | column): their difference >> 5 counts value spacings
-						const float gap = s2 == 0xFFFFFFFFu ? INFINITY : (float)((s2 >> 5) - (b >> 5)) * ulp;
-						const float margin = margin_coef * ((i ? xn1 : xn0) + c2max) + 4.0f * ulp;
-						if (gap <= margin) {
-							const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-							if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
-							else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
-						}
-					}
-				}
-			}
-			asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");   // the four warps that share these 32 rows
+			// The upper column half hands its state to the lower one through shared memory.  The slots
+			// alternate with the block count, so one barrier per block is enough: a slot is written
+			// again only after its reader has passed the barrier of the block in between.
 			TC_T(e5);
-			TC_ACC(e_merge, e4, e5);
+			uint32_t* mg = mg_state + ((blk_count & 1u) * TC_MA + i) * (3 * TC_MTILE);
+			if (half == 1) {
+				mg[row] = best; mg[TC_MTILE + row] = second; mg[2 * TC_MTILE + row] = bchunk;
+			}
+			asm volatile("bar.sync %0, 64;" :: "r"(bar_id) : "memory");
+			if (half == 0 && p < n && ok) {
+				const uint32_t ob = mg[row], os = mg[TC_MTILE + row], oc = mg[2 * TC_MTILE + row];
+				second = umin3(second, os, max(best, ob));
+				bchunk = ob < best ? oc : bchunk;
+				best = min(best, ob);
+				// key - key_base = M * mantissa + column
+				const uint32_t bm = (best - key_base) / key_mult;
+				asg[p] = bchunk * 32u + ((best - key_base) - bm * key_mult);
+				const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
+				const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
+				if (gap <= margin) {
+					const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
+					if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
+					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+				}
+			}
+			TC_T(e6);
+			TC_ACC(e_merge, e5, e6);
 		}
 #ifdef BKM_TC_TIMING
 		if (blockIdx.x == 3 && lane == 0 && (warp == 2 || warp == 7 || warp == 17))
@@ -713,6 +584,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 
 struct TcPlan {
 	CUtensorMap a_hi, a_lo, b_hi, b_lo;
+	CUtensorMap bh_hi, bh_lo;       // the means in boxes of 128 rows: one CTA's half of a tile (pair kernel)
+	bool pair_ok;                   // the CTA-pair kernel covers this shape
+	bool pair_allowed;
+	int max_pairs;                  // CTA pairs the device holds at once
 	Shape s;
 	TcPoints tp;
 	TcMeans tm;
@@ -780,8 +655,21 @@ TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, in
 		delete p;
 		return nullptr;
 	}
+	p->pair_allowed = true;
+	p->pair_ok = assign_tc_pair_supported(s.k, tm.k_pad, tp.d_pad, p->nt_cols, p->sm_count) &&
+		encode_plane(&p->bh_hi, tm.b_hi, tm.k_pad, tm.d_pad, TC_NT_MAX / 2) &&
+		encode_plane(&p->bh_lo, tm.b_lo, tm.k_pad, tm.d_pad, TC_NT_MAX / 2);
+	p->max_pairs = 0;
+	if (p->pair_ok && (assign_tc_pair_prepare(&p->max_pairs) != cudaSuccess || p->max_pairs < 1)) {
+		cudaGetLastError();
+		p->pair_ok = false;
+	}
+	if (getenv("BKM_DEBUG_PLAN")) fprintf(stderr, "bkm: tensor-core plan: pair kernel %s, %d co-resident pairs on %d SMs\n", p->pair_ok ? "on" : "off", p->max_pairs, p->sm_count);
 	return p;
 }
+
+void tc_plan_allow_pair(TcPlan* plan, bool allow) { if (plan) plan->pair_allowed = allow; }
+bool tc_plan_uses_pair(const TcPlan* plan) { return plan && plan->pair_ok && plan->pair_allowed; }
 
 void tc_plan_destroy(TcPlan* plan) { delete plan; }
 
@@ -798,6 +686,9 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t kchunks = p->tp.d_pad / kw;
 	const uint32_t ksteps_last = (p->s.dim - (kchunks - 1) * kw + 7) / 8;    // K steps of the last slice
 	const uint32_t idesc = p->idesc;
+	if (tc_plan_uses_pair(p))
+		return launch_assign_tc_pair(p->a_hi, p->a_lo, p->bh_hi, p->bh_lo, p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles,
+			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream);
 	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
 		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,
 		ctl, slot, flag_list, margin_coef);

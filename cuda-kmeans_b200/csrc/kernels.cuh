@@ -79,6 +79,9 @@ cudaError_t launch_compute_center(const float* pts, const Shape& s, float* cente
 struct TcPlan;
 TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err);
 void tc_plan_destroy(TcPlan* plan);
+// The CTA-pair kernel (means resident in shared memory) is used where it applies unless disallowed.
+void tc_plan_allow_pair(TcPlan* plan, bool allow);
+bool tc_plan_uses_pair(const TcPlan* plan);
 cudaError_t launch_assign_tc(TcPlan* plan, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
 	float margin_scale, cudaStream_t stream);
 

@@ -178,4 +178,85 @@ __device__ __forceinline__ void tmem_ld_wait()
 	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- CTA pairs (thread-block cluster of two, tcgen05 cta_group::2) ----
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+	uint32_t r;
+	asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+	return r;
+}
+
+// Barrier over all threads of the cluster; orders shared-memory writes before it with reads after it.
+__device__ __forceinline__ void cluster_sync()
+{
+	asm volatile("barrier.cluster.arrive.release.aligned;\n"
+		"barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank)
+{
+	uint32_t r;
+	asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+	return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+	asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v)
+{
+	asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(cluster_addr), "r"(v) : "memory");
+}
+
+// 2-D tiled TMA load into this CTA's shared memory whose completion bytes are counted on a
+// barrier of the pair's first CTA: clearing bit 24 of a shared address turns it into that CTA's.
+__device__ __forceinline__ uint32_t leader_cta_addr(uint32_t smem_addr) { return smem_addr & 0xFEFFFFFFu; }
+
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, int32_t x, int32_t y, uint32_t leader_bar_addr)
+{
+	asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+		:: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(leader_bar_addr), "r"(x), "r"(y) : "memory");
+}
+
+// TMEM allocation for a CTA pair: the same warp of both CTAs executes it.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t cols)
+{
+	asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
+{
+	asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+}
+
+// One MMA over both CTAs of the pair (M = 256: 128 accumulator rows in each CTA's tensor memory;
+// each CTA's shared memory holds its 128 rows of A and its half of the N rows of B at the
+// descriptor's address).  Issued by one thread of the pair's first CTA.
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+	asm volatile(
+		"{\n"
+		".reg .pred p;\n"
+		"setp.ne.b32 p, %4, 0;\n"
+		"tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+		"}\n"
+		:: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Arrives on the barrier at shared::cluster address `bar_addr` (of either CTA of the pair) once
+// all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar_addr)
+{
+	asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_addr) : "memory");
+}
+
 }} // namespace bkm::ptx

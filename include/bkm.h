@@ -167,7 +167,9 @@ int bkm_set_stream(bkm_handle_t h, void* stream);
 /* Tunables: "margin_scale" (multiplier on the near-tie band, default 1), "phase_timing"
  * (0/1: record per-phase CUDA events, default 1), "use_graph" (0 never, 1 always, 2 = default:
  * replay a CUDA graph of two iterations when the problem is small enough to be bound by launch
- * latency; single GPU only).  Unknown names fail with BKM_ERR_INVALID. */
+ * latency; single GPU only), "tc_pair" (0/1, default 1: let the tensor-core assignment run on CTA
+ * pairs with all means resident in shared memory where the shape allows, i.e. 257..1024 means
+ * of 17..32 dimensions).  Unknown names fail with BKM_ERR_INVALID. */
 int bkm_set_option(bkm_handle_t h, const char* name, double value);
 
 /* initialize(): copies points and initial means from HOST memory, runs the one-off

@@ -114,6 +114,31 @@ def test_variants_agree(pkg, torch_cuda, oracle_mod, workloads):
         assert ok, err
 
 
+@pytest.mark.parametrize("n,k,d,layout", [
+    (5000, 1024, 32, 1),      # four mean tiles, ragged last point tile, odd number of tiles
+    (4224, 300, 20, 0),       # k padded to 512: masked columns; dim padded to 32
+    (3000, 700, 12, 1),       # 16-float rows: one-CTA kernel either way
+    (130, 1000, 17, 0),       # fewer point tiles than SMs
+])
+def test_tc_pair_kernel_matches_single_cta_kernel(pkg, torch_cuda, oracle_mod, workloads, n, k, d, layout):
+    """The CTA-pair tensor-core kernel and the one-CTA kernel must both give the oracle's
+    assignment (bit-exact) for the same means."""
+    rows = workloads.generate_rows("mixture", n, d, 64, seed=11, sigma=0.05)
+    rng = np.random.default_rng(3)
+    mrows = np.ascontiguousarray(rows[rng.choice(n, k, replace=k > n)])
+    data, means = workloads.to_layout(rows, layout), workloads.to_layout(mrows, layout)
+    want = oracle_mod.assign(data, means, n, k, d, layout, layout, threads=8)
+    for pair in (0, 1):
+        km = pkg.KMeans(layout=layout, variant_assign=pkg.ASSIGN_TC)
+        km.initialize(d, k, n, 1, data, means)
+        km.set_option("tc_pair", pair)
+        km.set_option("use_graph", 0)
+        km.run(1)
+        got = km.getAssignment()
+        km.cleanup()
+        assert np.array_equal(got, want), (pair, int((got != want).sum()))
+
+
 def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
     """Headline configuration at full size: conservation laws + a sampled oracle check."""
     data, means, spec = workloads.make("c2")
