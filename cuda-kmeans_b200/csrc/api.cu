@@ -229,9 +229,11 @@ int check_shape(uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_mea
 }
 
 // Enqueues one assignment pass (fast pass + exact re-check, or the exact kernel alone).
+// With `fused` set the tensor-core pass also accumulates the update sums and the re-check moves
+// the points it reassigns, so no update pass must follow.
 int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* asg, const bkm::Shape& s,
 	const Workspace& w, int slot, bkm::TcPlan* plan, float margin_scale, int sm_count, cudaStream_t stream,
-	cudaEvent_t mid)
+	cudaEvent_t mid, const bkm::FusedAcc* fused = nullptr)
 {
 	if (variant == BKM_ASSIGN_EXACT) {
 		CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, nullptr, nullptr, sm_count, stream));
@@ -241,10 +243,10 @@ int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* 
 	if (variant == BKM_ASSIGN_SIMT) {
 		CUDA_TRY(bkm::launch_assign_simt(pts, w.cprep, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream));
 	} else {
-		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream));
+		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream, fused));
 	}
 	if (mid) CUDA_TRY(cudaEventRecord(mid, stream));
-	CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, w.flag_list, &w.ctl->flag_count, sm_count, stream));
+	CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, w.flag_list, &w.ctl->flag_count, sm_count, stream, fused));
 	return BKM_OK;
 }
 
@@ -284,6 +286,8 @@ struct bkm_handle_s {
 	// CUDA graph of two iterations (launch-bound problem sizes)
 	int use_graph = 2;                 // 0 = never, 1 = always (single GPU), 2 = by problem size
 	bool tc_pair = true;               // let the tensor-core assignment use its CTA-pair kernel where it applies
+	bool fuse_update = true;           // let that kernel accumulate the update sums (no separate update pass)
+	bool last_fused = false;
 	cudaGraphExec_t graph_exec = nullptr;
 	int graph_cur = 0, graph_slot = 0;
 	cudaStream_t graph_stream = nullptr;
@@ -531,6 +535,11 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value)
 		drop_graph(h);
 		return BKM_OK;
 	}
+	if (!strcmp(name, "fuse_update")) {
+		h->fuse_update = value != 0.0;
+		drop_graph(h);
+		return BKM_OK;
+	}
 	if (!strcmp(name, "tc_pair")) {
 		h->tc_pair = value != 0.0;
 		bkm::tc_plan_allow_pair(h->plan, h->tc_pair);
@@ -614,11 +623,19 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 	const size_t kd = (size_t)s.k * s.dim;
 	const int next = h->cur ^ 1;
 	if (ev) CUDA_TRY(cudaEventRecord(ev[0], st));
+	// The CTA-pair tensor-core pass can add every point to its cluster's sum on the way (the
+	// accumulators are zero between iterations: the finalize pass clears what it has read).
+	bkm::FusedAcc fa{h->ws.acc, h->ws.counts, h->ws.replicas, bkm::acc_replica_stride(s.k, s.dim), h->ws.tm.center};
+	const bool fused = h->fuse_update && h->assign_variant == BKM_ASSIGN_TC && bkm::tc_plan_can_fuse(h->plan, fa) &&
+		(size_t)s.dim * sizeof(float) * 4 <= 120 * 1024;
+	h->last_fused = fused;
+	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + (fused ? 0u : 1u) + 1u;
 	int rc = enqueue_assign(h->assign_variant, h->d_points, h->d_means[h->cur], h->d_asg, s, h->ws, h->slot,
-		h->plan, h->margin_scale, h->sm_count, st, ev ? ev[1] : nullptr);
+		h->plan, h->margin_scale, h->sm_count, st, ev ? ev[1] : nullptr, fused ? &fa : nullptr);
 	if (rc) return rc;
 	if (ev) CUDA_TRY(cudaEventRecord(ev[2], st));
-	bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, h->ws.replicas, s, h->update_variant, h->ws.ctl, h->sm_count, st);
+	if (!fused)
+		bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, h->ws.replicas, s, h->update_variant, h->ws.ctl, h->sm_count, st);
 	if (ev) CUDA_TRY(cudaEventRecord(ev[3], st));
 	if (h->comm) {
 		bkm::launch_merge_replicas(h->ws.acc, h->ws.counts, h->ws.replicas, s, st);
@@ -802,7 +819,7 @@ int bkm_counters(bkm_handle_t h, uint64_t out[4])
 	out[0] = c.last_flag_count;
 	out[1] = h->launches_per_iter;
 	out[2] = (uint64_t)h->assign_variant;
-	out[3] = (uint64_t)h->update_variant;
+	out[3] = h->last_fused ? (uint64_t)BKM_UPDATE_FUSED : (uint64_t)h->update_variant;
 	return BKM_OK;
 }
 

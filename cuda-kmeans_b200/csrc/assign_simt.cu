@@ -78,9 +78,11 @@ constexpr int LIST_PB = 4;
 template<bool SOA, bool SOAM>
 __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const float* __restrict__ pts,
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
-	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
+	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count,
+	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts)
 {
 	extern __shared__ float sx[];                       // LIST_PB points (dpad floats each), then the means tile
+	__shared__ uint32_t smoved[LIST_PB][2];             // (old, new) cluster of a point that changed, else old == new
 	const uint32_t dpad = (d + 3) & ~3u;
 	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + (size_t)LIST_PB * dpad);
 	__shared__ float sbest[LIST_PB][LIST_THREADS / 32];
@@ -163,21 +165,40 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 				const uint32_t oi = sidx[tid][v];
 				if (oi != 0xffffffffu && (bi == 0xffffffffu || ob < b || (ob == b && oi < bi))) { b = ob; bi = oi; }
 			}
-			asg[list[w0 + tid]] = bi;
+			const uint32_t i = list[w0 + tid];
+			smoved[tid][0] = fix_acc ? asg[i] : bi;
+			smoved[tid][1] = bi;
+			asg[i] = bi;
+		}
+		if (fix_acc) {
+			// the fast pass has already added these points to the sums of the clusters it picked
+			__syncthreads();
+			for (uint32_t p = 0; p < np; ++p) {
+				const uint32_t from = smoved[p][0], to = smoved[p][1];
+				if (from == to || from >= k) continue;
+				for (uint32_t j = tid; j < d; j += LIST_THREADS) {
+					const float x = sx[p * dpad + j];
+					atomicAdd(&fix_acc[(size_t)from * d + j], -x);
+					atomicAdd(&fix_acc[(size_t)to * d + j], x);
+				}
+				if (tid == 0) { atomicSub(&fix_counts[from], 1u); atomicAdd(&fix_counts[to], 1u); }
+			}
 		}
 	}
 }
 
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
-	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix)
 {
+	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
 		const size_t lsmem = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float) + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
 		const uint32_t lgrid = (uint32_t)sm_count * 8;
 #define BKM_LAUNCH_LIST(SOA, SOAM) do { \
 		auto kern = assign_exact_list_kernel<SOA, SOAM>; \
 		if (lsmem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lsmem); if (e != cudaSuccess) return e; } \
-		kern<<<lgrid, LIST_THREADS, lsmem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count); \
+		kern<<<lgrid, LIST_THREADS, lsmem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count, \
+			fix ? fix->acc : nullptr, fix ? fix->counts : nullptr); \
 	} while (0)
 		if (s.soa && s.soa_means) BKM_LAUNCH_LIST(true, true);
 		else if (s.soa && !s.soa_means) BKM_LAUNCH_LIST(true, false);

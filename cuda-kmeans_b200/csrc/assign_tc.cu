@@ -673,10 +673,19 @@ bool tc_plan_uses_pair(const TcPlan* plan) { return plan && plan->pair_ok && pla
 
 void tc_plan_destroy(TcPlan* plan) { delete plan; }
 
+// The pair kernel can accumulate the update sums when a point's row can go out as 128-bit vector
+// reductions: dim a multiple of 4 and 16-byte aligned accumulators.
+bool tc_plan_can_fuse(const TcPlan* p, const FusedAcc& f)
+{
+	return tc_plan_uses_pair(p) && p->s.dim % 4 == 0 && f.acc != nullptr && f.counts != nullptr && f.center != nullptr &&
+		(reinterpret_cast<uintptr_t>(f.acc) & 15u) == 0 && (f.rep_stride * sizeof(float)) % 16 == 0;
+}
+
 cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
-	float margin_scale, cudaStream_t stream)
+	float margin_scale, cudaStream_t stream, const FusedAcc* fused)
 {
 	if (!p) return cudaErrorInvalidValue;
+	if (fused && !tc_plan_can_fuse(p, *fused)) return cudaErrorInvalidValue;
 	const uint32_t n_tiles = (uint32_t)(p->tp.n_pad / TC_MTILE);
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
@@ -688,7 +697,7 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t idesc = p->idesc;
 	if (tc_plan_uses_pair(p))
 		return launch_assign_tc_pair(p->a_hi, p->a_lo, p->bh_hi, p->bh_lo, p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles,
-			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream);
+			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim);
 	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
 		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,
 		ctl, slot, flag_list, margin_coef);

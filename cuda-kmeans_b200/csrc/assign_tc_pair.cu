@@ -28,7 +28,8 @@ namespace bkm {
 
 constexpr uint32_t P2_AAUG_OFF = 208 * 1024;                      // constant ones tile (128 rows x one K step)
 constexpr uint32_t P2_MERGE_OFF = P2_AAUG_OFF + TC_MTILE * 8 * 4;
-constexpr uint32_t P2_MERGE_BYTES = 2 * 3 * 3 * TC_MTILE * 4;     // two slots x column parts 1..3 x (best, second, chunk)
+constexpr uint32_t P2_MERGE_BYTES = 2 * 3 * 3 * TC_MTILE * 4      // two slots x column parts 1..3 x (best, second, chunk)
+	+ 2 * TC_MTILE * 4;                                            // two slots of final clusters (fused update sums)
 constexpr uint32_t P2_BAR_OFF = P2_MERGE_OFF + P2_MERGE_BYTES;
 constexpr uint32_t P2_TOTAL = P2_BAR_OFF + 256;
 constexpr uint32_t P2_ALLOC = P2_TOTAL + 1024;                    // slack for 1024-byte alignment
@@ -65,6 +66,11 @@ bool assign_tc_pair_supported(uint32_t k, uint32_t k_pad, uint32_t d_pad, uint32
 	return a_off + 2 * (2 * TC_MTILE * kw * 4) <= P2_AAUG_OFF;
 }
 
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d)
+{
+	asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // Like wait_or_abort, and a wait that runs out also raises the flag of the other CTA.
 __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t peer_abort_addr)
 {
@@ -85,7 +91,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
 	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
 	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t n_ctiles, uint32_t kw, uint32_t ksteps, uint32_t idesc,
-	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef)
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef,
+	float* __restrict__ fuse_acc, uint32_t* __restrict__ fuse_counts, const float* __restrict__ center, uint32_t dim)
 {
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -110,7 +117,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	if (threadIdx.x == 0) {
 		for (uint32_t i = 0; i < P2_NA_MAX; ++i) {
 			ptx::mbar_init(&bars->a_full[i], 1);
-			ptx::mbar_init(&bars->a_empty[i], 1);
+			// the MMAs that read the tile and, when the update sums are accumulated here, the
+			// epilogue warps that read it again at the end of the step
+			ptx::mbar_init(&bars->a_empty[i], fuse_acc ? 1 + TC_EPI_WARPS : 1);
 		}
 		ptx::mbar_init(&bars->b_full, 1);
 		for (uint32_t i = 0; i < P2_ACCS; ++i) {
@@ -123,6 +132,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	if (warp == 1) {
 		ptx::tmem_alloc_pair(&bars->tmem_slot, TC_TMEM_COLS);
 		ptx::tmem_relinquish_pair();
+	}
+	if (fuse_acc) {
+		// pairs spread over the copies of the accumulators so that fewer reductions meet on a line
+		const size_t rep_stride = acc_replica_stride(k, dim);
+		const uint32_t rep = pair % acc_replicas(k, dim);
+		fuse_acc += rep * rep_stride;
+		fuse_counts += rep * rep_stride;
 	}
 	const float x2max = ctl->xmax2, c2max = ctl->cmax2[slot];
 	const KeyConsts kc = make_key_consts(x2max, c2max);
@@ -265,6 +281,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 		const uint32_t acc_empty_addr = ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[g]), 0);
 		uint32_t it = 0, c = 0;
 		bool ok = true;
+		// Fused update sums.  The 32 points of this quarter stay in the point tile (tf32 hi + lo of
+		// the centred coordinates) after their step.  Eight lanes cover one point's row with a
+		// 128-bit vector reduction each, so one instruction of a warp sends four full rows; the
+		// four warps of the quarter take eight points each.  A warp sends them after its first
+		// accumulator of the following step: the warps reach that point one accumulator fill after
+		// another, which keeps the SM's reduction path from being hit by all of them at once, and
+		// the tile buffer is handed back to the loader when the last of them has read it.
+		bool pending = false;
+		uint32_t pend_it = 0;
+		auto flush_sums = [&]() {
+			const uint32_t* s_mine = mg_state + 2 * 3 * 3 * TC_MTILE + (pend_it & 1u) * TC_MTILE;
+			const uint8_t* tile_hi = smem + a_off + (pend_it % n_abuf) * a_tile;
+			const uint32_t sub = lane >> 3, c4 = lane & 7u;
+			const bool dims_ok = c4 * 4 < dim;
+			float4 cen = make_float4(0.f, 0.f, 0.f, 0.f);
+			if (dims_ok) cen = reinterpret_cast<const float4*>(center)[c4];
+			#pragma unroll
+			for (uint32_t r4 = 0; r4 < 2; ++r4) {
+				const uint32_t trow = q * 32 + g * 8 + r4 * 4 + sub;
+				const uint32_t a = s_mine[trow];
+				const uint32_t off = trow * 128u + ((c4 ^ (trow & 7u)) << 4);     // 128-byte swizzle
+				if (a != 0xFFFFFFFFu && dims_ok) {
+					const float4 hi = *reinterpret_cast<const float4*>(tile_hi + off);
+					const float4 lo = *reinterpret_cast<const float4*>(tile_hi + a_plane + off);
+					red_add_v4(&fuse_acc[(size_t)a * dim + c4 * 4], (hi.x + lo.x) + cen.x, (hi.y + lo.y) + cen.y,
+						(hi.z + lo.z) + cen.z, (hi.w + lo.w) + cen.w);
+				}
+			}
+			__syncwarp();
+			if (lane == 0) ptx::mbar_arrive(&bars->a_empty[pend_it % n_abuf]);
+			pending = false;
+		};
 #ifdef BKM_TC_TIMING
 		long long e_wait = 0, e_work = 0, e_merge = 0;
 		const long long e_start = clock64();
@@ -317,9 +365,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 					__syncwarp();
 					if (lane == 0) ptx::mbar_arrive_cluster(acc_empty_addr);
 				}
+				if (pending) flush_sums();
 				TC_T(e2);
 				TC_ACC(e_work, e1, e2);
 			}
+			if (pending) flush_sums();                    // a step without an accumulator for this warp
 			TC_T(e3);
 			// Warps 1..3 of a quarter hand their state to warp 0 through shared memory.  The slots
 			// alternate with the step count, so one barrier per step is enough: a slot is written again
@@ -330,6 +380,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				dst[row] = best; dst[TC_MTILE + row] = second; dst[2 * TC_MTILE + row] = bchunk;
 			}
 			asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");   // the four warps that share these 32 rows
+			uint32_t mine = 0xFFFFFFFFu;                  // cluster of this thread's point (warps with g == 0)
 			if (g == 0 && p < n && ok) {
 				#pragma unroll
 				for (uint32_t o = 0; o < 3; ++o) {
@@ -341,7 +392,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				}
 				// key - key_base = M * mantissa + column
 				const uint32_t bm = (best - key_base) / key_mult;
-				asg[p] = bchunk * 32u + ((best - key_base) - bm * key_mult);
+				mine = bchunk * 32u + ((best - key_base) - bm * key_mult);
+				asg[p] = mine;
 				const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
 				const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
 				if (gap <= margin) {
@@ -350,9 +402,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
 				}
 			}
+			if (fuse_acc != nullptr) {
+				// Update sums: the final clusters go to shared memory; the reductions themselves are
+				// sent later (flush_sums), spread over the next step.
+				uint32_t* s_mine = mg_state + 2 * 3 * 3 * TC_MTILE + (it & 1u) * TC_MTILE;
+				if (g == 0) {
+					s_mine[row] = mine;
+					if (mine != 0xFFFFFFFFu) atomicAdd(&fuse_counts[mine], 1u);
+				}
+				asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");
+				pending = true;
+				pend_it = it;
+			}
 			TC_T(e4);
 			TC_ACC(e_merge, e3, e4);
 		}
+		if (pending) flush_sums();
 #ifdef BKM_TC_TIMING
 		if ((blockIdx.x == 6 || blockIdx.x == 7) && lane == 0 && (warp == 2 || warp == 7 || warp == 12 || warp == 17))
 			printf("pair epi cta %u warp %u: total %lld  wait %lld  work %lld  merge %lld\n", blockIdx.x, warp, clock64() - e_start, e_wait, e_work, e_merge);
@@ -396,7 +461,8 @@ cudaError_t assign_tc_pair_prepare(int* max_pairs)
 
 cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_lo, const CUtensorMap& b_hi, const CUtensorMap& b_lo,
 	const float* b_aug, const float* xnorm, uint32_t* asg, uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t d_pad,
-	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream)
+	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream,
+	const FusedAcc* fused, uint32_t dim)
 {
 	const uint32_t kw = d_pad == 16 ? 16u : TC_KCHUNK;
 	const uint32_t n_ctiles = k_pad / TC_NT_MAX;
@@ -405,7 +471,8 @@ cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_
 	// c_format = f32 (bit 4), a/b format = tf32 (bits 7.., 10..), K-major both, N>>3 at bit 17, M>>4 at bit 24: M = 256 over the pair, N = 128
 	const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((P2_UNIT_COLS >> 3) << 17) | (((2 * TC_MTILE) >> 4) << 24);
 	assign_tc_pair_kernel<<<2 * pairs, TC_THREADS, P2_ALLOC, stream>>>(a_hi, a_lo, b_hi, b_lo, b_aug, xnorm, asg,
-		n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef);
+		n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef,
+		fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim);
 	return cudaGetLastError();
 }
 

@@ -59,8 +59,18 @@ void launch_merge_replicas(float* acc, uint32_t* counts, uint32_t replicas, cons
 
 // ---- assignment on CUDA cores (assign_simt.cu) ----
 // Exact reference arithmetic.  With list != null only the points list[0..*list_count) are done.
+// With `fix` set (list form only) the kernel also moves every point whose cluster changed from
+// its old cluster's sum and size to the new one's - the correction that goes with an assignment
+// pass which has already accumulated the update sums (FusedAcc below).
+struct FusedAcc {
+	float* acc;           // [replicas][k*dim sums | k sizes], replica stride in 32-bit words
+	uint32_t* counts;
+	uint32_t replicas;
+	size_t rep_stride;
+	const float* center;  // the vector the split operands were centred by
+};
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
-	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream);
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix = nullptr);
 
 // Small-d fast pass (dim <= 8): approximate distances, near-ties appended to flag_list.
 bool assign_simt_supported(const Shape& s);
@@ -82,7 +92,11 @@ void tc_plan_destroy(TcPlan* plan);
 // The CTA-pair kernel (means resident in shared memory) is used where it applies unless disallowed.
 void tc_plan_allow_pair(TcPlan* plan, bool allow);
 bool tc_plan_uses_pair(const TcPlan* plan);
+// With `fused` set (allowed when tc_plan_can_fuse) the kernel also adds every point to the sum and
+// the size of the cluster it picked, so that no separate update pass is needed; points that the
+// exact re-check moves afterwards are corrected there.
+bool tc_plan_can_fuse(const TcPlan* plan, const FusedAcc& f);
 cudaError_t launch_assign_tc(TcPlan* plan, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
-	float margin_scale, cudaStream_t stream);
+	float margin_scale, cudaStream_t stream, const FusedAcc* fused = nullptr);
 
 } // namespace bkm

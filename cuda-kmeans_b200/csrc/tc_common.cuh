@@ -5,6 +5,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "kernels.cuh"
 #include "ptx.cuh"
 
 // Optional stage timing for development builds (-DBKM_TC_TIMING): one CTA prints how its MMA warp
@@ -200,6 +201,7 @@ bool assign_tc_pair_supported(uint32_t k, uint32_t k_pad, uint32_t d_pad, uint32
 cudaError_t assign_tc_pair_prepare(int* max_pairs);
 cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_lo, const CUtensorMap& b_hi, const CUtensorMap& b_lo,
 	const float* b_aug, const float* xnorm, uint32_t* asg, uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t d_pad,
-	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream);
+	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream,
+	const FusedAcc* fused, uint32_t dim);
 
 } // namespace bkm

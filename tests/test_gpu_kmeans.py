@@ -139,6 +139,34 @@ def test_tc_pair_kernel_matches_single_cta_kernel(pkg, torch_cuda, oracle_mod, w
         assert np.array_equal(got, want), (pair, int((got != want).sum()))
 
 
+@pytest.mark.parametrize("n,k,d,layout", [(20000, 1024, 32, 1), (4224, 300, 20, 0), (777, 512, 24, 1)])
+def test_fused_update_matches_separate_update(pkg, torch_cuda, oracle_mod, workloads, n, k, d, layout):
+    """The CTA-pair kernel can accumulate the update sums itself; means, sizes and assignment must
+    agree with the run that uses the separate update pass, and with the oracle step by step."""
+    rows = workloads.generate_rows("mixture", n, d, 64, seed=13, sigma=0.05)
+    data, means = workloads.to_layout(rows, layout), workloads.to_layout(np.ascontiguousarray(rows[:k]), layout)
+    outs = []
+    for fuse in (1, 0):
+        km = pkg.KMeans(layout=layout, variant_assign=pkg.ASSIGN_TC)
+        km.initialize(d, k, n, 3, data, means)
+        km.set_option("fuse_update", fuse)
+        km.set_option("use_graph", 0)
+        prev = np.asarray(means, dtype=np.float32).reshape(-1).copy()
+        for it in range(3):
+            km.run(1)
+            asg, cur, sizes = km.getAssignment(), km.getMeans(), km.getSizes()
+            want_asg = oracle_mod.assign(data, prev, n, k, d, layout, layout, threads=8)
+            assert np.array_equal(asg, want_asg), (fuse, it, int((asg != want_asg).sum()))
+            want, want_sizes = oracle_mod.update(data, asg, n, k, d, layout, layout)
+            assert np.array_equal(sizes, want_sizes), (fuse, it)
+            ok, err = means_close(cur, want)
+            assert ok, (fuse, it, err)
+            prev = cur
+        assert km.counters()["update_variant"] == ("fused" if fuse else "rows")
+        outs.append(prev)
+        km.cleanup()
+
+
 def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
     """Headline configuration at full size: conservation laws + a sampled oracle check."""
     data, means, spec = workloads.make("c2")
