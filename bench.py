@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--scaling", default=None, choices=[None, "weak", "strong"])
     ap.add_argument("--n", type=int, default=None, help="override the number of points (per job)")
     ap.add_argument("--assign", default="auto", choices=["auto", "exact", "simt", "tc"])
-    ap.add_argument("--update", default="auto", choices=["auto", "shared", "global", "rows"])
+    ap.add_argument("--update", default="auto", choices=["auto", "shared", "global", "rows", "sorted"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seed", type=int, default=42)
@@ -265,7 +265,7 @@ def main():
     dev_means = host_means.to("cuda")
 
     va = {"auto": 0, "exact": 1, "simt": 2, "tc": 3}[args.assign]
-    vu = {"auto": 0, "shared": 1, "global": 2, "rows": 3}[args.update]
+    vu = {"auto": 0, "shared": 1, "global": 2, "rows": 3, "sorted": 5}[args.update]
     km = pkg.KMeans(layout=lay, layout_means=laym, device=local_rank, variant_assign=va, variant_update=vu)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)

@@ -23,8 +23,9 @@ ASSIGN_AUTO, ASSIGN_EXACT, ASSIGN_SIMT, ASSIGN_TC = 0, 1, 2, 3
 UPDATE_AUTO, UPDATE_SHARED, UPDATE_GLOBAL, UPDATE_ROWS = 0, 1, 2, 3
 ASSIGN_NAMES = {ASSIGN_AUTO: "auto", ASSIGN_EXACT: "exact", ASSIGN_SIMT: "simt", ASSIGN_TC: "tc"}
 UPDATE_FUSED = 4   # reported by counters() only
+UPDATE_SORTED = 5
 UPDATE_NAMES = {UPDATE_AUTO: "auto", UPDATE_SHARED: "shared", UPDATE_GLOBAL: "global", UPDATE_ROWS: "rows",
-                UPDATE_FUSED: "fused"}
+                UPDATE_FUSED: "fused", UPDATE_SORTED: "sorted"}
 
 # Every symbol include/bkm.h declares (the CPU test suite checks the library exports them all).
 SYMBOLS = [

@@ -198,11 +198,18 @@ int resolve_update(int variant, const bkm::Shape& s, int device, int* out)
 {
 	switch (variant) {
 	case BKM_UPDATE_AUTO:
-		// rows of at least 16 floats: one coalesced L2 reduction per point beats shared-memory atomics
-		if (s.dim >= 16) *out = BKM_UPDATE_ROWS;
+		// row-major points: sort by cluster inside the block, one reduction per cluster and chunk;
+		// dimension-major points: rows of at least 16 floats go out as one coalesced L2 reduction
+		// per point, shorter ones through shared-memory buckets
+		if (!s.soa && bkm::update_sorted_supported(s)) *out = BKM_UPDATE_SORTED;
+		else if (s.dim >= 16) *out = BKM_UPDATE_ROWS;
 		else *out = bkm::update_shared_fits(s, device) ? BKM_UPDATE_SHARED : BKM_UPDATE_GLOBAL;
 		return BKM_OK;
 	case BKM_UPDATE_ROWS:
+		*out = variant;
+		return BKM_OK;
+	case BKM_UPDATE_SORTED:
+		if (!bkm::update_sorted_supported(s)) return fail(BKM_ERR_UNSUPPORTED, "the sorted update handles at most 1024 clusters (k=%u)", s.k);
 		*out = variant;
 		return BKM_OK;
 	case BKM_UPDATE_SHARED:
@@ -626,7 +633,10 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 	// The CTA-pair tensor-core pass can add every point to its cluster's sum on the way (the
 	// accumulators are zero between iterations: the finalize pass clears what it has read).
 	bkm::FusedAcc fa{h->ws.acc, h->ws.counts, h->ws.replicas, bkm::acc_replica_stride(s.k, s.dim), h->ws.tm.center};
-	const bool fused = h->fuse_update && h->assign_variant == BKM_ASSIGN_TC && bkm::tc_plan_can_fuse(h->plan, fa) &&
+	// (worth it where the update would otherwise be the row-wise kernel; the sorted update of
+	// row-major points costs less than the reductions cost inside the assignment kernel)
+	const bool fused = h->fuse_update && h->assign_variant == BKM_ASSIGN_TC && h->update_variant == BKM_UPDATE_ROWS &&
+		bkm::tc_plan_can_fuse(h->plan, fa) &&
 		(size_t)s.dim * sizeof(float) * 4 <= 120 * 1024;
 	h->last_fused = fused;
 	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + (fused ? 0u : 1u) + 1u;

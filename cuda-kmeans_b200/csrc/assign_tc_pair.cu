@@ -354,11 +354,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 						const uint32_t col0 = chunk0 * 32u;
 						const uint32_t left = k > col0 ? k - col0 : 0u;      // columns at or behind k are padding
 						if (left >= 64) {
-							chunk_update<false>(v0, key_mult, kc.one, chunk0, 32, best, second, bchunk);
-							chunk_update<false>(v1, key_mult, kc.one, chunk0 + 1, 32, best, second, bchunk);
+							chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
+							chunk_update<false>(v1, key_mult, chunk0 + 1, 32, best, second, bchunk);
 						} else {
-							if (left > 0) chunk_update<true>(v0, key_mult, kc.one, chunk0, left, best, second, bchunk);
-							if (left > 32) chunk_update<true>(v1, key_mult, kc.one, chunk0 + 1, left - 32, best, second, bchunk);
+							if (left > 0) chunk_update<true>(v0, key_mult, chunk0, left, best, second, bchunk);
+							if (left > 32) chunk_update<true>(v1, key_mult, chunk0 + 1, left - 32, best, second, bchunk);
 						}
 					}
 				} else {

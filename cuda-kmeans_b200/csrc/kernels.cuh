@@ -52,6 +52,7 @@ void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* mea
 // variant: BKM_UPDATE_SHARED or BKM_UPDATE_GLOBAL (already resolved).  acc/counts must be zero.
 // Returns false when the shared variant cannot hold k*dim in shared memory.
 bool update_shared_fits(const Shape& s, int device);
+bool update_sorted_supported(const Shape& s);
 void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, uint32_t replicas, const Shape& s,
 	int variant, Control* ctl, int sm_count, cudaStream_t stream);
 // Folds accumulator replicas 1.. into replica 0 (before an all-reduce of replica 0).

@@ -77,27 +77,6 @@ __device__ __forceinline__ uint64_t make_desc_aug(uint32_t smem_addr)
 
 __device__ __forceinline__ uint32_t umin3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_u32(a, b, c); }
 
-// Smallest and second-smallest of 32 keys by a tournament: 16 (min,max) pairs, then 15 merges
-// (b,s) x (b',s') -> (min(b,b'), min(max(b,b'), s, s')).  77 instructions, log depth.
-__device__ __forceinline__ void top2_of_32(const uint32_t (&p)[32], uint32_t& b, uint32_t& s)
-{
-	uint32_t lo[16], hi[16];
-	#pragma unroll
-	for (int i = 0; i < 16; ++i) { lo[i] = min(p[2 * i], p[2 * i + 1]); hi[i] = max(p[2 * i], p[2 * i + 1]); }
-	#pragma unroll
-	for (int n = 16; n > 1; n >>= 1) {
-		#pragma unroll
-		for (int i = 0; i < n / 2; ++i) {
-			const uint32_t nb = min(lo[2 * i], lo[2 * i + 1]);
-			const uint32_t ns = umin3(max(lo[2 * i], lo[2 * i + 1]), hi[2 * i], hi[2 * i + 1]);
-			lo[i] = nb;
-			hi[i] = ns;
-		}
-	}
-	b = lo[0];
-	s = hi[0];
-}
-
 // One 32-column chunk of an accumulator row.  The kernel adds a constant to every value so that
 // all of them are positive floats with the SAME exponent; their bit patterns then order like the
 // values, the upper exponent bits carry no information, and bits * M + column (M odd, > column:
@@ -119,7 +98,7 @@ __device__ __forceinline__ uint32_t min_of_32(const uint32_t (&p)[32])
 }
 
 template<bool MASKED>
-__device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t key_mult, uint32_t one, uint32_t chunk_id, uint32_t nvalid,
+__device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t key_mult, uint32_t chunk_id, uint32_t nvalid,
 	uint32_t& best, uint32_t& second, uint32_t& best_chunk)
 {
 	uint32_t p[32];
@@ -129,22 +108,22 @@ __device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t k
 		#pragma unroll
 		for (uint32_t t = 0; t < 32; ++t) p[t] = t < nvalid ? p[t] : 0xFFFFFFFFu;
 	}
-#ifdef BKM_TOP2_TOURNAMENT
-	uint32_t b, s2;
-	top2_of_32(p, b, s2);
-#else
-	// Two passes of plain minima instead of one (best, second) tournament.  The keys are distinct
+	// Two passes of plain minima instead of a (best, second) tournament.  The keys are distinct
 	// (they carry the column), so key - (smallest + 1) wraps to the top of the unsigned range for
 	// the smallest key only, and the minimum of these differences belongs to the second smallest.
-	// 32 + 5 min/max instructions instead of 77 + 5; the subtractions are split between the two
-	// integer pipes (`one` is 1 at run time, unknown to the compiler: a multiply-add stays a
-	// multiply-add).
+	// The second pass is 32 fused add-and-minimum instructions in four independent chains;
+	// 16 + 32 + 8 integer instructions per chunk where a tournament takes 77 + 5.
 	const uint32_t b = min_of_32(p);
 	const uint32_t nb1 = ~b;                       // -(b + 1)
+	uint32_t r0 = 0xFFFFFFFFu, r1 = 0xFFFFFFFFu, r2 = 0xFFFFFFFFu, r3 = 0xFFFFFFFFu;
 	#pragma unroll
-	for (uint32_t t = 0; t < 32; ++t) p[t] = (t & 1u) ? p[t] * one + nb1 : p[t] + nb1;
-	const uint32_t s2 = min_of_32(p) - nb1;        // + (b + 1); a lone valid key gives 0xFFFFFFFF again
-#endif
+	for (uint32_t t = 0; t < 32; t += 4) {
+		r0 = __viaddmin_u32(p[t], nb1, r0);
+		r1 = __viaddmin_u32(p[t + 1], nb1, r1);
+		r2 = __viaddmin_u32(p[t + 2], nb1, r2);
+		r3 = __viaddmin_u32(p[t + 3], nb1, r3);
+	}
+	const uint32_t s2 = min(umin3(r0, r1, r2), r3) - nb1;      // + (b + 1); a lone valid key gives 0xFFFFFFFF again
 	second = umin3(second, max(best, b), s2);
 	best_chunk = b < best ? chunk_id : best_chunk;
 	best = min(best, b);
@@ -157,7 +136,6 @@ struct KeyConsts {
 	float offset_c;      // constant added to every |c|^2 - 2 x.c by the extra K step
 	uint32_t key_mult;   // M
 	uint32_t key_base;   // M * (bit pattern of P) mod 2^32
-	uint32_t one;        // the number 1, computed so that the compiler cannot know it
 };
 
 // Offset constant: every value |c|^2 - 2 x.c lies in [-X2, X2 + 2*C2] (X2, C2 = largest |x|^2,
@@ -180,7 +158,6 @@ __device__ __forceinline__ KeyConsts make_key_consts(float x2max, float c2max)
 	const uint32_t eb = __float_as_uint(kc.pow2) >> 23;
 	while (kc.key_mult < 63 && ((kc.key_mult * eb) & 511u) > 510u - kc.key_mult) kc.key_mult += 2;
 	kc.key_base = kc.key_mult * __float_as_uint(kc.pow2);
-	kc.one = x2max < -1.0f ? 3u : 1u;       // a sum of squares is never negative
 	return kc;
 }
 

@@ -22,6 +22,16 @@
 
 namespace bkm {
 
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b)
+{
+	asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" :: "l"(addr), "f"(a), "f"(b) : "memory");
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d)
+{
+	asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 constexpr int UPD_THREADS = 512;
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
@@ -306,10 +316,6 @@ __global__ void __launch_bounds__(UPD_THREADS) update_kernel(const float* __rest
 // that the rows rarely collide; the per-cluster sizes go to global integer atomics.
 constexpr int ROWS_THREADS = 256;
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d)
-{
-	asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 // VEC: dim is a multiple of 4 and the buffers are 16-byte aligned, so that 8 lanes cover a
 // 32-dimension slice with one 128-bit vector reduction each and a warp handles 4 points per
@@ -386,6 +392,208 @@ __global__ void __launch_bounds__(ROWS_THREADS) update_rows_kernel(const float* 
 	if (bad) atomicOr(&ctl->status, (uint32_t)STATUS_BAD_INDEX);
 }
 
+// ------------------------------------------------------------------------------------------
+// update for few clusters: block-local counting sort, then one reduction per (cluster, chunk)
+// ------------------------------------------------------------------------------------------
+//
+// With few clusters every global or shared-memory reduction of the row-wise kernels lands on
+// one of a few hundred hot rows, and the memory system serialises them.  Here a block takes a
+// chunk of SORT_CHUNK consecutive points and sorts their positions by cluster in shared memory
+// (histogram, prefix sum, scatter).  Groups of `dg` lanes (one lane per dimension) then walk
+// equal shares of the sorted order, adding rows into a register while the cluster stays the
+// same and sending one row of reductions when it changes.  The number of reductions drops by
+// about the number of points per cluster and chunk (8 for 256 clusters), and the sums reach the
+// accumulators pre-added in a fixed small tree, which also keeps the rounding error down.
+
+constexpr uint32_t SORT_THREADS = 256;
+constexpr uint32_t SORT_CHUNK = 2048;
+constexpr uint32_t SORT_PER_THREAD = SORT_CHUNK / SORT_THREADS;
+constexpr uint32_t SORT_MAX_K = 1024;
+constexpr uint32_t SORT_SCAN = (SORT_MAX_K + 1 + SORT_THREADS - 1) / SORT_THREADS;   // buckets per thread in the scan
+
+bool update_sorted_supported(const Shape& s) { return s.k <= SORT_MAX_K; }
+
+template<bool SOA, int VW>
+__global__ void __launch_bounds__(SORT_THREADS) update_sorted_kernel(const float* __restrict__ pts,
+	const uint32_t* __restrict__ asg, float* __restrict__ acc, uint32_t* __restrict__ counts,
+	uint64_t n, uint32_t k, uint32_t d, uint32_t dg, uint32_t replicas, size_t rep_stride, Control* __restrict__ ctl)
+{
+	acc += (blockIdx.x % replicas) * rep_stride;
+	counts += (blockIdx.x % replicas) * rep_stride;
+	__shared__ uint32_t start[SORT_MAX_K + 2];      // after the scan: first sorted position of each cluster (k = trash bucket)
+	__shared__ __align__(8) uint16_t order[SORT_CHUNK];     // sorted position -> point within the chunk
+	__shared__ __align__(8) uint16_t cl_sorted[SORT_CHUNK]; // sorted position -> cluster
+	__shared__ uint32_t warp_sums[SORT_THREADS / 32];
+	const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+	const uint32_t nsub = 32 / dg;                  // lane groups per warp
+	const uint32_t dl = lane % dg, sub = lane / dg;
+	const uint32_t walker = warp * nsub + sub, walkers = (SORT_THREADS / 32) * nsub;
+	const uint64_t chunks = (n + SORT_CHUNK - 1) / SORT_CHUNK;
+	bool bad = false;
+	for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+		const uint64_t base = chunk * SORT_CHUNK;
+		const uint32_t cnt = (uint32_t)(n - base < SORT_CHUNK ? n - base : SORT_CHUNK);
+		__syncthreads();                            // the previous chunk's walkers are done
+		for (uint32_t c = tid; c <= k; c += SORT_THREADS) start[c] = 0;
+		__syncthreads();
+		uint32_t mine[SORT_PER_THREAD], rank[SORT_PER_THREAD];
+		#pragma unroll
+		for (uint32_t r = 0; r < SORT_PER_THREAD; ++r) {
+			const uint32_t i = r * SORT_THREADS + tid;
+			uint32_t c = k;                         // trash bucket: beyond the chunk or a bad index
+			if (i < cnt) {
+				c = asg[base + i];
+				if (c >= k) { bad = true; c = k; }
+			}
+			mine[r] = c;
+			rank[r] = atomicAdd(&start[c], 1u);     // the histogram pass also hands out the place within the bucket
+		}
+		__syncthreads();
+		// exclusive prefix sum over k + 1 buckets: a few buckets per thread, warp scan, warp totals
+		{
+			uint32_t v[SORT_SCAN], local = 0;
+			#pragma unroll
+			for (uint32_t r = 0; r < SORT_SCAN; ++r) { const uint32_t c = tid * SORT_SCAN + r; v[r] = c <= k ? start[c] : 0; local += v[r]; }
+			uint32_t incl = local;
+			#pragma unroll
+			for (uint32_t off = 1; off < 32; off <<= 1) { const uint32_t o = __shfl_up_sync(0xffffffffu, incl, off); if (lane >= off) incl += o; }
+			if (lane == 31) warp_sums[warp] = incl;
+			__syncthreads();
+			uint32_t before = 0;
+			for (uint32_t w = 0; w < warp; ++w) before += warp_sums[w];
+			uint32_t run = before + incl - local;
+			#pragma unroll
+			for (uint32_t r = 0; r < SORT_SCAN; ++r) {
+				const uint32_t c = tid * SORT_SCAN + r;
+				if (c <= k) start[c] = run;
+				run += v[r];
+			}
+		}
+		__syncthreads();
+		// sizes straight from the histogram; scatter of the positions
+		for (uint32_t c = tid; c < k; c += SORT_THREADS) {
+			const uint32_t sz = start[c + 1] - start[c];
+			if (sz) atomicAdd(&counts[c], sz);
+		}
+		#pragma unroll
+		for (uint32_t r = 0; r < SORT_PER_THREAD; ++r) {
+			const uint32_t pos = start[mine[r]] + rank[r];
+			order[pos] = (uint16_t)(r * SORT_THREADS + tid);
+			cl_sorted[pos] = (uint16_t)mine[r];
+		}
+		__syncthreads();
+		// every lane group walks an equal, 4-aligned share of the sorted order (the trash bucket is last)
+		const uint32_t total = start[k];
+		const uint32_t share = ((total + walkers - 1) / walkers + 3) & ~3u;
+		const uint32_t w0 = min(walker * share, total), w1 = min(w0 + share, total);
+		if (VW == 4) {
+			// row-major points, dim a multiple of 4: a lane holds four dimensions
+			const float4* rows = reinterpret_cast<const float4*>(pts + (size_t)base * d);
+			const uint32_t d4 = d >> 2;
+			for (uint32_t c0 = 0; c0 < d4; c0 += dg) {
+				const uint32_t j4 = c0 + dl;
+				const bool jok = j4 < d4;
+				float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+				uint32_t cur = w0 < w1 ? cl_sorted[w0] : 0u;
+				for (uint32_t sp = w0; sp < w1; sp += 4) {
+					const uint2 o2 = *reinterpret_cast<const uint2*>(&order[sp]);
+					const uint2 c2 = *reinterpret_cast<const uint2*>(&cl_sorted[sp]);
+					const uint32_t oi[4] = {o2.x & 0xffffu, o2.x >> 16, o2.y & 0xffffu, o2.y >> 16};
+					const uint32_t ci[4] = {c2.x & 0xffffu, c2.x >> 16, c2.y & 0xffffu, c2.y >> 16};
+					float4 x[4];
+					#pragma unroll
+					for (uint32_t u = 0; u < 4; ++u) {
+						x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+						if (sp + u < w1 && jok) x[u] = rows[oi[u] * d4 + j4];
+					}
+					#pragma unroll
+					for (uint32_t u = 0; u < 4; ++u) {
+						if (sp + u < w1) {
+							if (ci[u] != cur) {
+								if (jok) red_add_v4(&acc[(size_t)cur * d + j4 * 4], sum.x, sum.y, sum.z, sum.w);
+								sum = make_float4(0.f, 0.f, 0.f, 0.f);
+								cur = ci[u];
+							}
+							sum.x += x[u].x; sum.y += x[u].y; sum.z += x[u].z; sum.w += x[u].w;
+						}
+					}
+				}
+				if (w0 < w1 && jok) red_add_v4(&acc[(size_t)cur * d + j4 * 4], sum.x, sum.y, sum.z, sum.w);
+			}
+		} else if (VW == 2) {
+			// row-major points, even dim: a lane holds two dimensions
+			const float2* rows = reinterpret_cast<const float2*>(pts + (size_t)base * d);
+			const uint32_t d2 = d >> 1;
+			for (uint32_t c0 = 0; c0 < d2; c0 += dg) {
+				const uint32_t j2 = c0 + dl;
+				const bool jok = j2 < d2;
+				float2 sum = make_float2(0.f, 0.f);
+				uint32_t cur = w0 < w1 ? cl_sorted[w0] : 0u;
+				for (uint32_t sp = w0; sp < w1; sp += 4) {
+					const uint2 o2 = *reinterpret_cast<const uint2*>(&order[sp]);
+					const uint2 c2 = *reinterpret_cast<const uint2*>(&cl_sorted[sp]);
+					const uint32_t oi[4] = {o2.x & 0xffffu, o2.x >> 16, o2.y & 0xffffu, o2.y >> 16};
+					const uint32_t ci[4] = {c2.x & 0xffffu, c2.x >> 16, c2.y & 0xffffu, c2.y >> 16};
+					float2 x[4];
+					#pragma unroll
+					for (uint32_t u = 0; u < 4; ++u) {
+						x[u] = make_float2(0.f, 0.f);
+						if (sp + u < w1 && jok) x[u] = rows[oi[u] * d2 + j2];
+					}
+					#pragma unroll
+					for (uint32_t u = 0; u < 4; ++u) {
+						if (sp + u < w1) {
+							if (ci[u] != cur) {
+								if (jok) red_add_v2(&acc[(size_t)cur * d + j2 * 2], sum.x, sum.y);
+								sum = make_float2(0.f, 0.f);
+								cur = ci[u];
+							}
+							sum.x += x[u].x; sum.y += x[u].y;
+						}
+					}
+				}
+				if (w0 < w1 && jok) red_add_v2(&acc[(size_t)cur * d + j2 * 2], sum.x, sum.y);
+			}
+		} else {
+			for (uint32_t c0 = 0; c0 < d; c0 += dg) {
+				const uint32_t j = c0 + dl;
+				const bool jok = j < d;
+				// 32-bit offsets from the chunk's first point
+				const float* col = SOA ? pts + (size_t)j * n + base : pts + (size_t)base * d + j;
+				const uint32_t pstride = SOA ? 1u : d;
+				float sum = 0.0f;
+				uint32_t cur = w0 < w1 ? cl_sorted[w0] : 0u;
+				for (uint32_t sp = w0; sp < w1; sp += 4) {
+					// four sorted positions at a time: indices and clusters as one 8-byte load each
+					const uint2 o2 = *reinterpret_cast<const uint2*>(&order[sp]);
+					const uint2 c2 = *reinterpret_cast<const uint2*>(&cl_sorted[sp]);
+					const uint32_t oi[4] = {o2.x & 0xffffu, o2.x >> 16, o2.y & 0xffffu, o2.y >> 16};
+					const uint32_t ci[4] = {c2.x & 0xffffu, c2.x >> 16, c2.y & 0xffffu, c2.y >> 16};
+					float x[4];
+					#pragma unroll
+					for (uint32_t u = 0; u < 4; ++u) {
+						x[u] = 0.0f;
+						if (sp + u < w1 && jok) x[u] = col[oi[u] * pstride];
+					}
+					#pragma unroll
+					for (uint32_t u = 0; u < 4; ++u) {
+						if (sp + u < w1) {
+							if (ci[u] != cur) {
+								if (jok) atomicAdd(&acc[(size_t)cur * d + j], sum);
+								sum = 0.0f;
+								cur = ci[u];
+							}
+							sum += x[u];
+						}
+					}
+				}
+				if (w0 < w1 && jok) atomicAdd(&acc[(size_t)cur * d + j], sum);
+			}
+		}
+	}
+	if (bad) atomicOr(&ctl->status, (uint32_t)STATUS_BAD_INDEX);
+}
+
 static size_t update_replica_bytes(const Shape& s)
 {
 	const uint32_t dstride = s.dim | 1u;
@@ -400,6 +608,22 @@ bool update_shared_fits(const Shape& s, int /*device*/)
 void launch_update(const float* pts, const uint32_t* asg, float* acc, uint32_t* counts, uint32_t replicas, const Shape& s,
 	int variant, Control* ctl, int sm_count, cudaStream_t stream)
 {
+	if (variant == BKM_UPDATE_SORTED) {
+		// row-major points whose rows are whole 16- or 8-byte vectors: a lane holds four or two dimensions
+		const uintptr_t align = reinterpret_cast<uintptr_t>(pts) | reinterpret_cast<uintptr_t>(acc);
+		const int vw = s.soa ? 1 : (s.dim % 4 == 0 && (align & 15u) == 0 ? 4 : (s.dim % 2 == 0 && (align & 7u) == 0 ? 2 : 1));
+		const uint32_t per_point = s.dim / (uint32_t)vw;
+		uint32_t dg = vw == 1 ? 2 : 1;              // lanes per point: the power of two that covers a row, at most 32
+		while (dg < 32 && dg < per_point) dg <<= 1;
+		const uint64_t chunks = (s.n + SORT_CHUNK - 1) / SORT_CHUNK;
+		const uint32_t grid = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(chunks, 1), (uint64_t)sm_count * 8);
+		const size_t rep_stride = acc_replica_stride(s.k, s.dim);
+		if (s.soa) update_sorted_kernel<true, 1><<<grid, SORT_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dg, replicas, rep_stride, ctl);
+		else if (vw == 4) update_sorted_kernel<false, 4><<<grid, SORT_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dg, replicas, rep_stride, ctl);
+		else if (vw == 2) update_sorted_kernel<false, 2><<<grid, SORT_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dg, replicas, rep_stride, ctl);
+		else update_sorted_kernel<false, 1><<<grid, SORT_THREADS, 0, stream>>>(pts, asg, acc, counts, s.n, s.k, s.dim, dg, replicas, rep_stride, ctl);
+		return;
+	}
 	if (variant == BKM_UPDATE_ROWS) {
 		const uint64_t groups = (s.n + 31) / 32;
 		const uint64_t blocks = (groups + ROWS_THREADS / 32 - 1) / (ROWS_THREADS / 32);

@@ -54,6 +54,7 @@ extern "C" {
 #define BKM_UPDATE_GLOBAL 2  /* global atomics only (any k*dim) */
 #define BKM_UPDATE_ROWS 3    /* one coalesced 128-byte global reduction per point and 32 dimensions */
 #define BKM_UPDATE_FUSED 4   /* reported by bkm_counters only: the assignment pass accumulated the sums itself */
+#define BKM_UPDATE_SORTED 5  /* block-local counting sort by cluster, one reduction per cluster and 2048 points (k <= 1024) */
 
 const char* bkm_last_error(void);
 
@@ -171,7 +172,7 @@ int bkm_set_stream(bkm_handle_t h, void* stream);
  * latency; single GPU only), "tc_pair" (0/1, default 1: let the tensor-core assignment run on CTA
  * pairs with all means resident in shared memory where the shape allows, i.e. 257..1024 means
  * of 17..32 dimensions), "fuse_update" (0/1, default 1: let that kernel add every point to the sum
- * of the cluster it picks, which replaces the update pass of bkm_run; needs dim % 4 == 0).
+ * of the cluster it picks, which replaces the row-wise update pass of bkm_run; needs dim % 4 == 0).
  * Unknown names fail with BKM_ERR_INVALID. */
 int bkm_set_option(bkm_handle_t h, const char* name, double value);
 

@@ -34,6 +34,8 @@ def test_update_matches_oracle(pkg, torch_cuda, oracle_mod, n, k, d):
         variants = [pkg.UPDATE_AUTO, pkg.UPDATE_GLOBAL, pkg.UPDATE_ROWS]
         if k * ((d | 1) + 1) * 4 <= 227 * 1024 - 1024:
             variants.append(pkg.UPDATE_SHARED)
+        if k <= 1024:
+            variants.append(pkg.UPDATE_SORTED)
         for variant in variants:
             means, sizes = _run_update(pkg, torch_cuda, data, asg, n, k, d, layout, layout_means, variant)
             assert np.array_equal(sizes, want_sizes), (layout, layout_means, variant)
@@ -62,12 +64,12 @@ def test_hot_cluster_and_zipf(pkg, torch_cuda, oracle_mod):
         for layout in (0, 1):
             data = rows_to_layout(rows, layout)
             want64, want_sizes = oracle_mod.update_f64(data, asg, n, k, d, layout, layout)
-            for variant in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL, pkg.UPDATE_ROWS):
+            for variant in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL, pkg.UPDATE_ROWS, pkg.UPDATE_SORTED):
                 means, sizes = _run_update(pkg, torch_cuda, data, asg, n, k, d, layout, layout, variant)
                 assert np.array_equal(sizes, want_sizes)
                 # a single fp32 accumulator summed in arrival order drifts like the reference's own
                 # sequential sum; the privatised variant is hierarchical and stays tighter
-                ok, err = means_close(means, want64, rtol=1e-5 if variant == pkg.UPDATE_SHARED else 1e-4)
+                ok, err = means_close(means, want64, rtol=1e-5 if variant in (pkg.UPDATE_SHARED, pkg.UPDATE_SORTED) else 1e-4)
                 assert ok, (layout, variant, err)
 
 
@@ -78,7 +80,7 @@ def test_out_of_range_assignment_is_reported_not_faulted(pkg, torch_cuda):
     asg[7] = 99
     dev = DeviceArrays(torch_cuda, pkg, rows.reshape(-1), np.zeros(k * d, np.float32), n, k, d)
     dev.assignment = torch_cuda.from_numpy(asg.astype(np.int32)).to("cuda:0")
-    for variant in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL, pkg.UPDATE_ROWS):
+    for variant in (pkg.UPDATE_SHARED, pkg.UPDATE_GLOBAL, pkg.UPDATE_ROWS, pkg.UPDATE_SORTED):
         pkg.update(dev.points.data_ptr(), dev.assignment.data_ptr(), dev.means_out.data_ptr(), dev.sizes.data_ptr(),
                    n, k, d, 0, 0, dev.ws_ptr, dev.ws_bytes_avail, variant=variant)
         with pytest.raises(pkg.BkmError) as e:
