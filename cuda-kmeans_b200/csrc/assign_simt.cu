@@ -79,7 +79,7 @@ template<bool SOA, bool SOAM>
 __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const float* __restrict__ pts,
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
 	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count,
-	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts)
+	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts, uint32_t resident_ok)
 {
 	extern __shared__ float sx[];                       // LIST_PB points (dpad floats each), then the means tile
 	__shared__ uint32_t smoved[LIST_PB][2];             // (old, new) cluster of a point that changed, else old == new
@@ -90,6 +90,19 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
 	uint64_t total = *list_count;
 	if (total > n) total = n;
+	// A long list and few means: every block copies all means to shared memory once (rows of an
+	// odd number of floats, one mean per thread -> conflict-free) instead of fetching them again
+	// for every group of points.
+	const uint32_t ds = d | 1u;
+	float* mres = sx + (size_t)LIST_PB * dpad;
+	const bool resident = resident_ok != 0 && total >= (uint64_t)gridDim.x * LIST_PB * 4;
+	if (resident) {
+		for (uint32_t e = tid; e < k * d; e += LIST_THREADS) {
+			// e walks the means array in memory order (coalesced)
+			const uint32_t m = SOAM ? e % k : e / d, j = SOAM ? e / k : e % d;
+			mres[m * ds + j] = means[e];
+		}
+	}
 	for (uint64_t w0 = (uint64_t)blockIdx.x * LIST_PB; w0 < total; w0 += (uint64_t)gridDim.x * LIST_PB) {
 		const uint32_t np = total - w0 < LIST_PB ? (uint32_t)(total - w0) : LIST_PB;
 		__syncthreads();
@@ -107,7 +120,18 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 			float sum[LIST_PB];
 			#pragma unroll
 			for (int p = 0; p < LIST_PB; ++p) sum[p] = 0.0f;
-			if (SOAM) {
+			if (resident) {
+				if (m < k) {
+					for (uint32_t j = 0; j < d; ++j) {
+						const float c = mres[m * ds + j];
+						#pragma unroll
+						for (int p = 0; p < LIST_PB; ++p) {
+							const float diff = __fsub_rn(sx[p * dpad + j], c);
+							sum[p] = __fadd_rn(sum[p], __fmul_rn(diff, diff));
+						}
+					}
+				}
+			} else if (SOAM) {
 				if (m < k) {
 					for (uint32_t j = 0; j < d; ++j) {
 						const float c = means[(size_t)j * k + m];
@@ -192,13 +216,19 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 {
 	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
-		const size_t lsmem = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float) + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
+		const size_t points_bytes = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float);
+		size_t lsmem = points_bytes + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
+		// room for all means (the kernel uses it when the list is long): at most 64 KiB, so that
+		// several blocks still share an SM
+		const size_t resident_bytes = points_bytes + (size_t)s.k * (s.dim | 1u) * sizeof(float);
+		const uint32_t resident_ok = resident_bytes <= 64 * 1024 ? 1u : 0u;
+		if (resident_ok && resident_bytes > lsmem) lsmem = resident_bytes;
 		const uint32_t lgrid = (uint32_t)sm_count * 8;
 #define BKM_LAUNCH_LIST(SOA, SOAM) do { \
 		auto kern = assign_exact_list_kernel<SOA, SOAM>; \
 		if (lsmem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lsmem); if (e != cudaSuccess) return e; } \
 		kern<<<lgrid, LIST_THREADS, lsmem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count, \
-			fix ? fix->acc : nullptr, fix ? fix->counts : nullptr); \
+			fix ? fix->acc : nullptr, fix ? fix->counts : nullptr, resident_ok); \
 	} while (0)
 		if (s.soa && s.soa_means) BKM_LAUNCH_LIST(true, true);
 		else if (s.soa && !s.soa_means) BKM_LAUNCH_LIST(true, false);
