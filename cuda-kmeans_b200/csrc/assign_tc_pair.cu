@@ -72,16 +72,10 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 }
 
 // Like wait_or_abort, and a wait that runs out also raises the flag of the other CTA.
+template<uint32_t SLEEP_NS = 100>
 __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t peer_abort_addr)
 {
-	if (ptx::mbar_try_wait(bar, parity)) return true;
-	const uint64_t t0 = ptx::globaltimer_ns();
-	while (true) {
-		if (ptx::mbar_try_wait(bar, parity)) return true;
-		if (*abort_flag) return false;
-		if (ptx::globaltimer_ns() - t0 > ptx::WAIT_LIMIT_NS) break;
-	}
-	*abort_flag = 1;
+	if (wait_or_abort<SLEEP_NS>(bar, parity, abort_flag)) return true;
 	ptx::st_cluster_u32(peer_abort_addr, 1u);
 	return false;
 }
@@ -175,7 +169,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			bool ok = true;
 			for (uint32_t step = pair; step < steps_total && ok; step += n_pairs, ++it) {
 				const uint32_t buf = it % n_abuf, u = it / n_abuf;
-				ok = pair_wait(&bars->a_empty[buf], (u & 1u) ^ 1u, abort_flag, peer_abort_addr);
+				ok = pair_wait<400>(&bars->a_empty[buf], (u & 1u) ^ 1u, abort_flag, peer_abort_addr);
 				if (!ok) break;
 				if (rank == 0) ptx::mbar_arrive_expect_tx(&bars->a_full[buf], 2 * a_tile);
 				const uint32_t a_full_leader = ptx::leader_cta_addr(ptx::smem_u32(&bars->a_full[buf]));
@@ -225,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				for (uint32_t u = 0; u < n_units; ++u, ++c) {
 					const uint32_t acc = c % P2_ACCS;
 					TC_T(c2);
-					ok = pair_wait(&bars->acc_empty[acc], ((c / P2_ACCS) & 1u) ^ 1u, abort_flag, peer_abort_addr);
+					ok = pair_wait<400>(&bars->acc_empty[acc], ((c / P2_ACCS) & 1u) ^ 1u, abort_flag, peer_abort_addr);
 					if (!ok) break;
 					TC_T(c3);
 					TC_ACC(t_acc, c2, c3);

@@ -40,15 +40,35 @@ __device__ __forceinline__ float to_tf32(float x)
 	return __uint_as_float(u);
 }
 
-// Bounded wait that also gives up when another role already failed.
+// Bounded wait that also gives up when another role already failed.  try_wait suspends the
+// thread for a while by itself but comes back early often, so the loop around it decides how
+// much the waiting warps take from the warps that work.  SLEEP_NS = 0: look at the abort flag
+// and the clock in every round (the clock read is slow and paces the loop).  SLEEP_NS > 0:
+// sleep between rounds and look at flag and clock every 256th round only.
+template<uint32_t SLEEP_NS = 0>
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
 {
 	if (ptx::mbar_try_wait(bar, parity)) return true;
-	const uint64_t t0 = ptx::globaltimer_ns();
-	while (true) {
-		if (ptx::mbar_try_wait(bar, parity)) return true;
-		if (*abort_flag) return false;
-		if (ptx::globaltimer_ns() - t0 > ptx::WAIT_LIMIT_NS) break;
+	if (SLEEP_NS == 0) {
+		const uint64_t t0 = ptx::globaltimer_ns();
+		while (true) {
+			if (ptx::mbar_try_wait(bar, parity)) return true;
+			if (*abort_flag) return false;
+			if (ptx::globaltimer_ns() - t0 > ptx::WAIT_LIMIT_NS) break;
+		}
+	} else {
+		uint32_t spins = 0;
+		uint64_t t0 = 0;
+		while (true) {
+			if (ptx::mbar_try_wait(bar, parity)) return true;
+			__nanosleep(SLEEP_NS);
+			if ((++spins & 255u) == 0) {
+				if (*abort_flag) return false;
+				const uint64_t now = ptx::globaltimer_ns();
+				if (t0 == 0) t0 = now;
+				else if (now - t0 > ptx::WAIT_LIMIT_NS) break;
+			}
+		}
 	}
 	*abort_flag = 1;
 	return false;
