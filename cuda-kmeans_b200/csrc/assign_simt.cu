@@ -145,11 +145,15 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 			} else {
 				for (uint32_t j0 = 0; j0 < d; j0 += 32) {
 					__syncthreads();
-					#pragma unroll 4
+					// all 32 row segments of the warp in flight at once
+					float seg[32];
+					#pragma unroll
 					for (uint32_t r = 0; r < 32; ++r) {
 						const uint32_t row = warp * 32 + r;
-						tile[row][lane] = (m0 + row < k && j0 + lane < d) ? means[(size_t)(m0 + row) * d + j0 + lane] : 0.0f;
+						seg[r] = (m0 + row < k && j0 + lane < d) ? means[(size_t)(m0 + row) * d + j0 + lane] : 0.0f;
 					}
+					#pragma unroll
+					for (uint32_t r = 0; r < 32; ++r) tile[warp * 32 + r][lane] = seg[r];
 					__syncthreads();
 					const uint32_t jn = d - j0 < 32 ? d - j0 : 32;
 					for (uint32_t jj = 0; jj < jn; ++jj) {

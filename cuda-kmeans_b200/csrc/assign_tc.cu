@@ -51,12 +51,18 @@ constexpr uint32_t B_PLANE_BYTES = TC_NT_MAX * TC_KCHUNK * 4;    // 32 KiB: 256 
 constexpr uint32_t A_TILE_BYTES = 2 * A_PLANE_BYTES;             // hi + lo
 constexpr uint32_t B_STAGE_BYTES = 2 * B_PLANE_BYTES;
 constexpr uint32_t AUG_BYTES = TC_NT_MAX * 8 * 4;                // 8 KiB: 256 rows x one K step of 8
-// K-loop mode (dim > 32): both operands stream, one 32-dimension slice per stage:
-// [A hi | A lo | B hi | B lo | B's |c|^2 step]; two such stages fill the same bytes as the
-// resident-points layout below.
-constexpr uint32_t KSTAGE_BYTES = A_TILE_BYTES + B_STAGE_BYTES + AUG_BYTES;
-constexpr uint32_t KS_ALO_OFF = A_PLANE_BYTES, KS_BHI_OFF = A_TILE_BYTES, KS_BLO_OFF = A_TILE_BYTES + B_PLANE_BYTES,
-	KS_AUG_OFF = A_TILE_BYTES + B_STAGE_BYTES;
+// K-loop mode (dim > 32): both operands stream in 16-dimension slices (rows of 64 B, 64-byte
+// swizzle).  A stage holds the slice of BOTH point tiles of the block and of one mean tile:
+// [A0 hi | A0 lo | A1 hi | A1 lo | B hi | B lo], and feeds both accumulators, so every byte of
+// the mean tile that crosses from L2 is used for 256 points.  Three stages; the |c|^2 steps of
+// the current and the next mean tile sit behind them.
+constexpr uint32_t KL_KW = 16;
+constexpr uint32_t KL_STAGES = 3;
+constexpr uint32_t KL_A_PLANE = TC_MTILE * KL_KW * 4;            // 8 KiB
+constexpr uint32_t KL_B_PLANE = TC_NT_MAX * KL_KW * 4;           // 16 KiB
+constexpr uint32_t KL_A1_OFF = 2 * KL_A_PLANE, KL_B_OFF = 4 * KL_A_PLANE;
+constexpr uint32_t KL_STAGE_BYTES = KL_B_OFF + 2 * KL_B_PLANE;   // 64 KiB
+constexpr uint32_t KL_AUG_OFF = KL_STAGES * KL_STAGE_BYTES;      // two |c|^2 steps of 8 KiB
 constexpr uint32_t SM_A_OFF = 0;
 constexpr uint32_t SM_B_OFF = SM_A_OFF + TC_MA * A_TILE_BYTES;
 constexpr uint32_t SM_BAUG_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // |c|^2 K step per stage
@@ -182,8 +188,10 @@ constexpr uint32_t TC_NA_MAX = 8;        // most point-tile buffers (single resi
 struct TcBars {
 	uint64_t a_full[TC_NA_MAX];
 	uint64_t a_empty[TC_NA_MAX];
-	uint64_t b_full[TC_NB];
-	uint64_t b_empty[TC_NB];
+	uint64_t b_full[KL_STAGES];      // TC_NB of them in the resident-points modes
+	uint64_t b_empty[KL_STAGES];
+	uint64_t aug_full[2];            // K-loop mode: |c|^2 step of a mean tile has landed
+	uint64_t aug_empty[2];
 	uint64_t acc_full[TC_MA];
 	uint64_t acc_empty[TC_MA];
 	uint32_t tmem_slot;
@@ -191,7 +199,7 @@ struct TcBars {
 };
 static_assert(sizeof(TcBars) <= 256, "barrier block too large");
 static_assert(SM_ALLOC <= 227 * 1024, "shared memory budget exceeded");
-static_assert(TC_NB * KSTAGE_BYTES <= SM_AAUG_OFF, "K-loop stages overlap the constant tile");
+static_assert(KL_AUG_OFF + 2 * AUG_BYTES <= SM_AAUG_OFF, "K-loop stages overlap the constant tile");
 
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
@@ -230,9 +238,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			ptx::mbar_init(&bars->acc_full[i], 1);
 			ptx::mbar_init(&bars->acc_empty[i], TC_EPI_WARPS / TC_MA);
 		}
-		for (uint32_t i = 0; i < TC_NB; ++i) {
+		for (uint32_t i = 0; i < KL_STAGES; ++i) {
 			ptx::mbar_init(&bars->b_full[i], 1);
 			ptx::mbar_init(&bars->b_empty[i], 1);
+		}
+		for (uint32_t i = 0; i < 2; ++i) {
+			ptx::mbar_init(&bars->aug_full[i], 1);
+			ptx::mbar_init(&bars->aug_empty[i], 1);
 		}
 		bars->abort_flag = 0;
 		ptx::fence_mbar_init();
@@ -260,28 +272,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			uint32_t a_use[TC_NA_MAX] = {0, 0, 0, 0, 0, 0, 0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
+			uint32_t aug_count = 0;
 			if (kchunks > 1) {
-				// K-loop mode: one (point tile, centroid tile, 32-dimension slice) per stage
+				// K-loop mode: one (block of two point tiles, mean tile, 16-dimension slice) per stage
 				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-					for (uint32_t j = 0; j < n_ctiles && ok; ++j)
-						for (uint32_t i = 0; i < tiles && ok; ++i)
-							for (uint32_t kc = 0; kc < kchunks; ++kc) {
-								const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
-								ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
-								if (!ok) break;
-								uint8_t* dst = smem + s * KSTAGE_BYTES;
-								const bool last = kc == kchunks - 1;
-								const uint32_t aug_bytes = last ? nt_cols * 8 * 4 : 0u;
-								const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE), x = (int32_t)(kc * TC_KCHUNK);
-								ptx::mbar_arrive_expect_tx(&bars->b_full[s], A_TILE_BYTES + 2 * nt_cols * TC_KCHUNK * 4 + aug_bytes);
-								ptx::tma_load_2d(dst, &tm_a_hi, x, row, &bars->b_full[s]);
-								ptx::tma_load_2d(dst + KS_ALO_OFF, &tm_a_lo, x, row, &bars->b_full[s]);
-								ptx::tma_load_2d(dst + KS_BHI_OFF, &tm_b_hi, x, (int32_t)(j * nt_cols), &bars->b_full[s]);
-								ptx::tma_load_2d(dst + KS_BLO_OFF, &tm_b_lo, x, (int32_t)(j * nt_cols), &bars->b_full[s]);
-								if (last) ptx::bulk_g2s(dst + KS_AUG_OFF, b_aug + (size_t)j * nt_cols * 8, aug_bytes, &bars->b_full[s]);
-								++b_count;
+					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+						{
+							const uint32_t as = aug_count & 1u, au = aug_count >> 1;
+							ok = wait_or_abort(&bars->aug_empty[as], (au & 1u) ^ 1u, abort_flag);
+							if (!ok) break;
+							ptx::mbar_arrive_expect_tx(&bars->aug_full[as], nt_cols * 8 * 4);
+							ptx::bulk_g2s(smem + KL_AUG_OFF + as * AUG_BYTES, b_aug + (size_t)j * nt_cols * 8, nt_cols * 8 * 4, &bars->aug_full[as]);
+							++aug_count;
+						}
+						for (uint32_t kc = 0; kc < kchunks; ++kc) {
+							const uint32_t s = b_count % KL_STAGES, u = b_count / KL_STAGES;
+							ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
+							if (!ok) break;
+							uint8_t* dst = smem + s * KL_STAGE_BYTES;
+							const int32_t row = (int32_t)(blk * TC_MA * TC_MTILE), x = (int32_t)(kc * KL_KW);
+							ptx::mbar_arrive_expect_tx(&bars->b_full[s], tiles * 2 * KL_A_PLANE + 2 * nt_cols * KL_KW * 4);
+							ptx::tma_load_2d(dst, &tm_a_hi, x, row, &bars->b_full[s]);
+							ptx::tma_load_2d(dst + KL_A_PLANE, &tm_a_lo, x, row, &bars->b_full[s]);
+							if (tiles > 1) {
+								ptx::tma_load_2d(dst + KL_A1_OFF, &tm_a_hi, x, row + (int32_t)TC_MTILE, &bars->b_full[s]);
+								ptx::tma_load_2d(dst + KL_A1_OFF + KL_A_PLANE, &tm_a_lo, x, row + (int32_t)TC_MTILE, &bars->b_full[s]);
 							}
+							ptx::tma_load_2d(dst + KL_B_OFF, &tm_b_hi, x, (int32_t)(j * nt_cols), &bars->b_full[s]);
+							ptx::tma_load_2d(dst + KL_B_OFF + KL_B_PLANE, &tm_b_lo, x, (int32_t)(j * nt_cols), &bars->b_full[s]);
+							++b_count;
+						}
+					}
 				}
 			} else {
 				uint32_t g = 0;                       // running count of point tiles = position in the A ring
@@ -318,9 +340,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			// Do not leave while an own copy may still be in flight towards this CTA's shared memory.
 			for (uint32_t i = 0; i < TC_NA_MAX; ++i)
 				if (a_use[i]) ptx::mbar_wait(&bars->a_full[i], (a_use[i] - 1) & 1u);
-			for (uint32_t back = 0; back < TC_NB && back < b_count; ++back) {
+			const uint32_t ring = kchunks > 1 ? KL_STAGES : TC_NB;
+			for (uint32_t back = 0; back < ring && back < b_count; ++back) {
 				const uint32_t c = b_count - 1 - back;
-				ptx::mbar_wait(&bars->b_full[c % TC_NB], (c / TC_NB) & 1u);
+				ptx::mbar_wait(&bars->b_full[c % ring], (c / ring) & 1u);
+			}
+			for (uint32_t back = 0; back < 2 && back < aug_count; ++back) {
+				const uint32_t c = aug_count - 1 - back;
+				ptx::mbar_wait(&bars->aug_full[c & 1u], (c >> 1) & 1u);
 			}
 		}
 	} else if (warp == 1) {
@@ -334,44 +361,57 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			bool ok = true;
 			const uint64_t a_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_AAUG_OFF));
 			if (kchunks > 1) {
-				// K-loop mode: the accumulator of a (point tile, centroid tile) pair collects all slices
+				// K-loop mode: both accumulators of the block collect the slices of one mean tile together
+				uint32_t aug_count = 0;
 				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-					for (uint32_t j = 0; j < n_ctiles && ok; ++j)
+					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
 						for (uint32_t i = 0; i < tiles && ok; ++i) {
 							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
-							if (!ok) break;
-							ptx::tc_fence_after();
-							const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
-							for (uint32_t kc = 0; kc < kchunks; ++kc) {
-								const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
-								ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
-								if (!ok) break;
-								ptx::tc_fence_after();
-								const uint32_t base = ptx::smem_u32(smem + s * KSTAGE_BYTES);
-								const uint64_t a_hi = make_desc(base), a_lo = make_desc(base + KS_ALO_OFF);
-								const uint64_t b_hi = make_desc(base + KS_BHI_OFF), b_lo = make_desc(base + KS_BLO_OFF);
-								const bool last = kc == kchunks - 1;
-								const uint32_t steps = last ? ksteps : 4u;
-								if (ptx::elect_one()) {
-									#pragma unroll
-									for (uint32_t ks = 0; ks < 4; ++ks)
-										if (ks < steps) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, (kc | ks) > 0);
-									#pragma unroll
-									for (uint32_t ks = 0; ks < 4; ++ks)
-										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
-									#pragma unroll
-									for (uint32_t ks = 0; ks < 4; ++ks)
-										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
-									if (last) ptx::mma_tf32(d_tmem, a_aug_desc, make_desc_aug(base + KS_AUG_OFF), idesc, 1);
-									ptx::mma_commit(&bars->b_empty[s]);
-									if (last) ptx::mma_commit(&bars->acc_full[i]);
-								}
-								__syncwarp();
-								++b_count;
-							}
 							++acc_use[i];
 						}
+						if (!ok) break;
+						ptx::tc_fence_after();
+						for (uint32_t kc = 0; kc < kchunks; ++kc) {
+							const uint32_t s = b_count % KL_STAGES, u = b_count / KL_STAGES;
+							ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
+							if (!ok) break;
+							const bool last = kc == kchunks - 1;
+							const uint32_t as = aug_count & 1u;
+							if (last) {
+								ok = wait_or_abort(&bars->aug_full[as], (aug_count >> 1) & 1u, abort_flag);
+								if (!ok) break;
+							}
+							ptx::tc_fence_after();
+							const uint32_t base = ptx::smem_u32(smem + s * KL_STAGE_BYTES);
+							const uint64_t b_hi = make_desc_kw(base + KL_B_OFF, KL_KW), b_lo = make_desc_kw(base + KL_B_OFF + KL_B_PLANE, KL_KW);
+							const uint32_t steps = last ? ksteps : 2u;
+							if (ptx::elect_one()) {
+								for (uint32_t i = 0; i < tiles; ++i) {
+									const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
+									const uint64_t a_hi = make_desc_kw(base + i * KL_A1_OFF, KL_KW), a_lo = make_desc_kw(base + i * KL_A1_OFF + KL_A_PLANE, KL_KW);
+									#pragma unroll
+									for (uint32_t ks = 0; ks < 2; ++ks)
+										if (ks < steps) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, (kc | ks) > 0);
+									#pragma unroll
+									for (uint32_t ks = 0; ks < 2; ++ks)
+										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
+									#pragma unroll
+									for (uint32_t ks = 0; ks < 2; ++ks)
+										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
+									if (last) {
+										ptx::mma_tf32(d_tmem, a_aug_desc, make_desc_aug(ptx::smem_u32(smem + KL_AUG_OFF + as * AUG_BYTES)), idesc, 1);
+										ptx::mma_commit(&bars->acc_full[i]);
+									}
+								}
+								ptx::mma_commit(&bars->b_empty[s]);
+								if (last) ptx::mma_commit(&bars->aug_empty[as]);
+							}
+							__syncwarp();
+							++b_count;
+						}
+						++aug_count;
+					}
 				}
 			} else {
 #ifdef BKM_TC_TIMING
@@ -612,10 +652,11 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode()
 }
 
 // [rows][cols] fp32 row-major, box = box_rows x 32 columns with 128-byte swizzle, or, when the
-// rows are only 16 floats long, box_rows x 16 columns with 64-byte swizzle.
+// rows are only 16 floats long or the K loop runs (rows longer than 32 floats, 16-dimension
+// slices), box_rows x 16 columns with 64-byte swizzle.
 static bool encode_plane(CUtensorMap* out, const float* base, uint64_t rows, uint32_t cols, uint32_t box_rows)
 {
-	const uint32_t kw = cols == 16 ? 16u : TC_KCHUNK;
+	const uint32_t kw = (cols == 16 || cols > TC_KCHUNK) ? 16u : TC_KCHUNK;
 	auto enc = get_encode();
 	if (!enc) return false;
 	cuuint64_t dims[2] = {cols, rows};
@@ -691,8 +732,11 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
 	// error band of the split-TF32 GEMM form relative to |x|^2 + max|c|^2
 	const float margin_coef = margin_scale * (48.0f + 0.5f * (float)p->tp.d_pad) * 1.1920929e-07f;
-	const uint32_t kw = p->tp.d_pad == 16 ? 16u : TC_KCHUNK;
-	const uint32_t kchunks = p->tp.d_pad / kw;
+	// rows of 16 or 32 floats stay resident whole; longer rows stream in 16-dimension slices, and
+	// slices that hold padding only are skipped
+	const bool kloop = p->tp.d_pad > TC_KCHUNK;
+	const uint32_t kw = (p->tp.d_pad == 16 || kloop) ? 16u : TC_KCHUNK;
+	const uint32_t kchunks = kloop ? (p->s.dim + kw - 1) / kw : 1u;
 	const uint32_t ksteps_last = (p->s.dim - (kchunks - 1) * kw + 7) / 8;    // K steps of the last slice
 	const uint32_t idesc = p->idesc;
 	if (tc_plan_uses_pair(p))
