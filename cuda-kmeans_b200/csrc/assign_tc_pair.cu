@@ -118,7 +118,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 		ptx::mbar_init(&bars->b_full, 1);
 		for (uint32_t i = 0; i < P2_ACCS; ++i) {
 			ptx::mbar_init(&bars->acc_full[i], 1);
-			ptx::mbar_init(&bars->acc_empty[i], 2 * 4);          // one warp per TMEM lane quarter in each CTA
+			ptx::mbar_init(&bars->acc_empty[i], 2 * 8);          // two warps per TMEM lane quarter in each CTA
 		}
 		bars->abort_flag = 0;
 		ptx::fence_mbar_init();
@@ -139,12 +139,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base;
 	fill_a_aug(reinterpret_cast<float*>(smem + P2_AAUG_OFF), kc.offset_c, threadIdx.x, TC_THREADS);
 	{
-		// this CTA's half of every tile's |c|^2 K step: 128 rows = 4 KiB, contiguous in global memory
+		// This CTA's half of every tile's |c|^2 K step: 128 rows = 4 KiB, contiguous in global memory.
+		// Rows behind the last mean are padding (their operand rows are zero); they get the |c|^2 that
+		// puts their value at 2P - P/32, above every real value (at most 1.83 P) and inside [P, 2P),
+		// so that the arg-min needs no column masks.
 		float4* dst = reinterpret_cast<float4*>(smem + baug_off);
 		const uint32_t per_tile = P2_AUG_HALF_BYTES / 16;
+		const float cn_pad = to_tf32(kc.pow2 - x2max - kc.pow2 * (1.0f / 16.0f));
 		for (uint32_t e = threadIdx.x; e < n_ctiles * per_tile; e += TC_THREADS) {
 			const uint32_t j = e / per_tile, r = e - j * per_tile;
-			dst[e] = reinterpret_cast<const float4*>(b_aug + ((size_t)j * TC_NT_MAX + rank * P2_HALF) * 8)[r];
+			// float4 r of a tile half: rows (r / 16) * 8 + r % 8, K positions 4 * ((r / 8) % 2) ..
+			const uint32_t mean = j * TC_NT_MAX + rank * P2_HALF + (r >> 4) * 8 + (r & 7u);
+			float4 v = reinterpret_cast<const float4*>(b_aug + ((size_t)j * TC_NT_MAX + rank * P2_HALF) * 8)[r];
+			if (mean >= k && ((r >> 3) & 1u) == 0) v = make_float4(cn_pad, 0.0f, 1.0f, 1.0f);
+			dst[e] = v;
 		}
 	}
 	ptx::fence_proxy_async();
@@ -219,7 +227,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				for (uint32_t u = 0; u < n_units; ++u, ++c) {
 					const uint32_t acc = c % P2_ACCS;
 					TC_T(c2);
-					ok = pair_wait<400>(&bars->acc_empty[acc], ((c / P2_ACCS) & 1u) ^ 1u, abort_flag, peer_abort_addr);
+					ok = pair_wait<200>(&bars->acc_empty[acc], ((c / P2_ACCS) & 1u) ^ 1u, abort_flag, peer_abort_addr);
 					if (!ok) break;
 					TC_T(c3);
 					TC_ACC(t_acc, c2, c3);
@@ -263,17 +271,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 		}
 	} else {
 		// ---------------- epilogue (both CTAs, own accumulator rows) ----------------
-		// Warp (q, g): TMEM lane quarter q (the only lanes the warp may read), accumulator g.  The
-		// four warps of a scheduler own one accumulator each, so while one waits for tensor memory
-		// the others keep the integer pipes busy.  A warp takes its 128 columns two 32-column chunks
-		// at a time into registers and hands the accumulator back after its last load.
+		// Warp (q, g): TMEM lane quarter q (the only lanes the warp may read); g = 2 * column half +
+		// group.  The two groups of eight warps take the accumulator fills alternately; a warp moves
+		// its 64 columns to registers with one load, hands the accumulator back at once and reduces
+		// from registers, so an accumulator is away from the tensor cores for a load only.
 		// The loops are kept rolled (instruction cache).
 		const uint32_t q = warp & 3u;
 		const uint32_t g = (warp - 2) >> 2;           // 0..3
 		const uint32_t row = q * 32 + lane;
 		const float ulp = kc.pow2 * 1.1920929e-07f;   // spacing of the values inside [P, 2P)
-		const uint32_t acc_empty_addr = ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[g]), 0);
-		uint32_t it = 0, c = 0;
+		const uint32_t acc_empty_base = ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[0]), 0);
+		uint32_t it = 0;
 		bool ok = true;
 		// Fused update sums.  The 32 points of this quarter stay in the point tile (tf32 hi + lo of
 		// the centred coordinates) after their step.  Eight lanes cover one point's row with a
@@ -316,13 +324,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			const uint64_t p = (uint64_t)(2 * step + rank) * TC_MTILE + row;
 			float xn = 0.0f;
 			if (g == 0 && p < n) xn = xnorm[p];           // needed at the end of the step only: fetch early
+			// this warp's accumulator fills of the step: every second one, counted across steps; of
+			// each it takes 64 columns with one load and hands the accumulator back at once
+			const uint32_t c_step = it * n_units;
+			const uint32_t grp = g & 1u, colhalf = g >> 1;
 			#pragma unroll 1
-			for (uint32_t u = 0; u < n_units; ++u, ++c) {
-				if (c % P2_ACCS != g) continue;           // another warp's accumulator
+			for (uint32_t u = (grp - c_step) & 1u; u < n_units; u += 2) {
+				const uint32_t c = c_step + u;
+				const uint32_t acc = c % P2_ACCS;
+				const uint32_t acc_release = acc_empty_base + acc * 8u;
 				TC_T(e0);
 				if (ok) {
 					bool w = true;
-					if (lane == 0) w = pair_wait(&bars->acc_full[g], (c / P2_ACCS) & 1u, abort_flag, peer_abort_addr);
+					if (lane == 0) w = pair_wait(&bars->acc_full[acc], (c / P2_ACCS) & 1u, abort_flag, peer_abort_addr);
 					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
 				}
 				TC_T(e1);
@@ -330,34 +344,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				if (ok) {
 					ptx::tc_fence_after();
 					const uint32_t j = u >> 1, h = u & 1u;
-					#pragma unroll 1
-					for (uint32_t r = 0; r < 2; ++r) {
-						// columns [r*64, r*64+64) of the accumulator are rows h*64.. of CTA r's half of tile j
-						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + g * P2_UNIT_COLS + r * 64u;
-						uint32_t v0[32], v1[32];
-						ptx::tmem_ld32(taddr, v0);
-						ptx::tmem_ld32(taddr + 32, v1);
-						ptx::tmem_ld_wait();
-						if (r == 1) {
-							// last load: the tensor cores may fill this accumulator again
-							ptx::tc_fence_before();
-							__syncwarp();
-							if (lane == 0) ptx::mbar_arrive_cluster(acc_empty_addr);
-						}
-						const uint32_t chunk0 = j * 8u + r * 4u + h * 2u;    // in units of 32 means
-						const uint32_t col0 = chunk0 * 32u;
-						const uint32_t left = k > col0 ? k - col0 : 0u;      // columns at or behind k are padding
-						if (left >= 64) {
-							chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
-							chunk_update<false>(v1, key_mult, chunk0 + 1, 32, best, second, bchunk);
-						} else {
-							if (left > 0) chunk_update<true>(v0, key_mult, chunk0, left, best, second, bchunk);
-							if (left > 32) chunk_update<true>(v1, key_mult, chunk0 + 1, left - 32, best, second, bchunk);
-						}
-					}
+					// columns [colhalf*64, +64) of the accumulator are rows h*64.. of CTA colhalf's half of tile j
+					const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * P2_UNIT_COLS + colhalf * 64u;
+					uint32_t v0[32], v1[32];
+					ptx::tmem_ld32(taddr, v0);
+					ptx::tmem_ld32(taddr + 32, v1);
+					ptx::tmem_ld_wait();
+					ptx::tc_fence_before();
+					__syncwarp();
+					if (lane == 0) ptx::mbar_arrive_cluster(acc_release);
+					const uint32_t chunk0 = j * 8u + colhalf * 4u + h * 2u;    // in units of 32 means
+					chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
+					chunk_update<false>(v1, key_mult, chunk0 + 1, 32, best, second, bchunk);
 				} else {
 					__syncwarp();
-					if (lane == 0) ptx::mbar_arrive_cluster(acc_empty_addr);
+					if (lane == 0) ptx::mbar_arrive_cluster(acc_release);
 				}
 				if (pending) flush_sums();
 				TC_T(e2);
