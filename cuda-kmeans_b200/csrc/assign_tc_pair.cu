@@ -280,6 +280,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 		const uint32_t g = (warp - 2) >> 2;           // 0..3
 		const uint32_t row = q * 32 + lane;
 		const float ulp = kc.pow2 * 1.1920929e-07f;   // spacing of the values inside [P, 2P)
+		const uint32_t merger = 1u;                   // group 1, lower column half (fills per step are even in number)
 		const uint32_t acc_empty_base = ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[0]), 0);
 		uint32_t it = 0;
 		bool ok = true;
@@ -293,6 +294,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 		bool pending = false;
 		uint32_t pend_it = 0;
 		auto flush_sums = [&]() {
+			if (g != merger) asm volatile("bar.sync %0, 128;" :: "r"(9u + q) : "memory");   // the final clusters are written
 			const uint32_t* s_mine = mg_state + 2 * 3 * 3 * TC_MTILE + (pend_it & 1u) * TC_MTILE;
 			const uint8_t* tile_hi = smem + a_off + (pend_it % n_abuf) * a_tile;
 			const uint32_t sub = lane >> 3, c4 = lane & 7u;
@@ -323,7 +325,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
 			const uint64_t p = (uint64_t)(2 * step + rank) * TC_MTILE + row;
 			float xn = 0.0f;
-			if (g == 0 && p < n) xn = xnorm[p];           // needed at the end of the step only: fetch early
+			if (g == merger && p < n) xn = xnorm[p];      // needed at the end of the step only: fetch early
 			// this warp's accumulator fills of the step: every second one, counted across steps; of
 			// each it takes 64 columns with one load and hands the accumulator back at once
 			const uint32_t c_step = it * n_units;
@@ -366,46 +368,52 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			}
 			if (pending) flush_sums();                    // a step without an accumulator for this warp
 			TC_T(e3);
-			// Warps 1..3 of a quarter hand their state to warp 0 through shared memory.  The slots
-			// alternate with the step count, so one barrier per step is enough: a slot is written again
-			// only after its reader has passed the barrier of the step in between.
+			// Three warps of a quarter hand their state to the fourth through shared memory and go on
+			// without waiting (bar.arrive); the fourth waits for them (bar.sync), merges and writes the
+			// results.  Slots and barrier numbers alternate with the step count.  No warp can be a whole
+			// step ahead of another: every accumulator fill needs all warps of both groups to have
+			// released the fill four before it.  The merging warp belongs to the group that serves the
+			// last fill of a step (it is the last to finish anyway) and has the second fill of the next.
 			uint32_t* mg = mg_state + (it & 1u) * (3 * 3 * TC_MTILE);
-			if (g > 0) {
-				uint32_t* dst = mg + (g - 1) * (3 * TC_MTILE);
+			const uint32_t merge_bar = 1u + (it & 1u) * 4u + q;
+			uint32_t mine = 0xFFFFFFFFu;                  // cluster of this thread's point (merging warp)
+			if (g != merger) {
+				uint32_t* dst = mg + (g < merger ? g : g - 1) * (3 * TC_MTILE);
 				dst[row] = best; dst[TC_MTILE + row] = second; dst[2 * TC_MTILE + row] = bchunk;
-			}
-			asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");   // the four warps that share these 32 rows
-			uint32_t mine = 0xFFFFFFFFu;                  // cluster of this thread's point (warps with g == 0)
-			if (g == 0 && p < n && ok) {
-				#pragma unroll
-				for (uint32_t o = 0; o < 3; ++o) {
-					const uint32_t* src = mg + o * (3 * TC_MTILE);
-					const uint32_t ob = src[row], os = src[TC_MTILE + row], oc = src[2 * TC_MTILE + row];
-					second = umin3(second, os, max(best, ob));
-					bchunk = ob < best ? oc : bchunk;
-					best = min(best, ob);
-				}
-				// key - key_base = M * mantissa + column
-				const uint32_t bm = (best - key_base) / key_mult;
-				mine = bchunk * 32u + ((best - key_base) - bm * key_mult);
-				asg[p] = mine;
-				const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
-				const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
-				if (gap <= margin) {
-					const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-					if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
-					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+				asm volatile("bar.arrive %0, 128;" :: "r"(merge_bar) : "memory");
+			} else {
+				asm volatile("bar.sync %0, 128;" :: "r"(merge_bar) : "memory");
+				if (p < n && ok) {
+					#pragma unroll
+					for (uint32_t o = 0; o < 3; ++o) {
+						const uint32_t* src = mg + o * (3 * TC_MTILE);
+						const uint32_t ob = src[row], os = src[TC_MTILE + row], oc = src[2 * TC_MTILE + row];
+						second = umin3(second, os, max(best, ob));
+						bchunk = ob < best ? oc : bchunk;
+						best = min(best, ob);
+					}
+					// key - key_base = M * mantissa + column
+					const uint32_t bm = (best - key_base) / key_mult;
+					mine = bchunk * 32u + ((best - key_base) - bm * key_mult);
+					asg[p] = mine;
+					const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
+					const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
+					if (gap <= margin) {
+						const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
+						if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
+						else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+					}
 				}
 			}
 			if (fuse_acc != nullptr) {
 				// Update sums: the final clusters go to shared memory; the reductions themselves are
 				// sent later (flush_sums), spread over the next step.
-				uint32_t* s_mine = mg_state + 2 * 3 * 3 * TC_MTILE + (it & 1u) * TC_MTILE;
-				if (g == 0) {
+				if (g == merger) {
+					uint32_t* s_mine = mg_state + 2 * 3 * 3 * TC_MTILE + (it & 1u) * TC_MTILE;
 					s_mine[row] = mine;
 					if (mine != 0xFFFFFFFFu) atomicAdd(&fuse_counts[mine], 1u);
+					asm volatile("bar.arrive %0, 128;" :: "r"(9u + q) : "memory");
 				}
-				asm volatile("bar.sync %0, 128;" :: "r"(1u + q) : "memory");
 				pending = true;
 				pend_it = it;
 			}
