@@ -35,9 +35,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 V100_PUBLISHED_GEVALS = 84.4  # reference's best variant, N=2M d=32 k=1024, V100 (results/README.md:20)
-# dram__bytes_read.sum + dram__bytes_write.sum of one assign_tc_kernel launch on workload c2, from the ncu
-# capture summarised in profiles/assign_tc_kernel_c2.md (546.99 MB + 12.44 MB).
-C2_ASSIGN_TC_DRAM_BYTES = 559.4e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one assign_tc_pair_kernel launch on workload c2: the ncu
+# capture summarised in profiles/assign_tc_pair_kernel_c2.md was taken on a quarter of the points
+# (138.88 MB + 4.71 MB); the traffic is the point operands, read once, so it scales with the points: x 4.
+C2_ASSIGN_TC_DRAM_BYTES = 574.4e6
 
 
 def parse_args():
@@ -51,6 +52,8 @@ def parse_args():
     ap.add_argument("--n", type=int, default=None, help="override the number of points (per job)")
     ap.add_argument("--assign", default="auto", choices=["auto", "exact", "simt", "tc"])
     ap.add_argument("--update", default="auto", choices=["auto", "shared", "global", "rows", "sorted"])
+    ap.add_argument("--no-fuse", action="store_true",
+                    help="keep the update a launch of its own where the assignment kernel could accumulate the sums")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seed", type=int, default=42)
@@ -271,6 +274,8 @@ def main():
     torch.cuda.set_stream(stream)
     km.set_stream(stream.cuda_stream)
     km.initialize_device(dim, k, count, args.steps, dev_points.data_ptr(), dev_means.data_ptr())
+    if args.no_fuse:
+        km.set_option("fuse_update", 0)
     if world > 1:
         uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
@@ -363,7 +368,7 @@ def main():
             ach = flops_iter / (assign_ms * 1e-3) / 1e12
             traffic = C2_ASSIGN_TC_DRAM_BYTES if (args.workload == "c2" and not args.n and counters["assign_variant"] == "tc") else None
             roofline = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
-                        "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write)",
+                        "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from a quarter-size capture)",
                         "kernel": "assignment (%s)" % counters["assign_variant"],
                         "kernel_ms": assign_ms,
                         "peak_note": "TF32 dense taken as half the %s bf16 burst peak; 3xTF32 issues 3 tensor "
