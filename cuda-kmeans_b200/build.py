@@ -14,7 +14,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbkm.so")
 SOURCES = ["api.cu", "assign_simt.cu", "assign_tc.cu", "assign_tc_pair.cu", "update.cu", "no_alloc.cu"]
-HEADERS = ["common.cuh", "kernels.cuh", "ptx.cuh", os.path.join("..", "..", "include", "bkm.h")]
+HEADERS = ["common.cuh", "kernels.cuh", "ptx.cuh", "tc_common.cuh", os.path.join("..", "..", "include", "bkm.h")]
+CLI_SRC = os.path.join(HERE, "cli", "bkm_kmeans.cpp")
+CLI = os.path.join(HERE, "bkm-kmeans")
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -60,5 +62,18 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def build_cli(force=False):
+    """Compiles the command-line harness (cli/bkm_kmeans.cpp) next to the library; returns its path."""
+    lib = build()
+    if not force and os.path.exists(CLI) and os.path.getmtime(CLI) >= max(os.path.getmtime(CLI_SRC), os.path.getmtime(lib)):
+        return CLI
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc, "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(HERE, "..", "include"), CLI_SRC, "-L", HERE, "-lbkm",
+           "-Xlinker", "-rpath=$ORIGIN", "-o", CLI]
+    subprocess.check_call(cmd)
+    return CLI
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_cli(force="--force" in sys.argv))
