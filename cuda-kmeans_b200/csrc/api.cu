@@ -158,6 +158,7 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 		w.tp.a_hi = reinterpret_cast<float*>(take(aplane));
 		w.tp.a_lo = reinterpret_cast<float*>(take(aplane));
 		w.tp.xnorm = reinterpret_cast<float*>(take((size_t)w.tp.n_pad * sizeof(float)));
+		w.tp.partial = w.tp.d_pad > 32 ? reinterpret_cast<uint32_t*>(take((size_t)bkm::TC_JSPLIT * 3 * w.tp.n_pad * sizeof(uint32_t))) : nullptr;
 	}
 	w.bytes = off;
 	return w;

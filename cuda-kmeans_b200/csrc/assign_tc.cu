@@ -201,12 +201,52 @@ static_assert(sizeof(TcBars) <= 256, "barrier block too large");
 static_assert(SM_ALLOC <= 227 * 1024, "shared memory budget exceeded");
 static_assert(KL_AUG_OFF + 2 * AUG_BYTES <= SM_AAUG_OFF, "K-loop stages overlap the constant tile");
 
+// The end of a point's arg-min: decode the winning key (key - key_base = M * mantissa + column),
+// write the assignment, and queue the point for the exact kernel when best and second are closer
+// than `margin`.
+__device__ __forceinline__ void finish_point(uint32_t best, uint32_t second, uint32_t bchunk, uint32_t key_base, uint32_t key_mult,
+	float ulp, float margin, uint64_t p, uint64_t n, uint32_t* __restrict__ asg, Control* __restrict__ ctl, uint32_t* __restrict__ flag_list)
+{
+	const uint32_t bm = (best - key_base) / key_mult;
+	asg[p] = bchunk * 32u + ((best - key_base) - bm * key_mult);
+	// keys are (mantissa * M + column): the difference of the quotients counts value spacings
+	const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
+	if (gap <= margin) {
+		const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
+		if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
+		else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+	}
+}
+
+// Combines the partial arg-min results of the CTAs that shared the mean tiles of a point block.
+__global__ void __launch_bounds__(256) merge_partials_kernel(const uint32_t* __restrict__ partial, uint64_t partial_stride, uint32_t parts,
+	const float* __restrict__ xnorm, uint32_t* __restrict__ asg, uint64_t n, Control* __restrict__ ctl, int slot,
+	uint32_t* __restrict__ flag_list, float margin_coef)
+{
+	const float c2max = ctl->cmax2[slot];
+	const KeyConsts kc = make_key_consts(ctl->xmax2, c2max);
+	const float ulp = kc.pow2 * 1.1920929e-07f;
+	for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (uint64_t)gridDim.x * blockDim.x) {
+		uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
+		for (uint32_t part = 0; part < parts; ++part) {
+			const uint32_t* src = partial + (size_t)part * 3 * partial_stride + p;
+			const uint32_t ob = src[0], os = src[partial_stride], oc = src[2 * partial_stride];
+			second = umin3(second, os, max(best, ob));
+			bchunk = ob < best ? oc : bchunk;
+			best = min(best, ob);
+		}
+		finish_point(best, second, bchunk, kc.key_base, kc.key_mult, ulp, margin_coef * (xnorm[p] + c2max) + 4.0f * ulp,
+			p, n, asg, ctl, flag_list);
+	}
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
 	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
 	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t nt_cols, uint32_t kw, uint32_t kchunks, uint32_t ksteps, uint32_t idesc,
-	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef)
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef,
+	uint32_t jsplit, uint32_t* __restrict__ partial, uint64_t partial_stride)
 {
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -217,6 +257,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 	const uint32_t n_ctiles = k_pad / nt_cols;
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
+	// With jsplit > 1, `jsplit` neighbouring CTAs work on the same block of points and share the
+	// mean tiles among them (K loop with many mean tiles: the point tiles are re-read for every mean
+	// tile, and fewer distinct point blocks in flight keep those re-reads in L2).  Each writes its
+	// partial arg-min; merge_partials_kernel combines them.
+	const uint32_t jpart = blockIdx.x % jsplit, bid = blockIdx.x / jsplit, nbid = gridDim.x / jsplit;
+	const uint32_t jper = (n_ctiles + jsplit - 1) / jsplit;
+	const uint32_t j_begin = min(n_ctiles, jpart * jper), j_end = min(n_ctiles, j_begin + jper);
 	// Resident-points layout (dim <= 32).  With a single centroid tile (k <= 256) that tile is loaded
 	// once and stays, and the space of the second stage holds two more point tiles, so that the
 	// next block's points arrive while this block is still being multiplied.
@@ -275,9 +322,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			uint32_t aug_count = 0;
 			if (kchunks > 1) {
 				// K-loop mode: one (block of two point tiles, mean tile, 16-dimension slice) per stage
-				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+				for (uint32_t blk = bid; blk < nblocks && ok; blk += nbid) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						{
 							const uint32_t as = aug_count & 1u, au = aug_count >> 1;
 							ok = wait_or_abort(&bars->aug_empty[as], (au & 1u) ^ 1u, abort_flag);
@@ -308,7 +355,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			} else {
 				uint32_t g = 0;                       // running count of point tiles = position in the A ring
 				bool b_loaded = false;
-				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+				for (uint32_t blk = bid; blk < nblocks && ok; blk += nbid) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 					for (uint32_t i = 0; i < tiles && ok; ++i, ++g) {
 						const uint32_t buf = g % n_abuf, u = g / n_abuf;
@@ -321,7 +368,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						ptx::tma_load_2d(dst + a_plane, &tm_a_lo, 0, row, &bars->a_full[buf]);
 						++a_use[buf];
 					}
-					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						if (b_resident && b_loaded) break;
 						const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
 						ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
@@ -363,9 +410,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			if (kchunks > 1) {
 				// K-loop mode: both accumulators of the block collect the slices of one mean tile together
 				uint32_t aug_count = 0;
-				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+				for (uint32_t blk = bid; blk < nblocks && ok; blk += nbid) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						for (uint32_t i = 0; i < tiles && ok; ++i) {
 							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
 							++acc_use[i];
@@ -420,9 +467,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 #endif
 				uint32_t g = 0;                       // position of the block's first tile in the A ring
 				bool b_ready = false;
-				for (uint32_t blk = blockIdx.x; blk < nblocks && ok; blk += gridDim.x) {
+				for (uint32_t blk = bid; blk < nblocks && ok; blk += nbid) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
-					for (uint32_t j = 0; j < n_ctiles && ok; ++j) {
+					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						const uint32_t s = b_resident ? 0u : b_count % TC_NB, u = b_count / TC_NB;
 						TC_T(c0);
 						if (!(b_resident && b_ready)) {
@@ -438,7 +485,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						for (uint32_t i = 0; i < tiles; ++i) {
 							const uint32_t buf = (g + i) % n_abuf, ua = (g + i) / n_abuf;
 							TC_T(c2);
-							if (j == 0) {
+							if (j == j_begin) {
 								ok = wait_or_abort(&bars->a_full[buf], ua & 1u, abort_flag);
 								if (!ok) break;
 							}
@@ -466,7 +513,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
 								ptx::mma_tf32(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
 								ptx::mma_commit(&bars->acc_full[i]);
-								if (j == n_ctiles - 1) ptx::mma_commit(&bars->a_empty[buf]);
+								if (j == j_end - 1) ptx::mma_commit(&bars->a_empty[buf]);
 							}
 							__syncwarp();
 							TC_T(c5);
@@ -515,7 +562,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		long long e_wait = 0, e_ld = 0, e_cmp = 0, e_merge = 0;
 		const long long e_start = clock64();
 #endif
-		for (uint32_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x, ++blk_count) {
+		for (uint32_t blk = bid; blk < nblocks; blk += nbid, ++blk_count) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 			if (i >= tiles) continue;              // odd tail: this accumulator is not used in the last block
 			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
@@ -524,7 +571,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			float xn = 0.0f;
 			if (half == 0 && p < n) xn = xnorm[p];
 			#pragma unroll 1
-			for (uint32_t j = 0; j < n_ctiles; ++j) {
+			for (uint32_t j = j_begin; j < j_end; ++j) {
 				TC_T(e0);
 				if (ok) {
 					// one lane polls the barrier, the warp follows
@@ -588,15 +635,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				second = umin3(second, os, max(best, ob));
 				bchunk = ob < best ? oc : bchunk;
 				best = min(best, ob);
-				// key - key_base = M * mantissa + column
-				const uint32_t bm = (best - key_base) / key_mult;
-				asg[p] = bchunk * 32u + ((best - key_base) - bm * key_mult);
-				const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
-				const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
-				if (gap <= margin) {
-					const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-					if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
-					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
+				if (partial != nullptr) {
+					// this CTA saw only its share of the mean tiles: the keys go out as they are
+					uint32_t* dst = partial + (size_t)jpart * 3 * partial_stride + p;
+					dst[0] = best; dst[partial_stride] = second; dst[2 * partial_stride] = bchunk;
+				} else {
+					finish_point(best, second, bchunk, key_base, key_mult, ulp, margin_coef * (xn + c2max) + 4.0f * ulp,
+						p, n, asg, ctl, flag_list);
 				}
 			}
 			TC_T(e6);
@@ -742,9 +787,18 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	if (tc_plan_uses_pair(p))
 		return launch_assign_tc_pair(p->a_hi, p->a_lo, p->bh_hi, p->bh_lo, p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles,
 			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim);
-	assign_tc_kernel<<<grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
+	// K loop with several mean tiles: pairs of neighbouring CTAs share a point block (see the kernel)
+	const uint32_t n_ctiles = p->tm.k_pad / p->nt_cols;
+	const uint32_t jsplit = (kloop && n_ctiles >= 2 * TC_JSPLIT && p->tp.partial != nullptr && p->sm_count >= (int)TC_JSPLIT) ? TC_JSPLIT : 1u;
+	const uint32_t grid_j = jsplit * std::min<uint32_t>(nblocks, (uint32_t)p->sm_count / jsplit);
+	assign_tc_kernel<<<jsplit > 1 ? grid_j : grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
 		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,
-		ctl, slot, flag_list, margin_coef);
+		ctl, slot, flag_list, margin_coef, jsplit, jsplit > 1 ? p->tp.partial : nullptr, p->tp.n_pad);
+	if (jsplit > 1) {
+		const uint32_t mgrid = (uint32_t)std::min<uint64_t>((p->s.n + 255) / 256, (uint64_t)p->sm_count * 8);
+		merge_partials_kernel<<<mgrid, 256, 0, stream>>>(p->tp.partial, p->tp.n_pad, jsplit, p->tp.xnorm, asg, p->s.n, ctl, slot,
+			flag_list, margin_coef);
+	}
 	return cudaGetLastError();
 }
 

@@ -33,7 +33,9 @@ struct TcPoints {
 	float* xnorm;    // [n_pad] |x|^2
 	uint64_t n_pad;  // n rounded up to TC_MTILE
 	uint32_t d_pad;
+	uint32_t* partial; // K loop only (d_pad > 32): [TC_JSPLIT][3][n_pad] partial arg-min keys, else null
 };
+constexpr uint32_t TC_JSPLIT = 2;   // CTAs that can share the mean tiles of one point block in the K loop
 
 // ---- means preparation + divide (update.cu) ----
 
