@@ -35,7 +35,7 @@ SYMBOLS = [
     "bkm_run_async", "bkm_synchronize", "bkm_get_means", "bkm_get_assignment", "bkm_get_sizes",
     "bkm_device_means", "bkm_device_assignment", "bkm_set_means", "bkm_iterations_done",
     "bkm_phase_ms", "bkm_counters", "bkm_comm_unique_id", "bkm_comm_init", "bkm_shard_range",
-    "bkm_kmeans_host_f32", "bkm_update_noalloc_f32",
+    "bkm_kmeans_host_f32", "bkm_update_noalloc_f32", "bkm_selftest_wait_timeout",
 ]
 
 
@@ -101,6 +101,7 @@ def lib():
     L.bkm_shard_range.argtypes = [u64, ci, ci, ctypes.POINTER(u64), ctypes.POINTER(u64)]
     L.bkm_kmeans_host_f32.argtypes = [vp, vp, vp, u64, u32, u32, u32, ci, ci, ci]
     L.bkm_update_noalloc_f32.argtypes = [vp, vp, vp, vp, u64, u32, u32, ci, ci, vp]
+    L.bkm_selftest_wait_timeout.argtypes = [vp, u32, vp]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("bkm_last_error", "bkm_workspace_bytes"):
@@ -187,6 +188,12 @@ def iterate(points, means_in, means_out, sizes, assignment, n, k, dim, layout, l
 
 def workspace_check(workspace, stream=0):
     check(lib().bkm_workspace_check(workspace, stream))
+
+
+def selftest_wait_timeout(workspace, limit_ms=50, stream=0):
+    """Enqueues the bounded-wait self-test (bkm_selftest_wait_timeout): a wait that runs out after
+    limit_ms and records the time-out status in the workspace's control block."""
+    check(lib().bkm_selftest_wait_timeout(workspace, int(limit_ms), stream))
 
 
 def kmeans_host(points, means, n, k, dim, iters, layout=LAYOUT_AOS, layout_means=None, device=0):

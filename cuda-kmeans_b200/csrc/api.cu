@@ -442,6 +442,20 @@ int bkm_workspace_check(const void* workspace, void* stream)
 	return BKM_OK;
 }
 
+// Exercises the failure path of the kernels' bounded waits without breaking anything: a one-thread
+// kernel waits `limit_ms` (1..1000) for a barrier nobody arrives on, gives up and records
+// STATUS_WAIT_TIMEOUT in the workspace's control block.  Returns BKM_OK after enqueueing; the
+// status is then visible to bkm_workspace_check (BKM_ERR_DEVICE), and the workspace must be
+// cleared (or passed to a stateless call, which clears the status) before further use.
+int bkm_selftest_wait_timeout(void* workspace, uint32_t limit_ms, void* stream)
+{
+	if (!workspace) return fail(BKM_ERR_INVALID, "workspace is null");
+	if (limit_ms < 1 || limit_ms > 1000) return fail(BKM_ERR_INVALID, "limit_ms must be 1..1000");
+	CUDA_TRY(bkm::launch_wait_timeout_selftest(reinterpret_cast<bkm::Control*>(workspace), (uint64_t)limit_ms * 1000000ull,
+		static_cast<cudaStream_t>(stream)));
+	return BKM_OK;
+}
+
 // ---- driver -------------------------------------------------------------------------------------
 
 int bkm_create(const bkm_config_t* cfg, bkm_handle_t* out)

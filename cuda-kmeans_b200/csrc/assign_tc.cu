@@ -664,6 +664,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 }
 
 // ------------------------------------------------------------------------------------------
+// self-test of the bounded wait
+// ------------------------------------------------------------------------------------------
+
+// One thread waits for a barrier phase that nothing will ever complete, with a short limit, and
+// reports through the status word exactly as the assignment kernels do when a wait runs out.
+__global__ void wait_timeout_selftest_kernel(Control* ctl, uint64_t limit_ns)
+{
+	__shared__ uint64_t bar;
+	if (threadIdx.x == 0) {
+		ptx::mbar_init(&bar, 1);
+		ptx::fence_mbar_init();
+		if (!ptx::mbar_wait(&bar, 0, limit_ns)) atomicOr(&ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
+	}
+}
+
+cudaError_t launch_wait_timeout_selftest(Control* ctl, uint64_t limit_ns, cudaStream_t stream)
+{
+	wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(ctl, limit_ns);
+	return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
 

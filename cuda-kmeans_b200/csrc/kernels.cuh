@@ -102,4 +102,7 @@ bool tc_plan_can_fuse(const TcPlan* plan, const FusedAcc& f);
 cudaError_t launch_assign_tc(TcPlan* plan, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
 	float margin_scale, cudaStream_t stream, const FusedAcc* fused = nullptr);
 
+// A wait that is made to run out (nothing ever arrives): sets STATUS_WAIT_TIMEOUT in `ctl` after `limit_ns`.
+cudaError_t launch_wait_timeout_selftest(Control* ctl, uint64_t limit_ns, cudaStream_t stream);
+
 } // namespace bkm

@@ -66,14 +66,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 	return ok != 0;
 }
 
-// Bounded wait.  Returns false if the phase did not complete within WAIT_LIMIT_NS.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+// Bounded wait.  Returns false if the phase did not complete within `limit_ns`.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = WAIT_LIMIT_NS)
 {
 	if (mbar_try_wait(bar, parity)) return true;
 	const uint64_t t0 = globaltimer_ns();
 	while (true) {
 		if (mbar_try_wait(bar, parity)) return true;
-		if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+		if (globaltimer_ns() - t0 > limit_ns) return false;
 	}
 }
 

@@ -133,6 +133,15 @@ int bkm_update_noalloc_f32(const float* points, const uint32_t* assignment, floa
  * after each runner (headers/cuda.hpp:76, 83). */
 int bkm_workspace_check(const void* workspace, void* stream);
 
+/* Self-test of the kernels' bounded waits (no counterpart in the reference, whose kernels have no
+ * waits): enqueues a one-thread kernel that waits limit_ms (1..1000) milliseconds for a barrier
+ * nobody arrives on, gives up, and records the "wait timeout" status bit in the control block at
+ * the start of `workspace` (at least 256 bytes of device memory) - the path an assignment kernel
+ * takes when a pipeline stage never delivers.  Nothing hangs and the context stays usable;
+ * bkm_workspace_check then reports BKM_ERR_DEVICE.  Clear the first 32 bytes of the workspace (or
+ * pass it to a stateless call, which does) before reusing it. */
+int bkm_selftest_wait_timeout(void* workspace, uint32_t limit_ms, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Fixed-iteration driver.  Replaces CudaKMeansAlgorithm (headers/cuda.hpp:19-112) behind the
  * IKMeansAlgorithm call sequence initialize / run / getMeans / getAssignment / cleanup

@@ -95,3 +95,28 @@ def test_unsupported_variant_is_reported(pkg, torch_cuda):
         pkg.assign(dev.points.data_ptr(), dev.means.data_ptr(), dev.assignment.data_ptr(), 64, 4, 64, 0, 0,
                    dev.ws_ptr, 256, variant=pkg.ASSIGN_EXACT)
     assert e.value.code == pkg.ERR_INVALID
+
+
+def test_bounded_wait_reports_instead_of_hanging(pkg, torch_cuda):
+    """A barrier wait that can never complete must give up after its limit, leave the status word
+    set for the host to read, and leave the context usable (no trap, no hang)."""
+    import time
+    ws = torch_cuda.zeros(4096, dtype=torch_cuda.uint8, device="cuda:0")
+    torch_cuda.cuda.synchronize()
+    t0 = time.perf_counter()
+    pkg.selftest_wait_timeout(ws.data_ptr(), limit_ms=100)
+    with pytest.raises(pkg.BkmError) as e:
+        pkg.workspace_check(ws.data_ptr())
+    dt = time.perf_counter() - t0
+    assert e.value.code == pkg.ERR_DEVICE
+    assert "wait timeout" in str(e.value)
+    assert 0.09 <= dt < 2.0, dt                      # it waited for the limit, and only for the limit
+    assert int(ws[:4].view(torch_cuda.int32).item()) & 1 == 1
+    # the context is alive: a normal assignment runs right after it
+    n, k, d = 3000, 300, 20
+    rng = np.random.default_rng(5)
+    rows = rng.random((n, d), dtype=np.float32)
+    dev = DeviceArrays(torch_cuda, pkg, rows.reshape(-1), rows[:k].reshape(-1).copy(), n, k, d)
+    pkg.assign(dev.points.data_ptr(), dev.means.data_ptr(), dev.assignment.data_ptr(), n, k, d, 0, 0, dev.ws_ptr, dev.ws_bytes_avail)
+    pkg.workspace_check(dev.ws_ptr)
+    assert int(dev.assignment.cpu().numpy().astype(np.uint32).max()) < k
