@@ -80,6 +80,9 @@ __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, volati
 	return false;
 }
 
+// KSTEPS = K steps of 8 dimensions per product (3 for dim 17..24, 4 for dim 25..32): a template
+// parameter so that the MMA-issuing warp runs a straight line of instructions.
+template<uint32_t KSTEPS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assign_tc_pair_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -202,7 +205,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 		// each CTA's half of a mean tile.  Four 128-column accumulators are in flight, which gives
 		// the hand-offs between the CTAs (a few hundred cycles each way) room to hide.
 		if (rank == 0) {
-			const uint64_t a_aug_desc = make_desc_aug(ptx::smem_u32(smem + P2_AAUG_OFF));
+			const uint32_t a_aug_lo = desc_lo_aug(ptx::smem_u32(smem + P2_AAUG_OFF));
 			const uint32_t peer = 1u;
 			// barriers are 8 bytes apart, and so are their images in the other CTA
 			const uint32_t a_empty_peer_base = ptx::map_to_cta(ptx::smem_u32(&bars->a_empty[0]), peer);
@@ -222,8 +225,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				if (!ok) break;
 				TC_T(c1);
 				TC_ACC(t_a, c0, c1);
+				// descriptor halves (see desc_lo_sw128): +2 in the address field = 32 bytes = one K step
 				const uint32_t a_addr = ptx::smem_u32(smem + a_off + buf * a_tile);
-				const uint64_t a_hi = make_desc_kw(a_addr, kw), a_lo = make_desc_kw(a_addr + a_plane, kw);
+				const uint32_t a_hi = desc_lo_sw128(a_addr), a_lo = desc_lo_sw128(a_addr + a_plane);
 				for (uint32_t u = 0; u < n_units; ++u, ++c) {
 					const uint32_t acc = c % P2_ACCS;
 					TC_T(c2);
@@ -234,23 +238,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 					ptx::tc_fence_after();
 					// rows [h*64, h*64+64) of this CTA's (and, at the same offset, the other CTA's) half of tile j
 					const uint32_t j = u >> 1, h = u & 1u;
-					const uint32_t b_addr = ptx::smem_u32(smem + j * b_tile) + h * (P2_UNIT_ROWS * kw * 4);
-					const uint64_t b_hi = make_desc_kw(b_addr, kw), b_lo = make_desc_kw(b_addr + b_plane, kw);
-					const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + baug_off + j * P2_AUG_HALF_BYTES) + h * (P2_UNIT_ROWS * 8 * 4));
+					const uint32_t b_addr = ptx::smem_u32(smem + j * b_tile) + h * (P2_UNIT_ROWS * TC_KCHUNK * 4);
+					const uint32_t b_hi = desc_lo_sw128(b_addr), b_lo = desc_lo_sw128(b_addr + b_plane);
+					const uint32_t b_aug_lo = desc_lo_aug(ptx::smem_u32(smem + baug_off + j * P2_AUG_HALF_BYTES) + h * (P2_UNIT_ROWS * 8 * 4));
 					const uint32_t d_tmem = tmem_base + acc * P2_UNIT_COLS;
 					if (ptx::elect_one()) {
-						// small cross terms first, then the dominant hi*hi term, then |c|^2;
-						// +2 in the descriptor's address field = 32 bytes = one K step
+						// small cross terms first, then the dominant hi*hi term, then |c|^2
+						ptx::mma_tf32_pair_halves<false>(d_tmem, a_lo, DESC_HI_SW128, b_hi, DESC_HI_SW128, idesc);
 						#pragma unroll
-						for (uint32_t ks = 0; ks < 4; ++ks)
-							if (ks < ksteps) ptx::mma_tf32_pair(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
+						for (uint32_t ks = 1; ks < KSTEPS; ++ks)
+							ptx::mma_tf32_pair_halves<true>(d_tmem, a_lo + 2 * ks, DESC_HI_SW128, b_hi + 2 * ks, DESC_HI_SW128, idesc);
 						#pragma unroll
-						for (uint32_t ks = 0; ks < 4; ++ks)
-							if (ks < ksteps) ptx::mma_tf32_pair(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
+						for (uint32_t ks = 0; ks < KSTEPS; ++ks)
+							ptx::mma_tf32_pair_halves<true>(d_tmem, a_hi + 2 * ks, DESC_HI_SW128, b_lo + 2 * ks, DESC_HI_SW128, idesc);
 						#pragma unroll
-						for (uint32_t ks = 0; ks < 4; ++ks)
-							if (ks < ksteps) ptx::mma_tf32_pair(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
-						ptx::mma_tf32_pair(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
+						for (uint32_t ks = 0; ks < KSTEPS; ++ks)
+							ptx::mma_tf32_pair_halves<true>(d_tmem, a_hi + 2 * ks, DESC_HI_SW128, b_hi + 2 * ks, DESC_HI_SW128, idesc);
+						ptx::mma_tf32_pair_halves<true>(d_tmem, a_aug_lo, DESC_HI_AUG, b_aug_lo, DESC_HI_AUG, idesc);
 						ptx::mma_commit_pair(acc_full_own + acc * 8u);
 						ptx::mma_commit_pair(acc_full_peer + acc * 8u);
 						if (u == n_units - 1) {
@@ -444,7 +448,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 // GPCs, and a GPC may have an odd number of SMs), so the answer can be less than SMs / 2.
 cudaError_t assign_tc_pair_prepare(int* max_pairs)
 {
-	cudaError_t e = cudaFuncSetAttribute(assign_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_ALLOC);
+	cudaError_t e = cudaFuncSetAttribute(assign_tc_pair_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_ALLOC);
+	if (e != cudaSuccess) return e;
+	e = cudaFuncSetAttribute(assign_tc_pair_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_ALLOC);
 	if (e != cudaSuccess) return e;
 	cudaLaunchConfig_t cfg = {};
 	cfg.gridDim = dim3(2 * 74, 1, 1);
@@ -456,7 +462,7 @@ cudaError_t assign_tc_pair_prepare(int* max_pairs)
 	cfg.attrs = &attr;
 	cfg.numAttrs = 1;
 	int clusters = 0;
-	e = cudaOccupancyMaxActiveClusters(&clusters, assign_tc_pair_kernel, &cfg);
+	e = cudaOccupancyMaxActiveClusters(&clusters, assign_tc_pair_kernel<4>, &cfg);
 	if (e != cudaSuccess) return e;
 	*max_pairs = clusters;
 	return cudaSuccess;
@@ -473,9 +479,16 @@ cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_
 	const uint32_t pairs = std::min<uint32_t>(steps, (uint32_t)max_pairs);
 	// c_format = f32 (bit 4), a/b format = tf32 (bits 7.., 10..), K-major both, N>>3 at bit 17, M>>4 at bit 24: M = 256 over the pair, N = 128
 	const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((P2_UNIT_COLS >> 3) << 17) | (((2 * TC_MTILE) >> 4) << 24);
-	assign_tc_pair_kernel<<<2 * pairs, TC_THREADS, P2_ALLOC, stream>>>(a_hi, a_lo, b_hi, b_lo, b_aug, xnorm, asg,
-		n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef,
-		fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim);
+	if (ksteps == 4)
+		assign_tc_pair_kernel<4><<<2 * pairs, TC_THREADS, P2_ALLOC, stream>>>(a_hi, a_lo, b_hi, b_lo, b_aug, xnorm, asg,
+			n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef,
+			fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim);
+	else if (ksteps == 3)
+		assign_tc_pair_kernel<3><<<2 * pairs, TC_THREADS, P2_ALLOC, stream>>>(a_hi, a_lo, b_hi, b_lo, b_aug, xnorm, asg,
+			n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef,
+			fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim);
+	else
+		return cudaErrorInvalidValue;       // dim 17..32 only: three or four K steps
 	return cudaGetLastError();
 }
 

@@ -252,6 +252,25 @@ __device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, 
 		:: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// The same with the two 64-bit shared-memory descriptors given as 32-bit halves.  Within one
+// operand tile only the low half (the address field) changes from instruction to instruction and
+// the high half is a constant of the layout, which leaves the issuing thread one 32-bit add per
+// operand and MMA instead of 64-bit descriptor arithmetic.  ACC = accumulate onto the destination.
+template<bool ACC>
+__device__ __forceinline__ void mma_tf32_pair_halves(uint32_t d_tmem, uint32_t a_lo32, uint32_t a_hi32, uint32_t b_lo32, uint32_t b_hi32, uint32_t idesc)
+{
+	asm volatile(
+		"{\n"
+		".reg .pred p;\n"
+		".reg .b64 da, db;\n"
+		"mov.b64 da, {%1, %2};\n"
+		"mov.b64 db, {%3, %4};\n"
+		"setp.ne.b32 p, %6, 0;\n"
+		"tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %5, p;\n"
+		"}\n"
+		:: "r"(d_tmem), "r"(a_lo32), "r"(a_hi32), "r"(b_lo32), "r"(b_hi32), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
+}
+
 // Arrives on the barrier at shared::cluster address `bar_addr` (of either CTA of the pair) once
 // all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar_addr)

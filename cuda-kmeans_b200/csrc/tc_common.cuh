@@ -95,6 +95,13 @@ __device__ __forceinline__ uint64_t make_desc_aug(uint32_t smem_addr)
 	return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (8ull << 16) | (16ull << 32) | (1ull << 46);
 }
 
+// The two 32-bit halves of those descriptors: the low half holds the address field (>> 4) and the
+// leading byte offset, the high half is a constant of the layout.
+constexpr uint32_t DESC_HI_SW128 = 64u | (1u << 14) | (2u << 29);     // 128-byte swizzle, 8-row groups 1024 B apart
+constexpr uint32_t DESC_HI_AUG = 16u | (1u << 14);                    // no swizzle, row groups 256 B apart
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_aug(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (8u << 16); }
+
 __device__ __forceinline__ uint32_t umin3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_u32(a, b, c); }
 
 // One 32-column chunk of an accumulator row.  The kernel adds a constant to every value so that
