@@ -185,6 +185,26 @@ cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints
 
 constexpr uint32_t TC_NA_MAX = 8;        // most point-tile buffers (single resident centroid tile, 16-float rows)
 
+// The 3xTF32 products of one operand-tile pair over KS steps of 8 dimensions: the small cross
+// terms lo*hi and hi*lo first, then the dominant hi*hi.  Operands are the low halves of the
+// descriptors (+2 in the address field = 32 bytes = one K step), `hi_word` their common high half.
+// `acc_first` = accumulate the very first product onto the destination.
+template<uint32_t KS>
+__device__ __forceinline__ void issue_products(uint32_t d_tmem, uint32_t a_hi, uint32_t a_lo, uint32_t b_hi, uint32_t b_lo,
+	uint32_t hi_word, uint32_t idesc, uint32_t acc_first)
+{
+	ptx::mma_tf32_halves(d_tmem, a_lo, hi_word, b_hi, hi_word, idesc, acc_first);
+	#pragma unroll
+	for (uint32_t ks = 1; ks < KS; ++ks)
+		ptx::mma_tf32_halves(d_tmem, a_lo + 2 * ks, hi_word, b_hi + 2 * ks, hi_word, idesc, 1);
+	#pragma unroll
+	for (uint32_t ks = 0; ks < KS; ++ks)
+		ptx::mma_tf32_halves(d_tmem, a_hi + 2 * ks, hi_word, b_lo + 2 * ks, hi_word, idesc, 1);
+	#pragma unroll
+	for (uint32_t ks = 0; ks < KS; ++ks)
+		ptx::mma_tf32_halves(d_tmem, a_hi + 2 * ks, hi_word, b_hi + 2 * ks, hi_word, idesc, 1);
+}
+
 struct TcBars {
 	uint64_t a_full[TC_NA_MAX];
 	uint64_t a_empty[TC_NA_MAX];
@@ -406,7 +426,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			uint32_t acc_use[TC_MA] = {0, 0};
 			uint32_t b_count = 0;
 			bool ok = true;
-			const uint64_t a_aug_desc = make_desc_aug(ptx::smem_u32(smem + SM_AAUG_OFF));
+			const uint32_t a_aug_lo = desc_lo_aug(ptx::smem_u32(smem + SM_AAUG_OFF));
+			const uint32_t desc_hi = kw == 32 ? DESC_HI_SW128 : DESC_HI_SW64;
 			if (kchunks > 1) {
 				// K-loop mode: both accumulators of the block collect the slices of one mean tile together
 				uint32_t aug_count = 0;
@@ -447,7 +468,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 									for (uint32_t ks = 0; ks < 2; ++ks)
 										if (ks < steps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
 									if (last) {
-										ptx::mma_tf32(d_tmem, a_aug_desc, make_desc_aug(ptx::smem_u32(smem + KL_AUG_OFF + as * AUG_BYTES)), idesc, 1);
+										ptx::mma_tf32(d_tmem, make_desc_aug(ptx::smem_u32(smem + SM_AAUG_OFF)), make_desc_aug(ptx::smem_u32(smem + KL_AUG_OFF + as * AUG_BYTES)), idesc, 1);
 										ptx::mma_commit(&bars->acc_full[i]);
 									}
 								}
@@ -480,8 +501,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						TC_T(c1);
 						TC_ACC(t_b, c0, c1);
 						const uint32_t b_addr = ptx::smem_u32(smem + sm_b_off + s * b_stage);
-						const uint64_t b_hi = make_desc_kw(b_addr, kw), b_lo = make_desc_kw(b_addr + b_plane, kw);
-						const uint64_t b_aug_desc = make_desc_aug(ptx::smem_u32(smem + sm_baug_off + s * AUG_BYTES));
+						const uint32_t b_hi = desc_lo_sw128(b_addr), b_lo = desc_lo_sw128(b_addr + b_plane);
+						const uint32_t b_aug_lo = desc_lo_aug(ptx::smem_u32(smem + sm_baug_off + s * AUG_BYTES));
 						for (uint32_t i = 0; i < tiles; ++i) {
 							const uint32_t buf = (g + i) % n_abuf, ua = (g + i) / n_abuf;
 							TC_T(c2);
@@ -497,21 +518,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							TC_ACC(t_acc, c3, c4);
 							ptx::tc_fence_after();
 							const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + buf * a_tile);
-							const uint64_t a_hi = make_desc_kw(a_addr, kw), a_lo = make_desc_kw(a_addr + a_plane, kw);
+							const uint32_t a_hi = desc_lo_sw128(a_addr), a_lo = desc_lo_sw128(a_addr + a_plane);
 							const uint32_t d_tmem = tmem_base + i * TC_NT_MAX;
 							if (ptx::elect_one()) {
-								// small cross terms first, then the dominant hi*hi term, then |c|^2;
-								// +2 in the descriptor's address field = 32 bytes = one K step
-								#pragma unroll
-								for (uint32_t ks = 0; ks < 4; ++ks)
-									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_lo + 2 * ks, b_hi + 2 * ks, idesc, ks > 0);
-								#pragma unroll
-								for (uint32_t ks = 0; ks < 4; ++ks)
-									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_lo + 2 * ks, idesc, 1);
-								#pragma unroll
-								for (uint32_t ks = 0; ks < 4; ++ks)
-									if (ks < ksteps) ptx::mma_tf32(d_tmem, a_hi + 2 * ks, b_hi + 2 * ks, idesc, 1);
-								ptx::mma_tf32(d_tmem, a_aug_desc, b_aug_desc, idesc, 1);
+								switch (ksteps) {
+								case 4: issue_products<4>(d_tmem, a_hi, a_lo, b_hi, b_lo, desc_hi, idesc, 0); break;
+								case 3: issue_products<3>(d_tmem, a_hi, a_lo, b_hi, b_lo, desc_hi, idesc, 0); break;
+								case 2: issue_products<2>(d_tmem, a_hi, a_lo, b_hi, b_lo, desc_hi, idesc, 0); break;
+								default: issue_products<1>(d_tmem, a_hi, a_lo, b_hi, b_lo, desc_hi, idesc, 0); break;
+								}
+								ptx::mma_tf32_halves(d_tmem, a_aug_lo, DESC_HI_AUG, b_aug_lo, DESC_HI_AUG, idesc, 1);
 								ptx::mma_commit(&bars->acc_full[i]);
 								if (j == j_end - 1) ptx::mma_commit(&bars->a_empty[buf]);
 							}

@@ -152,6 +152,23 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
 		:: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// The same with the two 64-bit shared-memory descriptors given as 32-bit halves: within one
+// operand tile only the low half (the address field) changes from instruction to instruction, so
+// the issuing thread spends one 32-bit add per operand and MMA instead of 64-bit arithmetic.
+__device__ __forceinline__ void mma_tf32_halves(uint32_t d_tmem, uint32_t a_lo32, uint32_t a_hi32, uint32_t b_lo32, uint32_t b_hi32, uint32_t idesc, uint32_t accumulate)
+{
+	asm volatile(
+		"{\n"
+		".reg .pred p;\n"
+		".reg .b64 da, db;\n"
+		"mov.b64 da, {%1, %2};\n"
+		"mov.b64 db, {%3, %4};\n"
+		"setp.ne.b32 p, %6, 0;\n"
+		"tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n"
+		"}\n"
+		:: "r"(d_tmem), "r"(a_lo32), "r"(a_hi32), "r"(b_lo32), "r"(b_hi32), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // Arrives on `bar` once all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar)
 {

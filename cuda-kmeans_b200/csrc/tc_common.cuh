@@ -99,6 +99,7 @@ __device__ __forceinline__ uint64_t make_desc_aug(uint32_t smem_addr)
 // leading byte offset, the high half is a constant of the layout.
 constexpr uint32_t DESC_HI_SW128 = 64u | (1u << 14) | (2u << 29);     // 128-byte swizzle, 8-row groups 1024 B apart
 constexpr uint32_t DESC_HI_AUG = 16u | (1u << 14);                    // no swizzle, row groups 256 B apart
+constexpr uint32_t DESC_HI_SW64 = 32u | (1u << 14) | (4u << 29);      // 64-byte swizzle, 8-row groups 512 B apart
 __device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
 __device__ __forceinline__ uint32_t desc_lo_aug(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (8u << 16); }
 
