@@ -105,6 +105,7 @@ Nccl* nccl()
 
 struct Workspace {
 	bkm::Control* ctl = nullptr;
+	void* split_scratch = nullptr; // re-check kernel: partial results of blocks that share a group (kept zeroed)
 	float* acc = nullptr;          // k*dim sums (replica 0; further replicas acc_replica_stride words apart)
 	uint32_t* counts = nullptr;    // k sizes (directly behind the sums of each replica)
 	uint32_t replicas = 1;
@@ -132,6 +133,7 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 		return p;
 	};
 	w.ctl = reinterpret_cast<bkm::Control*>(take(sizeof(bkm::Control)));
+	w.split_scratch = take(bkm::list_split_scratch_bytes());
 	const size_t kd = (size_t)k * dim;
 	w.replicas = bkm::acc_replicas(k, dim);
 	w.acc_bytes = (size_t)w.replicas * bkm::acc_replica_stride(k, dim) * sizeof(float);
@@ -254,7 +256,7 @@ int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* 
 		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream, fused));
 	}
 	if (mid) CUDA_TRY(cudaEventRecord(mid, stream));
-	CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, w.flag_list, &w.ctl->flag_count, sm_count, stream, fused));
+	CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, w.flag_list, &w.ctl->flag_count, sm_count, stream, fused, w.split_scratch));
 	return BKM_OK;
 }
 
@@ -357,6 +359,7 @@ static int stateless_assign(const float* points, const float* means, uint32_t* a
 	int rc = resolve_assign(variant, s, &v);
 	if (rc) return rc;
 	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	CUDA_TRY(cudaMemsetAsync(w.split_scratch, 0, bkm::list_split_scratch_bytes(), st));
 	bkm::TcPlan* plan = nullptr;
 	if (v == BKM_ASSIGN_SIMT) {
 		CUDA_TRY(cudaMemsetAsync(w.cprep, 0, w.cprep_bytes, st));

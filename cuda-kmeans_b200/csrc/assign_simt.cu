@@ -66,6 +66,24 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
 }
 
 
+// Four consecutive dimensions of one mean against the LIST_PB staged points: each point's four
+// coordinates come with one 128-bit shared load (the same address for the whole warp), and the
+// squares are added in dimension order, one rounding per operation, as in the scalar loop.
+template<int PB>
+__device__ __forceinline__ void add_four_dims(float (&sum)[PB], const float* sx, uint32_t dpad, uint32_t j,
+	float c0, float c1, float c2, float c3)
+{
+	#pragma unroll
+	for (int p = 0; p < PB; ++p) {
+		const float4 x = *reinterpret_cast<const float4*>(sx + p * dpad + j);
+		const float d0 = __fsub_rn(x.x, c0), d1 = __fsub_rn(x.y, c1), d2 = __fsub_rn(x.z, c2), d3 = __fsub_rn(x.w, c3);
+		sum[p] = __fadd_rn(sum[p], __fmul_rn(d0, d0));
+		sum[p] = __fadd_rn(sum[p], __fmul_rn(d1, d1));
+		sum[p] = __fadd_rn(sum[p], __fmul_rn(d2, d2));
+		sum[p] = __fadd_rn(sum[p], __fmul_rn(d3, d3));
+	}
+}
+
 // The same arithmetic for a list of queued points: one block per LIST_PB points, one mean per
 // thread at a time, so that a short list still fills the machine and every mean that is
 // fetched serves LIST_PB points.  Each distance is still summed in dimension order by a single
@@ -74,15 +92,18 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
 // directly (consecutive threads = consecutive means).
 constexpr int LIST_THREADS = 256;
 constexpr int LIST_PB = 4;
+constexpr uint32_t LIST_SPLIT_MAX_BLOCKS = 2048;   // grid size up to which a short list is shared between blocks
 
 template<bool SOA, bool SOAM>
 __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const float* __restrict__ pts,
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
 	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count,
-	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts, uint32_t resident_ok)
+	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts, uint32_t resident_ok,
+	unsigned long long* __restrict__ split_keys, uint32_t* __restrict__ split_arrive)
 {
-	extern __shared__ float sx[];                       // LIST_PB points (dpad floats each), then the means tile
+	extern __shared__ __align__(16) float sx[];         // LIST_PB points (dpad floats each), then the means tile
 	__shared__ uint32_t smoved[LIST_PB][2];             // (old, new) cluster of a point that changed, else old == new
+	__shared__ uint32_t s_last;                         // this block is the last of its group's blocks to finish
 	const uint32_t dpad = (d + 3) & ~3u;
 	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + (size_t)LIST_PB * dpad);
 	__shared__ float sbest[LIST_PB][LIST_THREADS / 32];
@@ -103,27 +124,79 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 			mres[m * ds + j] = means[e];
 		}
 	}
-	for (uint64_t w0 = (uint64_t)blockIdx.x * LIST_PB; w0 < total; w0 += (uint64_t)gridDim.x * LIST_PB) {
+	// Staging of a group's points: two dependent global reads (the list entry, then the coordinate)
+	// for each of the LIST_PB * d floats, all of them in flight together.  With few dimensions
+	// (at most two floats per thread) a thread fetches the NEXT group's floats into registers
+	// while the block works on the current group, which takes both reads off the block's
+	// critical path.  Unused slots of the last group repeat its first point.
+	const uint32_t pe = LIST_PB * d;
+	const bool prefetch = pe <= 2 * LIST_THREADS;
+	uint32_t pf_p[2], pf_j[2];
+	float pf[2] = {0.0f, 0.0f};
+	#pragma unroll
+	for (uint32_t r = 0; r < 2; ++r) {
+		const uint32_t e = tid + r * LIST_THREADS;
+		pf_p[r] = e / d;
+		pf_j[r] = e - pf_p[r] * d;
+	}
+	auto fetch = [&](uint64_t g0) {
+		#pragma unroll
+		for (uint32_t r = 0; r < 2; ++r) {
+			if (tid + r * LIST_THREADS < pe) {
+				const uint64_t idx = g0 + pf_p[r] < total ? g0 + pf_p[r] : g0;
+				pf[r] = pts[at<SOA>((uint64_t)list[idx], pf_j[r], n, d)];
+			}
+		}
+	};
+	// A short list (fewer groups than blocks) would leave most of the machine idle while a few
+	// blocks walk all k means one after another.  The blocks then share the groups: `splits`
+	// blocks take one group, each a contiguous range of the means, and combine their results in
+	// global memory (see below); every block has at most one piece of work.
+	const uint64_t groups = (total + LIST_PB - 1) / LIST_PB;
+	const uint32_t mchunks = (k + LIST_THREADS - 1) / LIST_THREADS;
+	uint32_t splits = 1;
+	if (split_keys != nullptr && groups > 0 && groups < gridDim.x && gridDim.x <= LIST_SPLIT_MAX_BLOCKS && mchunks > 1) {
+		splits = gridDim.x / (uint32_t)groups;
+		if (splits > mchunks) splits = mchunks;
+	}
+	const uint32_t split_group = blockIdx.x / splits, split_part = blockIdx.x - split_group * splits;
+	const uint32_t m_begin = splits > 1 ? (split_part * mchunks / splits) * LIST_THREADS : 0u;
+	const uint32_t m_end = splits > 1 ? min(k, ((split_part + 1) * mchunks / splits) * LIST_THREADS) : k;
+	const uint64_t stride = (uint64_t)gridDim.x * LIST_PB;        // with splits > 1 one step leaves the list
+	const uint64_t w_first = (uint64_t)(splits > 1 ? split_group : blockIdx.x) * LIST_PB;
+	if (prefetch && w_first < total) fetch(w_first);
+	for (uint64_t w0 = w_first; w0 < total; w0 += stride) {
 		const uint32_t np = total - w0 < LIST_PB ? (uint32_t)(total - w0) : LIST_PB;
 		__syncthreads();
-		for (uint32_t p = 0; p < LIST_PB; ++p) {
-			const uint64_t i = list[w0 + (p < np ? p : 0)];      // unused slots repeat the first point
-			for (uint32_t j = tid; j < d; j += LIST_THREADS) sx[p * dpad + j] = pts[at<SOA>(i, j, n, d)];
+		if (prefetch) {
+			#pragma unroll
+			for (uint32_t r = 0; r < 2; ++r)
+				if (tid + r * LIST_THREADS < pe) sx[pf_p[r] * dpad + pf_j[r]] = pf[r];
+		} else {
+			for (uint32_t e = tid; e < pe; e += LIST_THREADS) {
+				const uint32_t p = e / d, j = e - p * d;
+				const uint64_t idx = w0 + p < total ? w0 + p : w0;
+				sx[p * dpad + j] = pts[at<SOA>((uint64_t)list[idx], j, n, d)];
+			}
 		}
 		__syncthreads();
+		if (prefetch && w0 + stride < total) fetch(w0 + stride);
 		float best[LIST_PB];
 		uint32_t bidx[LIST_PB];
 		#pragma unroll
 		for (int p = 0; p < LIST_PB; ++p) { best[p] = INFINITY; bidx[p] = 0xffffffffu; }
-		for (uint32_t m0 = 0; m0 < k; m0 += LIST_THREADS) {
+		for (uint32_t m0 = m_begin; m0 < m_end; m0 += LIST_THREADS) {
 			const uint32_t m = m0 + tid;
 			float sum[LIST_PB];
 			#pragma unroll
 			for (int p = 0; p < LIST_PB; ++p) sum[p] = 0.0f;
 			if (resident) {
 				if (m < k) {
-					for (uint32_t j = 0; j < d; ++j) {
-						const float c = mres[m * ds + j];
+					const float* cm = mres + m * ds;
+					uint32_t j = 0;
+					for (; j + 4 <= d; j += 4) add_four_dims<LIST_PB>(sum, sx, dpad, j, cm[j], cm[j + 1], cm[j + 2], cm[j + 3]);
+					for (; j < d; ++j) {
+						const float c = cm[j];
 						#pragma unroll
 						for (int p = 0; p < LIST_PB; ++p) {
 							const float diff = __fsub_rn(sx[p * dpad + j], c);
@@ -133,8 +206,12 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 				}
 			} else if (SOAM) {
 				if (m < k) {
-					for (uint32_t j = 0; j < d; ++j) {
-						const float c = means[(size_t)j * k + m];
+					const float* cm = means + m;
+					uint32_t j = 0;
+					for (; j + 4 <= d; j += 4)
+						add_four_dims<LIST_PB>(sum, sx, dpad, j, cm[(size_t)j * k], cm[(size_t)(j + 1) * k], cm[(size_t)(j + 2) * k], cm[(size_t)(j + 3) * k]);
+					for (; j < d; ++j) {
+						const float c = cm[(size_t)j * k];
 						#pragma unroll
 						for (int p = 0; p < LIST_PB; ++p) {
 							const float diff = __fsub_rn(sx[p * dpad + j], c);
@@ -156,7 +233,10 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 					for (uint32_t r = 0; r < 32; ++r) tile[warp * 32 + r][lane] = seg[r];
 					__syncthreads();
 					const uint32_t jn = d - j0 < 32 ? d - j0 : 32;
-					for (uint32_t jj = 0; jj < jn; ++jj) {
+					uint32_t jj = 0;
+					for (; jj + 4 <= jn; jj += 4)
+						add_four_dims<LIST_PB>(sum, sx, dpad, j0 + jj, tile[tid][jj], tile[tid][jj + 1], tile[tid][jj + 2], tile[tid][jj + 3]);
+					for (; jj < jn; ++jj) {
 						const float c = tile[tid][jj];
 						#pragma unroll
 						for (int p = 0; p < LIST_PB; ++p) {
@@ -176,13 +256,13 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 		}
 		#pragma unroll
 		for (int p = 0; p < LIST_PB; ++p) {
-			#pragma unroll
-			for (int off = 16; off > 0; off >>= 1) {
-				const float ob = __shfl_xor_sync(0xffffffffu, best[p], off);
-				const uint32_t oi = __shfl_xor_sync(0xffffffffu, bidx[p], off);
-				if (oi != 0xffffffffu && (bidx[p] == 0xffffffffu || ob < best[p] || (ob == best[p] && oi < bidx[p]))) { best[p] = ob; bidx[p] = oi; }
-			}
-			if (lane == 0) { sbest[p][warp] = best[p]; sidx[p][warp] = bidx[p]; }
+			// Distances are >= +0, so their bit patterns order like the values: the warp's smallest
+			// distance, then the lowest index among the means that have it (a thread without a mean
+			// holds infinity and the index 0xffffffff).
+			const uint32_t bits = __float_as_uint(best[p]);
+			const uint32_t mn = __reduce_min_sync(0xffffffffu, bits);
+			const uint32_t mi = __reduce_min_sync(0xffffffffu, bits == mn ? bidx[p] : 0xffffffffu);
+			if (lane == 0) { sbest[p][warp] = __uint_as_float(mn); sidx[p][warp] = mi; }
 		}
 		__syncthreads();
 		if (tid < np) {
@@ -193,10 +273,36 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 				const uint32_t oi = sidx[tid][v];
 				if (oi != 0xffffffffu && (bi == 0xffffffffu || ob < b || (ob == b && oi < bi))) { b = ob; bi = oi; }
 			}
-			const uint32_t i = list[w0 + tid];
-			smoved[tid][0] = fix_acc ? asg[i] : bi;
-			smoved[tid][1] = bi;
-			asg[i] = bi;
+			if (splits > 1) {
+				// (distance, index) as one 64-bit key whose minimum is the smallest distance and, among
+				// equal distances, the lowest index; stored inverted so that zero means "nothing yet"
+				const unsigned long long key = ((unsigned long long)__float_as_uint(b) << 32) | bi;
+				atomicMax(&split_keys[w0 + tid], ~key);
+			} else {
+				const uint32_t i = list[w0 + tid];
+				smoved[tid][0] = fix_acc ? asg[i] : bi;
+				smoved[tid][1] = bi;
+				asg[i] = bi;
+			}
+		}
+		if (splits > 1) {
+			// The block that arrives last for its group finds all partial results in place; it
+			// writes the assignment and leaves keys and counter zeroed for the next launch.
+			__threadfence();
+			__syncthreads();
+			if (tid == 0) s_last = atomicAdd(&split_arrive[split_group], 1u) == splits - 1 ? 1u : 0u;
+			__syncthreads();
+			if (s_last == 0) break;
+			__threadfence();
+			if (tid < np) {
+				const unsigned long long key = ~atomicExch(&split_keys[w0 + tid], 0ull);
+				const uint32_t bi = (uint32_t)key;
+				const uint32_t i = list[w0 + tid];
+				smoved[tid][0] = fix_acc ? asg[i] : bi;
+				smoved[tid][1] = bi;
+				asg[i] = bi;
+			}
+			if (tid == 0) split_arrive[split_group] = 0;
 		}
 		if (fix_acc) {
 			// the fast pass has already added these points to the sums of the clusters it picked
@@ -215,9 +321,16 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	}
 }
 
-cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
-	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix)
+size_t list_split_scratch_bytes()
 {
+	return (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB * sizeof(unsigned long long) + (size_t)LIST_SPLIT_MAX_BLOCKS * sizeof(uint32_t);
+}
+
+cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix, void* split_scratch)
+{
+	unsigned long long* split_keys = reinterpret_cast<unsigned long long*>(split_scratch);
+	uint32_t* split_arrive = split_scratch ? reinterpret_cast<uint32_t*>(split_keys + (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB) : nullptr;
 	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
 		const size_t points_bytes = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float);
@@ -232,7 +345,7 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 		auto kern = assign_exact_list_kernel<SOA, SOAM>; \
 		if (lsmem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lsmem); if (e != cudaSuccess) return e; } \
 		kern<<<lgrid, LIST_THREADS, lsmem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count, \
-			fix ? fix->acc : nullptr, fix ? fix->counts : nullptr, resident_ok); \
+			fix ? fix->acc : nullptr, fix ? fix->counts : nullptr, resident_ok, split_keys, split_arrive); \
 	} while (0)
 		if (s.soa && s.soa_means) BKM_LAUNCH_LIST(true, true);
 		else if (s.soa && !s.soa_means) BKM_LAUNCH_LIST(true, false);

@@ -72,8 +72,12 @@ struct FusedAcc {
 	size_t rep_stride;
 	const float* center;  // the vector the split operands were centred by
 };
+// `split_scratch` (optional): list_split_scratch_bytes() of zeroed device memory, 8-byte aligned,
+// through which the blocks share the groups of a short list; the kernel leaves it zeroed.
+size_t list_split_scratch_bytes();
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
-	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix = nullptr);
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix = nullptr,
+	void* split_scratch = nullptr);
 
 // Small-d fast pass (dim <= 8): approximate distances, near-ties appended to flag_list.
 bool assign_simt_supported(const Shape& s);
