@@ -162,6 +162,8 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	const uint32_t split_group = blockIdx.x / splits, split_part = blockIdx.x - split_group * splits;
 	const uint32_t m_begin = splits > 1 ? (split_part * mchunks / splits) * LIST_THREADS : 0u;
 	const uint32_t m_end = splits > 1 ? min(k, ((split_part + 1) * mchunks / splits) * LIST_THREADS) : k;
+	const uint32_t n_chunks = (m_end - m_begin + LIST_THREADS - 1) / LIST_THREADS;
+	const uint32_t chunk_rot = (splits > 1 ? split_group : blockIdx.x) % n_chunks;
 	const uint64_t stride = (uint64_t)gridDim.x * LIST_PB;        // with splits > 1 one step leaves the list
 	const uint64_t w_first = (uint64_t)(splits > 1 ? split_group : blockIdx.x) * LIST_PB;
 	if (prefetch && w_first < total) fetch(w_first);
@@ -185,7 +187,10 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 		uint32_t bidx[LIST_PB];
 		#pragma unroll
 		for (int p = 0; p < LIST_PB; ++p) { best[p] = INFINITY; bidx[p] = 0xffffffffu; }
-		for (uint32_t m0 = m_begin; m0 < m_end; m0 += LIST_THREADS) {
+		// The blocks walk their chunks of 256 means starting at different chunks, so that blocks
+		// working at the same time do not all ask the L2 for the same rows at once.
+		for (uint32_t c = 0; c < n_chunks; ++c) {
+			const uint32_t m0 = m_begin + (c + chunk_rot < n_chunks ? c + chunk_rot : c + chunk_rot - n_chunks) * LIST_THREADS;
 			const uint32_t m = m0 + tid;
 			float sum[LIST_PB];
 			#pragma unroll
@@ -250,7 +255,8 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 				#pragma unroll
 				for (int p = 0; p < LIST_PB; ++p) {
 					const float dist = __fsqrt_rn(sum[p]);
-					if (bidx[p] == 0xffffffffu || dist < best[p]) { best[p] = dist; bidx[p] = m; }
+					// (the chunks come in rotated order: the lower index wins a tie explicitly)
+					if (bidx[p] == 0xffffffffu || dist < best[p] || (dist == best[p] && m < bidx[p])) { best[p] = dist; bidx[p] = m; }
 				}
 			}
 		}

@@ -224,13 +224,13 @@ static_assert(KL_AUG_OFF + 2 * AUG_BYTES <= SM_AAUG_OFF, "K-loop stages overlap 
 // The end of a point's arg-min: decode the winning key (key - key_base = M * mantissa + column),
 // write the assignment, and queue the point for the exact kernel when best and second are closer
 // than `margin`.
-__device__ __forceinline__ void finish_point(uint32_t best, uint32_t second, uint32_t bchunk, uint32_t key_base, uint32_t key_mult,
+__device__ __forceinline__ void finish_point(uint32_t best, uint32_t second, uint32_t bchunk, uint32_t key_base, uint32_t key_mult, uint32_t key_magic,
 	float ulp, float margin, uint64_t p, uint64_t n, uint32_t* __restrict__ asg, Control* __restrict__ ctl, uint32_t* __restrict__ flag_list)
 {
-	const uint32_t bm = (best - key_base) / key_mult;
+	const uint32_t bm = div_key(best - key_base, key_magic);
 	asg[p] = bchunk * 32u + ((best - key_base) - bm * key_mult);
 	// keys are (mantissa * M + column): the difference of the quotients counts value spacings
-	const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
+	const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)(div_key(second - key_base, key_magic) - bm) * ulp;
 	if (gap <= margin) {
 		const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
 		if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(256) merge_partials_kernel(const uint32_t* __r
 			bchunk = ob < best ? oc : bchunk;
 			best = min(best, ob);
 		}
-		finish_point(best, second, bchunk, kc.key_base, kc.key_mult, ulp, margin_coef * (xnorm[p] + c2max) + 4.0f * ulp,
+		finish_point(best, second, bchunk, kc.key_base, kc.key_mult, kc.key_magic, ulp, margin_coef * (xnorm[p] + c2max) + 4.0f * ulp,
 			p, n, asg, ctl, flag_list);
 	}
 }
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const float x2max = ctl->xmax2, c2max = ctl->cmax2[slot];
 	const KeyConsts kc = make_key_consts(x2max, c2max);
 	const float pow2 = kc.pow2;
-	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base;
+	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base, key_magic = kc.key_magic;
 	fill_a_aug(reinterpret_cast<float*>(smem + SM_AAUG_OFF), kc.offset_c, threadIdx.x, TC_THREADS);
 	ptx::fence_proxy_async();
 	ptx::tc_fence_before();
@@ -656,7 +656,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					uint32_t* dst = partial + (size_t)jpart * 3 * partial_stride + p;
 					dst[0] = best; dst[partial_stride] = second; dst[2 * partial_stride] = bchunk;
 				} else {
-					finish_point(best, second, bchunk, key_base, key_mult, ulp, margin_coef * (xn + c2max) + 4.0f * ulp,
+					finish_point(best, second, bchunk, key_base, key_mult, key_magic, ulp, margin_coef * (xn + c2max) + 4.0f * ulp,
 						p, n, asg, ctl, flag_list);
 				}
 			}

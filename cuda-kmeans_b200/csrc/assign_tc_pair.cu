@@ -139,7 +139,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	}
 	const float x2max = ctl->xmax2, c2max = ctl->cmax2[slot];
 	const KeyConsts kc = make_key_consts(x2max, c2max);
-	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base;
+	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base, key_magic = kc.key_magic;
 	fill_a_aug(reinterpret_cast<float*>(smem + P2_AAUG_OFF), kc.offset_c, threadIdx.x, TC_THREADS);
 	{
 		// This CTA's half of every tile's |c|^2 K step: 128 rows = 4 KiB, contiguous in global memory.
@@ -397,10 +397,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 						best = min(best, ob);
 					}
 					// key - key_base = M * mantissa + column
-					const uint32_t bm = (best - key_base) / key_mult;
+					const uint32_t bm = div_key(best - key_base, key_magic);
 					mine = bchunk * 32u + ((best - key_base) - bm * key_mult);
 					asg[p] = mine;
-					const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)((second - key_base) / key_mult - bm) * ulp;
+					const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)(div_key(second - key_base, key_magic) - bm) * ulp;
 					const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
 					if (gap <= margin) {
 						const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);

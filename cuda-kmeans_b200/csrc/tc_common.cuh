@@ -164,6 +164,7 @@ struct KeyConsts {
 	float offset_c;      // constant added to every |c|^2 - 2 x.c by the extra K step
 	uint32_t key_mult;   // M
 	uint32_t key_base;   // M * (bit pattern of P) mod 2^32
+	uint32_t key_magic;  // multiplier of div_key for this M
 };
 
 // Offset constant: every value |c|^2 - 2 x.c lies in [-X2, X2 + 2*C2] (X2, C2 = largest |x|^2,
@@ -186,7 +187,17 @@ __device__ __forceinline__ KeyConsts make_key_consts(float x2max, float c2max)
 	const uint32_t eb = __float_as_uint(kc.pow2) >> 23;
 	while (kc.key_mult < 63 && ((kc.key_mult * eb) & 511u) > 510u - kc.key_mult) kc.key_mult += 2;
 	kc.key_base = kc.key_mult * __float_as_uint(kc.pow2);
+	kc.key_magic = (uint32_t)((((unsigned long long)(64u - kc.key_mult)) << 32) / kc.key_mult) + 1u;
 	return kc;
+}
+
+// x / M for the key multipliers (33 <= M <= 63) without the integer-division sequence: with
+// magic = floor(2^32 * (64 - M) / M) + 1 and t = high word of magic * x, the quotient is
+// (t + (x - t) / 2) / 32, exact for every 32-bit x (division by an invariant, round-up method).
+__device__ __forceinline__ uint32_t div_key(uint32_t x, uint32_t magic)
+{
+	const uint32_t t = __umulhi(magic, x);
+	return (t + ((x - t) >> 1)) >> 5;
 }
 
 // The constant A operand of the extra K step (128 rows, no-swizzle layout): columns 0 and 1 are
