@@ -74,6 +74,22 @@ def test_duplicate_means_pick_lowest_index(pkg, torch_cuda):
             assert got.max() < 20, pkg.ASSIGN_NAMES[variant]
 
 
+def test_short_recheck_list_is_shared_between_blocks(pkg, torch_cuda, oracle_mod):
+    """Every mean exists twice, so every point is queued for the exact re-check; with more than 256
+    means and fewer groups of queued points than blocks, the blocks split the means of a group
+    between them and merge their partial results (lowest index on equal distances)."""
+    rng = np.random.default_rng(21)
+    for (n, k, d, layout, layout_means) in [(1200, 600, 24, 0, 0), (900, 1024, 32, 1, 1), (401, 2048, 40, 0, 1)]:
+        centres = rng.random((k, d), dtype=np.float32)
+        centres[k // 2:] = centres[:k // 2]
+        rows = rng.random((n, d), dtype=np.float32)
+        data, means = rows_to_layout(rows, layout), rows_to_layout(centres, layout_means)
+        want = oracle_mod.assign(data, means, n, k, d, layout, layout_means, threads=8)
+        assert want.max() < k // 2
+        got = _run_assign(pkg, torch_cuda, data, means, n, k, d, layout, layout_means, pkg.ASSIGN_TC)
+        assert np.array_equal(got, want), (n, k, d, int((got != want).sum()))
+
+
 def test_c2_shape_sample_matches_oracle(pkg, torch_cuda, oracle_mod, workloads):
     """Headline shape (dim 32, k 1024, SoA) on 2^16 points, every point checked."""
     n = 1 << 16
