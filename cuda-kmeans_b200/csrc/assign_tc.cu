@@ -583,9 +583,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			if (i >= tiles) continue;              // odd tail: this accumulator is not used in the last block
 			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
 			const uint64_t p = (uint64_t)(blk * TC_MA + i) * TC_MTILE + row;
-			// |x|^2 of this thread's point is only needed at the end of the block: fetch it now
-			float xn = 0.0f;
-			if (half == 0 && p < n) xn = xnorm[p];
+			float xn = 0.0f;                       // |x|^2 of this thread's point, needed at the end of the block
 			#pragma unroll 1
 			for (uint32_t j = j_begin; j < j_end; ++j) {
 				TC_T(e0);
@@ -616,6 +614,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							ptx::tc_fence_before();
 							__syncwarp();
 							if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[i]);
+							// fetched behind the hand-back of the block's last accumulator: the arithmetic on
+							// the chunks just loaded covers the latency
+							if (j == j_end - 1 && half == 0 && p < n) xn = xnorm[p];
 						}
 						TC_T(e3);
 						TC_ACC(e_ld, e2, e3);
