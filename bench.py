@@ -7,20 +7,25 @@ default workload is the headline configuration "c2": N = 2^21 points, dim 32, k 
 SoA points, i.i.d. uniform [0,1) coordinates, initial means = the first k points (seeded
 synthetic data; the reference measures on its own random generator, no dataset is involved).
 With N GPUs (one process per GPU, torchrun) every rank holds its own 2^21-point shard of a
-G * 2^21 point data set (weak scaling) and the k x dim sums and k sizes are all-reduced with
-NCCL every iteration.  `--workload c5 --scaling strong` runs the sharded 2^28-point
-configuration instead.
+G * 2^21 point data set (weak scaling) and the k x dim sums and k sizes are exchanged between
+the ranks every iteration.  `--workload c5 --scaling strong` runs the sharded 2^28-point
+configuration as the headline instead.
 
 Rank 0 prints ONE JSON line: `value` is giga distance evaluations per second (N_total * k /
 iteration time) with the data resident in HBM, timed with CUDA events on the launching stream
 and maximised over ranks; `e2e` is the same metric through the host-buffer C-ABI calls with
 the host<->device copies inside the timed region; `roofline` describes the dominant kernel
-(the assignment); `cpu_baseline` is the reference's serial CPU k-means on a bounded sample.
+(the assignment) against a TF32 matrix-multiply rate measured in the same run; `cpu_baseline`
+is the reference's serial CPU k-means on a bounded sample; `parity` is a check of one more
+iteration against the CPU oracle and across ranks (outside the timed region); `c5_strong` is
+the sharded 2^28-point configuration at the same number of GPUs, and `configs` (one GPU only)
+holds the remaining benchmark configurations.  `--no-extras` skips those extra measurements.
 
 `--impl reference` times the reference's own serial CPU implementation instead (compiled from
 its headers into oracle/_ref, else the plain-C port in oracle/).
 """
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -35,10 +40,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 V100_PUBLISHED_GEVALS = 84.4  # reference's best variant, N=2M d=32 k=1024, V100 (results/README.md:20)
-# dram__bytes_read.sum + dram__bytes_write.sum of one assign_tc_pair_kernel launch on workload c2: the ncu
-# capture summarised in profiles/assign_tc_pair_kernel_c2.md was taken on a quarter of the points
-# (138.88 MB + 4.71 MB); the traffic is the point operands, read once, so it scales with the points: x 4.
-C2_ASSIGN_TC_DRAM_BYTES = 574.9e6
+# DRAM bytes (read + write, from one profiler capture) that one assignment launch on workload c2
+# moves per point: the capture ran on 2^19 points (138.88 MB read + 4.71 MB written); the traffic is
+# the point operands, read once, so it grows in proportion to the points.
+C2_ASSIGN_TC_DRAM_BYTES_PER_POINT = (138.88e6 + 4.71e6) / (1 << 19)
+PARITY_SAMPLE = 4096
 
 
 def parse_args():
@@ -54,8 +60,12 @@ def parse_args():
     ap.add_argument("--update", default="auto", choices=["auto", "shared", "global", "rows", "sorted"])
     ap.add_argument("--no-fuse", action="store_true",
                     help="keep the update a launch of its own where the assignment kernel could accumulate the sums")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
+                    help="how the ranks exchange sums and sizes: NCCL all-reduce, or the library's peer-load kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the c5 strong-scaling run and the other configurations")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--seed", type=int, default=42)
     return ap.parse_args()
 
@@ -68,6 +78,30 @@ def measured_peaks():
         return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
                     bf16_tflops_sustained=p.get("bf16_tflops_sustained"), source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def measure_tf32_peak(torch, size=8192, reps=10):
+    """Dense TF32 matrix-multiply rate of this GPU right now (TFLOP/s): a library GEMM with TF32
+    allowed, best of `reps` - a measurement only, the denominator of the tensor roofline."""
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(size, size, device="cuda", dtype=torch.float32)
+        b = torch.randn(size, size, device="cuda", dtype=torch.float32)
+        for _ in range(3):
+            torch.matmul(a, b)
+        best = float("inf")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(reps):
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        del a, b
+        return 2.0 * size ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
 
 
 class ClockSampler(threading.Thread):
@@ -198,6 +232,215 @@ def cpu_reference_leg(workloads, spec, seed, sample_n, steps, warmup):
                        "serial by construction (1 thread)" % (sample_n, steps, dt)), dt
 
 
+class Job:
+    """One workload resident on this rank's GPU behind a k-means handle."""
+
+    def __init__(self, ctx, name, scaling, n_override=None, host_copy=False):
+        torch, pkg, workloads, args = ctx["torch"], ctx["pkg"], ctx["workloads"], ctx["args"]
+        world, rank = ctx["world"], ctx["rank"]
+        spec = dict(workloads.CONFIGS[name])
+        spec["layout_means"] = spec["layout"]
+        if n_override:
+            spec["n"] = n_override
+        self.spec, self.name, self.scaling = spec, name, scaling
+        k, dim, lay, laym = spec["k"], spec["dim"], spec["layout"], spec["layout_means"]
+        self.n_total = spec["n"] * world if scaling == "weak" else spec["n"]
+        self.begin, self.count = pkg.shard_range(self.n_total, world, rank)
+        self.host_points = None
+        if host_copy and self.count * dim * 4 <= (2 << 30):
+            rows = workloads.generate_rows(spec["kind"], self.n_total, dim, k, args.seed, spec.get("sigma", 0.05),
+                                           spec.get("zipf"), begin=self.begin, count=self.count)
+            first = rows[:k] if self.begin == 0 else workloads.generate_rows(
+                spec["kind"], self.n_total, dim, k, args.seed, spec.get("sigma", 0.05), spec.get("zipf"), begin=0, count=k)
+            self.host_points = torch.from_numpy(workloads.to_layout(rows, lay)).pin_memory()
+            del rows
+            self.dev_points = self.host_points.to("cuda", non_blocking=False)
+        else:
+            self.dev_points, first = device_rows(torch, workloads, spec, self.n_total, self.begin, self.count, args.seed)
+        self.host_means = torch.from_numpy(workloads.to_layout(first, laym)).pin_memory()
+        self.dev_means = self.host_means.to("cuda")
+        self.km = None
+
+    def handle(self, ctx, va=0, vu=0, device_init=True, fuse=True):
+        torch, pkg, args = ctx["torch"], ctx["pkg"], ctx["args"]
+        spec = self.spec
+        km = pkg.KMeans(layout=spec["layout"], layout_means=spec["layout_means"], device=ctx["local_rank"],
+                        variant_assign=va, variant_update=vu)
+        km.set_stream(ctx["stream"].cuda_stream)
+        if device_init:
+            km.initialize_device(spec["dim"], spec["k"], self.count, 1, self.dev_points.data_ptr(), self.dev_means.data_ptr())
+        else:
+            km.initialize(spec["dim"], spec["k"], self.count, 1, self.host_points.numpy(), self.host_means.numpy())
+        if not fuse:
+            km.set_option("fuse_update", 0)
+        if ctx["world"] > 1:
+            ctx["join"](km)
+        return km
+
+    def rows_sample(self, torch, idx):
+        """(len(idx), dim) numpy rows of this rank's shard."""
+        spec = self.spec
+        ti = torch.from_numpy(idx.astype(np.int64)).cuda()
+        view = self.dev_points.view(self.count, spec["dim"]) if spec["layout"] == 0 else self.dev_points.view(spec["dim"], self.count).t()
+        return view[ti].contiguous().cpu().numpy()
+
+
+def timed_run(ctx, km, steps, warmup, sample_clocks=True):
+    """`warmup` untimed iterations, then exactly `steps` timed with CUDA events on the launching
+    stream between two barriers; returns (ms per step maximised over ranks, clocks, phases, counters)."""
+    torch, dist, stream = ctx["torch"], ctx["dist"], ctx["stream"]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    km.run(warmup)
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(ctx["local_rank"])) if sample_clocks else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    km.run_async(steps)
+    e1.record(stream)
+    barrier()
+    km.synchronize()
+    clocks = sampler.stop() if sampler else None
+    ms_total = e0.elapsed_time(e1)
+    phases = km.phase_ms()
+    counters = km.counters()
+    by_rank = None
+    if dist is not None:
+        t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+        # per-rank phase times (each on its own device clock): the spread of the work before the
+        # exchange is rank skew, the smallest exchange time is what the exchange itself costs
+        names = ["assign", "recheck", "update", "allreduce", "finalize", "iteration"]
+        mine = torch.tensor([phases[x] for x in names], device="cuda", dtype=torch.float64)
+        allp = [torch.zeros_like(mine) for _ in range(ctx["world"])]
+        dist.all_gather(allp, mine)
+        allp = torch.stack(allp).cpu().numpy()
+        before = allp[:, 0] + allp[:, 1] + allp[:, 2]
+        by_rank = {"compute_before_exchange_min": float(before.min()), "compute_before_exchange_max": float(before.max()),
+                   "exchange_min": float(allp[:, 3].min()), "exchange_max": float(allp[:, 3].max()),
+                   "finalize_max": float(allp[:, 4].max()), "iteration_max": float(allp[:, 5].max())}
+    return ms_total / steps, clocks, phases, counters, by_rank
+
+
+def parity_check(ctx, job, km):
+    """One more iteration, outside any timed region, checked against the CPU oracle and across the
+    ranks: a sample of this rank's assignment bit for bit against serial.hpp's arg-min (restated in
+    oracle/) for the means the iteration started from, the sizes adding up to the number of points,
+    size-weighted means adding up to the sum of all points, and identical means on every rank."""
+    import oracle
+    torch, dist = ctx["torch"], ctx["dist"]
+    spec = job.spec
+    k, dim, lay, laym = spec["k"], spec["dim"], spec["layout"], spec["layout_means"]
+    prev = km.getMeans()
+    km.run(1)
+    means, sizes = km.getMeans(), km.getSizes()
+    rng = np.random.default_rng(1234 + ctx["rank"])
+    m = min(PARITY_SAMPLE if dim <= 64 else 1024, job.count)
+    idx = np.sort(rng.choice(job.count, m, replace=False))
+    rows = job.rows_sample(torch, idx)
+    got = km.getAssignment()[idx]
+    want = oracle.assign(ctx["workloads"].to_layout(rows, lay), prev, m, k, dim, lay, laym, threads=8)
+    mismatches = int((got != want).sum())
+    # conservation: sum_c size_c * mean_c == sum of all points, per dimension (double precision)
+    view = job.dev_points.view(job.count, dim) if lay == 0 else job.dev_points.view(dim, job.count).t()
+    total = view.sum(dim=0, dtype=torch.float64)
+    abs_total = torch.linalg.vector_norm(view, ord=1, dim=0, dtype=torch.float64)    # sum of |x| per dimension: the error scale
+    size_sum = int(sizes.astype(np.int64).sum())
+    digest = int.from_bytes(hashlib.sha256(means.tobytes()).digest()[:7], "little")
+    same_means = True
+    if dist is not None:
+        dist.all_reduce(total)
+        dist.all_reduce(abs_total)
+        d = torch.tensor([digest], device="cuda", dtype=torch.int64)
+        alld = [torch.zeros_like(d) for _ in range(ctx["world"])]
+        dist.all_gather(alld, d)
+        same_means = len({int(x.item()) for x in alld}) == 1
+        mm = torch.tensor([mismatches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(mm)
+        mismatches = int(mm.item())
+    mrows = ctx["workloads"].from_layout(means, k, dim, laym).astype(np.float64)
+    got_total = (mrows * sizes.astype(np.float64)[:, None]).sum(axis=0)
+    want_total = total.cpu().numpy()
+    scale = max(float(abs_total.max().item()), 1e-30)
+    cons_err = float(np.abs(got_total - want_total).max() / scale)
+    ok = mismatches == 0 and size_sum == job.n_total and same_means and cons_err <= 1e-5
+    return {"ok": bool(ok), "sampled_points_per_rank": int(m), "assignment_mismatches_vs_oracle": mismatches,
+            "sizes_sum": size_sum, "n_total": int(job.n_total), "means_identical_on_all_ranks": bool(same_means),
+            "conservation_rel_err": cons_err,
+            "what": "one extra iteration: sampled assignment == oracle arg-min for the previous means (bit-exact), "
+                    "sum of sizes == N_total, sum_c size_c*mean_c == sum of points (<= 1e-5), means hash equal on all ranks"}
+
+
+def roofline_of(ctx, job, phases, counters, plan, ms_step, tf32_peak):
+    peaks = ctx["peaks"]
+    spec = job.spec
+    k, dim = spec["k"], spec["dim"]
+    flops_iter = 2.0 * job.count * k * dim            # algorithmic flops of one assignment launch on this rank
+    bytes_iter = 4.0 * job.count * dim
+    assign_ms = phases["assign"]
+    roofline = None
+    if assign_ms > 0:
+        if counters["assign_variant"] == "tc":
+            ach = flops_iter / (assign_ms * 1e-3) / 1e12
+            traffic = C2_ASSIGN_TC_DRAM_BYTES_PER_POINT * job.count if (job.name == "c2" and plan["kernel"] == "tc_pair") else None
+            ksteps = (min(dim, 32) + 7) // 8 if dim <= 32 else None
+            issued = (3.0 * ksteps + 1.0) / ksteps if ksteps else 3.0 + 8.0 / dim
+            roofline = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
+                        "peak_tf32_measured": tf32_peak,
+                        "frac_tensor_issued": issued * ach / tf32_peak,
+                        "tensor_flops_per_algorithmic_flop": issued,
+                        "frac_vs_half_bf16_burst": ach / (peaks["bf16_tflops"] * 0.5),
+                        "traffic": traffic,
+                        "traffic_unit": "bytes per launch (profiler DRAM read+write per point of a 2^19-point capture x points of this launch)",
+                        "kernel": "assignment (%s)" % plan["kernel"], "kernel_ms": assign_ms,
+                        "peak_note": "peak = TF32 library GEMM (8192^3, best of 10) measured in this run; `frac` counts "
+                                     "algorithmic flops 2*N*k*d; the split-TF32 scheme issues `tensor_flops_per_algorithmic_flop` "
+                                     "tensor flops for each, `frac_tensor_issued` is that work against the same peak; half the %s "
+                                     "bf16 burst peak is %.1f TFLOP/s" % (peaks["source"], peaks["bf16_tflops"] * 0.5)}
+        else:
+            ach = bytes_iter / (assign_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                        "kernel": "assignment (%s)" % plan["kernel"], "kernel_ms": assign_ms,
+                        "peak_note": "%s HBM copy bandwidth; algorithmic bytes 4*N*d" % peaks["source"]}
+    # the contractual whole-iteration roofline: slower of 2Nkd flops at the TF32 rate and 4Nd bytes at HBM bandwidth
+    t_roof = max(flops_iter / (tf32_peak * 1e12), bytes_iter / (peaks["hbm_gbs"] * 1e9))
+    iteration_roofline = {"roofline_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_step,
+                          "peaks": "tf32 = %.1f TFLOP/s (measured in this run), hbm = %.1f GB/s (%s)" % (
+                              tf32_peak, peaks["hbm_gbs"], peaks["source"])}
+    return roofline, iteration_roofline
+
+
+def extra_config(ctx, name, scaling, steps, warmup, tf32_peak):
+    """One more configuration measured after the headline one (device-generated data)."""
+    torch = ctx["torch"]
+    job = Job(ctx, name, scaling)
+    km = job.handle(ctx)
+    ms_step, clocks, phases, counters, by_rank = timed_run(ctx, km, steps, warmup, sample_clocks=True)
+    plan = km.assign_plan()
+    roofline, iteration_roofline = roofline_of(ctx, job, phases, counters, plan, ms_step, tf32_peak)
+    parity = None if ctx["args"].no_parity else parity_check(ctx, job, km)
+    spec = job.spec
+    out = {"workload": "%s: N_total=%d (%d on this rank) x dim %d, k=%d, fp32, %s points, %s" % (
+        name, job.n_total, job.count, spec["dim"], spec["k"], "SoA" if spec["layout"] == 1 else "AoS", spec["kind"]),
+        "scaling": scaling, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+        "value": job.n_total * spec["k"] / (ms_step * 1e-3) / 1e9, "unit": "G dist-evals/s",
+        "phases_ms": phases, "phases_ms_across_ranks": by_rank, "variants": counters, "plan": plan, "clocks": clocks,
+        "roofline": roofline, "iteration_roofline": iteration_roofline, "parity": parity,
+        "gpu_launches": counters["launches_per_iter"] * steps}
+    km.cleanup()
+    del job, km
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     args = parse_args()
     import __graft_entry__ as entry
@@ -214,8 +457,10 @@ def main():
         spec["n"] = args.n
     k, dim, lay, laym = spec["k"], spec["dim"], spec["layout"], spec["layout_means"]
     scaling = args.scaling or ("strong" if args.workload == "c5" else "weak")
-    config = {"workload": "%s: N=%d x dim %d, k=%d, fp32, %s points" % (
-        args.workload, spec["n"], dim, k, "SoA" if lay == 1 else "AoS"),
+    n_total_cfg = spec["n"] * args.gpus if scaling == "weak" else spec["n"]
+    per_gpu = " per GPU, N_total=%d" % n_total_cfg if scaling == "weak" else " in total, sharded over the GPUs"
+    config = {"workload": "%s: N=%d%s x dim %d, k=%d, fp32, %s points" % (
+        args.workload, spec["n"], per_gpu, dim, k, "SoA" if lay == 1 else "AoS"),
         "distribution": spec["kind"], "init": "first k points", "l2": "inputs exceed L2 (no flush needed)"
         if spec["n"] * dim * 4 > 126e6 else "inputs fit L2: working set is re-read from L2 between steps"}
 
@@ -249,82 +494,57 @@ def main():
         import torch.distributed as dist
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
 
-    n_total = spec["n"] * world if scaling == "weak" else spec["n"]
-    begin, count = pkg.shard_range(n_total, world, rank)
-    big = count * dim * 4 > (2 << 30)          # beyond 2 GiB the shard is generated on the device
-    if big:
-        dev_points, first = device_rows(torch, workloads, spec, n_total, begin, count, args.seed)
-        host_points = None
-        args.no_e2e = True                        # no host copy of a shard this large is kept
-    else:
-        rows = workloads.generate_rows(spec["kind"], n_total, dim, k, args.seed, spec.get("sigma", 0.05),
-                                       spec.get("zipf"), begin=begin, count=count)
-        first = rows[:k] if begin == 0 else workloads.generate_rows(
-            spec["kind"], n_total, dim, k, args.seed, spec.get("sigma", 0.05), spec.get("zipf"), begin=0, count=k)
-        host_points = torch.from_numpy(workloads.to_layout(rows, lay)).pin_memory()
-        del rows
-        dev_points = host_points.to("cuda", non_blocking=False)
-    host_means = torch.from_numpy(workloads.to_layout(first, laym)).pin_memory()
-    dev_means = host_means.to("cuda")
-
-    va = {"auto": 0, "exact": 1, "simt": 2, "tc": 3}[args.assign]
-    vu = {"auto": 0, "shared": 1, "global": 2, "rows": 3, "sorted": 5}[args.update]
-    km = pkg.KMeans(layout=lay, layout_means=laym, device=local_rank, variant_assign=va, variant_update=vu)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
-    km.set_stream(stream.cuda_stream)
-    km.initialize_device(dim, k, count, args.steps, dev_points.data_ptr(), dev_means.data_ptr())
-    if args.no_fuse:
-        km.set_option("fuse_update", 0)
-    if world > 1:
+    exchange_used = {"mode": "none"}
+
+    def join(km):
+        """Makes `km` one rank of the job: NCCL communicator through the launcher's process group, then
+        (unless --exchange nccl) the peer-memory exchange."""
         uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
             uid.copy_(torch.frombuffer(bytearray(pkg.comm_unique_id()), dtype=torch.uint8))
         dist.broadcast(uid, 0)
         km.comm_init(bytes(uid.cpu().numpy().tobytes()), world, rank)
+        exchange_used["mode"] = "nccl"
+        if args.exchange != "nccl" and hasattr(km, "peer_exchange_init"):
+            if km.peer_exchange_init(dist, torch):
+                exchange_used["mode"] = "peer"
+            elif args.exchange == "peer":
+                raise SystemExit("--exchange peer: the peer-memory exchange could not be set up")
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    ctx = dict(torch=torch, pkg=pkg, workloads=workloads, args=args, world=world, rank=rank, local_rank=local_rank,
+               dist=dist, stream=stream, join=join, peaks=measured_peaks())
 
-    km.run(args.warmup)
-    barrier()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    km.run_async(args.steps)
-    e1.record(stream)
-    barrier()
-    km.synchronize()
-    clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    phases = km.phase_ms()
-    counters = km.counters()
+    tf32_peak = measure_tf32_peak(torch)
     if dist is not None:
-        t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+        t = torch.tensor([tf32_peak], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        tf32_peak = float(t.item())
+
+    va = {"auto": 0, "exact": 1, "simt": 2, "tc": 3}[args.assign]
+    vu = {"auto": 0, "shared": 1, "global": 2, "rows": 3, "sorted": 5}[args.update]
+    job = Job(ctx, args.workload, scaling, n_override=args.n, host_copy=True)
+    n_total, count = job.n_total, job.count
+    km = job.handle(ctx, va, vu, fuse=not args.no_fuse)
+    ms_step, clocks, phases, counters, by_rank = timed_run(ctx, km, args.steps, args.warmup)
     value = n_total * k / (ms_step * 1e-3) / 1e9
+    plan = km.assign_plan()
+    parity = None if args.no_parity else parity_check(ctx, job, km)
 
     # ---------------- end to end through the host-buffer calls ----------------
     e2e = None
-    if not args.no_e2e and host_points is not None:
+    if not args.no_e2e and job.host_points is not None:
         e2e_steps = max(3, min(args.steps, 20))
-        km2 = pkg.KMeans(layout=lay, layout_means=laym, device=local_rank, variant_assign=va, variant_update=vu)
-        km2.set_stream(stream.cuda_stream)
-        hp, hm = host_points.numpy(), host_means.numpy()   # (host_points exists: large shards skip this leg)
+        km2 = job.handle(ctx, va, vu, device_init=False, fuse=not args.no_fuse)
+        hp, hm = job.host_points.numpy(), job.host_means.numpy()
         out_means = torch.empty(k * dim, dtype=torch.float32).pin_memory()
         out_asg = torch.empty(count, dtype=torch.int32).pin_memory()
-        km2.initialize(dim, k, count, 1, hp, hm)
-        if world > 1:
-            uid2 = torch.zeros(128, dtype=torch.uint8, device="cuda")
-            if rank == 0:
-                uid2.copy_(torch.frombuffer(bytearray(pkg.comm_unique_id()), dtype=torch.uint8))
-            dist.broadcast(uid2, 0)
-            km2.comm_init(bytes(uid2.cpu().numpy().tobytes()), world, rank)
+
+        def barrier():
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
 
         def e2e_step():
             # host -> device copy of points and means, preprocessing, one iteration, results back
@@ -336,6 +556,7 @@ def main():
         for _ in range(3):
             e2e_step()
         barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record(stream)
         for _ in range(e2e_steps):
@@ -356,39 +577,25 @@ def main():
                "call": "bkm_initialize(host) + bkm_run(1) + bkm_get_means + bkm_get_assignment, pinned host buffers"}
         km2.cleanup()
 
-    # ---------------- roofline of the dominant kernel (assignment) ----------------
-    peaks = measured_peaks()
-    flops_iter = 2.0 * count * k * dim            # algorithmic flops of one assignment launch on this rank
-    bytes_iter = 4.0 * count * dim
-    assign_ms = phases["assign"]
-    roofline = None
-    if assign_ms > 0:
-        if counters["assign_variant"] == "tc" or flops_iter / (peaks["bf16_tflops"] * 0.5e12) > bytes_iter / (peaks["hbm_gbs"] * 1e9):
-            tf32_peak = peaks["bf16_tflops"] * 0.5
-            ach = flops_iter / (assign_ms * 1e-3) / 1e12
-            traffic = C2_ASSIGN_TC_DRAM_BYTES if (args.workload == "c2" and not args.n and counters["assign_variant"] == "tc") else None
-            roofline = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
-                        "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from a quarter-size capture)",
-                        "kernel": "assignment (%s)" % counters["assign_variant"],
-                        "kernel_ms": assign_ms,
-                        "peak_note": "TF32 dense taken as half the %s bf16 burst peak; 3xTF32 issues 3 tensor "
-                                     "flops per algorithmic flop, so 1/3 is the ceiling of this fraction" % peaks["source"]}
-        else:
-            ach = bytes_iter / (assign_ms * 1e-3) / 1e9
-            roofline = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": ach / peaks["hbm_gbs"], "traffic": None,
-                        "kernel": "assignment (%s)" % counters["assign_variant"], "kernel_ms": assign_ms,
-                        "peak_note": "%s HBM copy bandwidth" % peaks["source"]}
-    # the contractual whole-iteration roofline: slower of 2Nkd flops at peak and 4Nd bytes at HBM bandwidth
-    t_roof = max(2.0 * count * k * dim / (peaks["bf16_tflops"] * 0.5e12), 4.0 * count * dim / (peaks["hbm_gbs"] * 1e9))
-    iteration_roofline = {"roofline_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_step,
-                          "peaks": "tf32 = bf16/2 = %.1f TFLOP/s, hbm = %.1f GB/s (%s)" % (
-                              peaks["bf16_tflops"] * 0.5, peaks["hbm_gbs"], peaks["source"])}
+    roofline, iteration_roofline = roofline_of(ctx, job, phases, counters, plan, ms_step, tf32_peak)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_n = min(spec["n"], max(1 << 12, (1 << 26) // (k * max(1, dim // 32 + (dim % 32 > 0)))))
         cpu_baseline, _ = cpu_reference_leg(workloads, spec, args.seed, sample_n, 1, 0)
+
+    km.cleanup()
+    del km, job
+    torch.cuda.empty_cache()
+
+    # ---------------- the other configurations (outside the headline measurement) ----------------
+    c5_strong, configs = None, None
+    if not args.no_extras and args.workload == "c2" and not args.n:
+        c5_strong = extra_config(ctx, "c5", "strong", 10, 3, tf32_peak)
+        if world == 1:
+            configs = {"c1": extra_config(ctx, "c1", "strong", 200, 20, tf32_peak),
+                       "c3": extra_config(ctx, "c3", "strong", 50, 5, tf32_peak),
+                       "c4": extra_config(ctx, "c4", "strong", 10, 3, tf32_peak)}
 
     if rank == 0:
         line = {"metric": "k-means iteration throughput", "value": value, "unit": "G dist-evals/s",
@@ -399,10 +606,11 @@ def main():
                 "dtype": "f32", "data": "synthetic", "config": config, "e2e": e2e,
                 "gpu_launches": counters["launches_per_iter"] * args.steps,
                 "roofline": roofline, "iteration_roofline": iteration_roofline, "cpu_baseline": cpu_baseline,
-                "clocks": clocks, "phases_ms": phases, "variants": counters,
-                "ns_per_input_float": ms_step * 1e6 / (n_total * dim)}
+                "clocks": clocks, "phases_ms": phases, "phases_ms_across_ranks": by_rank, "variants": counters, "plan": plan,
+                "exchange": exchange_used["mode"], "parity": parity,
+                "ns_per_input_float": ms_step * 1e6 / (n_total * dim),
+                "c5_strong": c5_strong, "configs": configs}
         print(json.dumps(line))
-    km.cleanup()
     if dist is not None:
         dist.destroy_process_group()
     return 0

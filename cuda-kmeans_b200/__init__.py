@@ -22,6 +22,7 @@ LAYOUT_AOS, LAYOUT_SOA = 0, 1
 ASSIGN_AUTO, ASSIGN_EXACT, ASSIGN_SIMT, ASSIGN_TC = 0, 1, 2, 3
 UPDATE_AUTO, UPDATE_SHARED, UPDATE_GLOBAL, UPDATE_ROWS = 0, 1, 2, 3
 ASSIGN_NAMES = {ASSIGN_AUTO: "auto", ASSIGN_EXACT: "exact", ASSIGN_SIMT: "simt", ASSIGN_TC: "tc"}
+PLAN_NAMES = {0: "exact", 1: "simt", 2: "tc_resident", 3: "tc_kloop", 4: "tc_pair"}
 UPDATE_FUSED = 4   # reported by counters() only
 UPDATE_SORTED = 5
 UPDATE_NAMES = {UPDATE_AUTO: "auto", UPDATE_SHARED: "shared", UPDATE_GLOBAL: "global", UPDATE_ROWS: "rows",
@@ -35,7 +36,8 @@ SYMBOLS = [
     "bkm_run_async", "bkm_synchronize", "bkm_get_means", "bkm_get_assignment", "bkm_get_sizes",
     "bkm_device_means", "bkm_device_assignment", "bkm_set_means", "bkm_iterations_done",
     "bkm_phase_ms", "bkm_counters", "bkm_comm_unique_id", "bkm_comm_init", "bkm_shard_range",
-    "bkm_kmeans_host_f32", "bkm_update_noalloc_f32", "bkm_selftest_wait_timeout",
+    "bkm_kmeans_host_f32", "bkm_update_noalloc_f32", "bkm_selftest_wait_timeout", "bkm_assign_plan",
+    "bkm_noalloc_check",
 ]
 
 
@@ -102,6 +104,8 @@ def lib():
     L.bkm_kmeans_host_f32.argtypes = [vp, vp, vp, u64, u32, u32, u32, ci, ci, ci]
     L.bkm_update_noalloc_f32.argtypes = [vp, vp, vp, vp, u64, u32, u32, ci, ci, vp]
     L.bkm_selftest_wait_timeout.argtypes = [vp, u32, vp]
+    L.bkm_assign_plan.argtypes = [vp, ctypes.POINTER(u32)]
+    L.bkm_noalloc_check.argtypes = [vp]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("bkm_last_error", "bkm_workspace_bytes"):
@@ -175,6 +179,12 @@ def update_noalloc(points, assignment, means, sizes, n, k, dim, layout, layout_m
     """bkm_update_noalloc_f32: the update step on the library's built-in scratch (no workspace, no
     allocation); k*dim + k is limited to NOALLOC_MAX_WORDS and calls on one device must not overlap."""
     check(lib().bkm_update_noalloc_f32(points, assignment, means, sizes, n, k, dim, layout, layout_means, stream))
+
+
+def noalloc_check(stream=0):
+    """bkm_noalloc_check: raises BkmError(ERR_DEVICE) if the last update_noalloc call on the current
+    device saw an assignment value >= k."""
+    check(lib().bkm_noalloc_check(stream))
 
 
 NOALLOC_MAX_WORDS = 512 * 1024 - 128
@@ -328,6 +338,13 @@ class KMeans:
         return {"rechecked": int(arr[0]), "launches_per_iter": int(arr[1]),
                 "assign_variant": ASSIGN_NAMES.get(int(arr[2]), "?"),
                 "update_variant": UPDATE_NAMES.get(int(arr[3]), "?")}
+
+    def assign_plan(self):
+        """dict describing the assignment kernel the handle launches (bkm_assign_plan)."""
+        arr = (ctypes.c_uint32 * 4)()
+        check(lib().bkm_assign_plan(self._need(), arr))
+        return {"kernel": PLAN_NAMES.get(int(arr[0]), "?"), "mean_tiles": int(arr[1]), "block_split": int(arr[2]),
+                "fused_update": bool(arr[3])}
 
     def _create(self, dim, k, n, iters):
         self.cleanup()

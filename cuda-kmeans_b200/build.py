@@ -45,8 +45,7 @@ def build(force=False, verbose=False):
     procs = []
     for src in _sources():
         obj = src[:-3] + ".o"
-        extra = os.environ.get("BKM_EXTRA_NVCC_FLAGS", "").split()      # e.g. -DBKM_TC_TIMING for a development build
-        cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
     failed = False

@@ -697,6 +697,9 @@ static bool graph_wanted(bkm_handle_t h, uint32_t iters)
 {
 	if (h->comm || iters < 4) return false;
 	if (h->use_graph == 0) return false;
+	// the legacy default stream (what bkm_set_stream(h, NULL) selects) and the per-thread default
+	// stream cannot be captured: plain launches there
+	if (h->stream == nullptr || h->stream == cudaStreamLegacy || h->stream == cudaStreamPerThread) return false;
 	if (h->use_graph == 1) return true;
 	return (double)h->shape.n * h->shape.k * h->shape.dim <= 1.0e8;     // auto: launch-bound sizes only
 }
@@ -848,6 +851,20 @@ int bkm_counters(bkm_handle_t h, uint64_t out[4])
 	out[1] = h->launches_per_iter;
 	out[2] = (uint64_t)h->assign_variant;
 	out[3] = h->last_fused ? (uint64_t)BKM_UPDATE_FUSED : (uint64_t)h->update_variant;
+	return BKM_OK;
+}
+
+int bkm_assign_plan(bkm_handle_t h, uint32_t out[4])
+{
+	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	out[0] = out[1] = out[2] = out[3] = 0;
+	if (h->assign_variant == BKM_ASSIGN_EXACT) out[0] = BKM_PLAN_EXACT;
+	else if (h->assign_variant == BKM_ASSIGN_SIMT) out[0] = BKM_PLAN_SIMT;
+	else {
+		if (!h->plan) return fail(BKM_ERR_STATE, "the tensor-core plan exists after initialize only");
+		bkm::tc_plan_describe(h->plan, out);
+	}
+	out[3] = h->last_fused ? 1u : 0u;
 	return BKM_OK;
 }
 

@@ -35,6 +35,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include "../../include/bkm.h"
 #include "kernels.cuh"
 #include "ptx.cuh"
 #include "tc_common.cuh"
@@ -173,7 +174,7 @@ cudaError_t launch_compute_center(const float* pts, const Shape& s, float* cente
 cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream)
 {
 	const uint64_t groups = tp.n_pad / 32;
-	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148 * 16);
+	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, (uint64_t)current_sm_count() * 16);
 	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl);
 	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl);
 	return cudaGetLastError();
@@ -482,40 +483,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					}
 				}
 			} else {
-#ifdef BKM_TC_TIMING
-				long long t_b = 0, t_a = 0, t_acc = 0, t_issue = 0;
-				const long long t_start = clock64();
-#endif
 				uint32_t g = 0;                       // position of the block's first tile in the A ring
 				bool b_ready = false;
 				for (uint32_t blk = bid; blk < nblocks && ok; blk += nbid) {
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						const uint32_t s = b_resident ? 0u : b_count % TC_NB, u = b_count / TC_NB;
-						TC_T(c0);
 						if (!(b_resident && b_ready)) {
 							ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
 							if (!ok) break;
 							b_ready = true;
 						}
-						TC_T(c1);
-						TC_ACC(t_b, c0, c1);
 						const uint32_t b_addr = ptx::smem_u32(smem + sm_b_off + s * b_stage);
 						const uint32_t b_hi = desc_lo_sw128(b_addr), b_lo = desc_lo_sw128(b_addr + b_plane);
 						const uint32_t b_aug_lo = desc_lo_aug(ptx::smem_u32(smem + sm_baug_off + s * AUG_BYTES));
 						for (uint32_t i = 0; i < tiles; ++i) {
 							const uint32_t buf = (g + i) % n_abuf, ua = (g + i) / n_abuf;
-							TC_T(c2);
 							if (j == j_begin) {
 								ok = wait_or_abort(&bars->a_full[buf], ua & 1u, abort_flag);
 								if (!ok) break;
 							}
-							TC_T(c3);
 							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
 							if (!ok) break;
-							TC_T(c4);
-							TC_ACC(t_a, c2, c3);
-							TC_ACC(t_acc, c3, c4);
 							ptx::tc_fence_after();
 							const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + buf * a_tile);
 							const uint32_t a_hi = desc_lo_sw128(a_addr), a_lo = desc_lo_sw128(a_addr + a_plane);
@@ -532,8 +521,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 								if (j == j_end - 1) ptx::mma_commit(&bars->a_empty[buf]);
 							}
 							__syncwarp();
-							TC_T(c5);
-							TC_ACC(t_issue, c4, c5);
 							++acc_use[i];
 						}
 						if (!ok) break;
@@ -545,11 +532,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					}
 					g += tiles;
 				}
-#ifdef BKM_TC_TIMING
-				if (blockIdx.x == 3 && lane == 0)
-					printf("mma warp: total %lld  wait_b %lld  wait_a %lld  wait_acc %lld  issue %lld  (tiles %u)\n",
-						clock64() - t_start, t_b, t_a, t_acc, t_issue, g);
-#endif
 			}
 		}
 	} else {
@@ -574,10 +556,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		const uint32_t bar_id = 1u + i * 4u + q;   // named barrier of the two warps that share these rows
 		uint32_t acc_use = 0, blk_count = 0;
 		bool ok = true;
-#ifdef BKM_TC_TIMING
-		long long e_wait = 0, e_ld = 0, e_cmp = 0, e_merge = 0;
-		const long long e_start = clock64();
-#endif
 		for (uint32_t blk = bid; blk < nblocks; blk += nbid, ++blk_count) {
 			const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 			if (i >= tiles) continue;              // odd tail: this accumulator is not used in the last block
@@ -586,7 +564,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			float xn = 0.0f;                       // |x|^2 of this thread's point, needed at the end of the block
 			#pragma unroll 1
 			for (uint32_t j = j_begin; j < j_end; ++j) {
-				TC_T(e0);
 				if (ok) {
 					// one lane polls the barrier, the warp follows
 					bool w = true;
@@ -594,8 +571,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
 				}
 				++acc_use;
-				TC_T(e1);
-				TC_ACC(e_wait, e0, e1);
 				if (ok && nchunks > 0) {
 					ptx::tc_fence_after();
 					#pragma unroll 1
@@ -604,7 +579,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
 						const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
 						const bool two = c + 1 < nchunks;
-						TC_T(e2);
 						uint32_t v0[32], v1[32];
 						ptx::tmem_ld32(taddr, v0);
 						if (two) ptx::tmem_ld32(taddr + 32, v1);
@@ -618,8 +592,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							// the chunks just loaded covers the latency
 							if (j == j_end - 1 && half == 0 && p < n) xn = xnorm[p];
 						}
-						TC_T(e3);
-						TC_ACC(e_ld, e2, e3);
 						// columns at or behind k are padding
 						const uint32_t col0 = chunk0 * 32u;
 						const uint32_t left = k > col0 ? k - col0 : 0u;
@@ -630,8 +602,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							if (left > 0) chunk_update<true>(v0, key_mult, chunk0, left, best, second, bchunk);
 							if (two && left > 32) chunk_update<true>(v1, key_mult, chunk0 + 1, left - 32, best, second, bchunk);
 						}
-						TC_T(e4);
-						TC_ACC(e_cmp, e3, e4);
 					}
 				} else {
 					__syncwarp();
@@ -641,7 +611,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			// The upper column half hands its state to the lower one through shared memory.  The slots
 			// alternate with the block count, so one barrier per block is enough: a slot is written
 			// again only after its reader has passed the barrier of the block in between.
-			TC_T(e5);
 			uint32_t* mg = mg_state + ((blk_count & 1u) * TC_MA + i) * (3 * TC_MTILE);
 			if (half == 1) {
 				mg[row] = best; mg[TC_MTILE + row] = second; mg[2 * TC_MTILE + row] = bchunk;
@@ -661,13 +630,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						p, n, asg, ctl, flag_list);
 				}
 			}
-			TC_T(e6);
-			TC_ACC(e_merge, e5, e6);
 		}
-#ifdef BKM_TC_TIMING
-		if (blockIdx.x == 3 && lane == 0 && (warp == 2 || warp == 7 || warp == 17))
-			printf("epi warp %u: total %lld  wait %lld  ld %lld  compute %lld  merge %lld\n", warp, clock64() - e_start, e_wait, e_ld, e_cmp, e_merge);
-#endif
 	}
 
 	ptx::tc_fence_before();
@@ -765,7 +728,7 @@ TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, in
 	p->nt_cols = tc_nt_cols(s.k);
 	// c_format = f32 (bit 4), a/b format = tf32 (bits 7.., 10..), K-major both, N>>3 at bit 17, M>>4 at bit 24
 	p->idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p->nt_cols >> 3) << 17) | ((TC_MTILE >> 4) << 24);
-	if (cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) p->sm_count = 148;
+	if (cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || p->sm_count < 1) { cudaGetLastError(); if (err) *err = e_attr; delete p; return nullptr; }
 	if (!encode_plane(&p->a_hi, tp.a_hi, tp.n_pad, tp.d_pad, TC_MTILE) ||
 		!encode_plane(&p->a_lo, tp.a_lo, tp.n_pad, tp.d_pad, TC_MTILE) ||
 		!encode_plane(&p->b_hi, tm.b_hi, tm.k_pad, tm.d_pad, p->nt_cols) ||
@@ -785,11 +748,10 @@ TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, in
 		encode_plane(&p->bh_hi, tm.b_hi, tm.k_pad, tm.d_pad, TC_NT_MAX / 2) &&
 		encode_plane(&p->bh_lo, tm.b_lo, tm.k_pad, tm.d_pad, TC_NT_MAX / 2);
 	p->max_pairs = 0;
-	if (p->pair_ok && (assign_tc_pair_prepare(&p->max_pairs) != cudaSuccess || p->max_pairs < 1)) {
+	if (p->pair_ok && (assign_tc_pair_prepare(p->sm_count, &p->max_pairs) != cudaSuccess || p->max_pairs < 1)) {
 		cudaGetLastError();
 		p->pair_ok = false;
 	}
-	if (getenv("BKM_DEBUG_PLAN")) fprintf(stderr, "bkm: tensor-core plan: pair kernel %s, %d co-resident pairs on %d SMs\n", p->pair_ok ? "on" : "off", p->max_pairs, p->sm_count);
 	return p;
 }
 
@@ -804,6 +766,23 @@ bool tc_plan_can_fuse(const TcPlan* p, const FusedAcc& f)
 {
 	return tc_plan_uses_pair(p) && p->s.dim % 4 == 0 && f.acc != nullptr && f.counts != nullptr && f.center != nullptr &&
 		(reinterpret_cast<uintptr_t>(f.acc) & 15u) == 0 && (f.rep_stride * sizeof(float)) % 16 == 0;
+}
+
+// K loop with several mean tiles: pairs of neighbouring CTAs share a point block (see the kernel)
+static uint32_t plan_jsplit(const TcPlan* p)
+{
+	const bool kloop = p->tp.d_pad > TC_KCHUNK;
+	const uint32_t n_ctiles = p->tm.k_pad / p->nt_cols;
+	return (kloop && n_ctiles >= 2 * TC_JSPLIT && p->tp.partial != nullptr && p->sm_count >= (int)TC_JSPLIT) ? TC_JSPLIT : 1u;
+}
+
+void tc_plan_describe(const TcPlan* p, uint32_t out[4])
+{
+	out[1] = p->tm.k_pad / p->nt_cols;
+	out[2] = 1;
+	if (tc_plan_uses_pair(p)) { out[0] = BKM_PLAN_TC_PAIR; return; }
+	out[0] = p->tp.d_pad > TC_KCHUNK ? BKM_PLAN_TC_KLOOP : BKM_PLAN_TC_RESIDENT;
+	out[2] = plan_jsplit(p);
 }
 
 cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
@@ -826,9 +805,7 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	if (tc_plan_uses_pair(p))
 		return launch_assign_tc_pair(p->a_hi, p->a_lo, p->bh_hi, p->bh_lo, p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles,
 			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim);
-	// K loop with several mean tiles: pairs of neighbouring CTAs share a point block (see the kernel)
-	const uint32_t n_ctiles = p->tm.k_pad / p->nt_cols;
-	const uint32_t jsplit = (kloop && n_ctiles >= 2 * TC_JSPLIT && p->tp.partial != nullptr && p->sm_count >= (int)TC_JSPLIT) ? TC_JSPLIT : 1u;
+	const uint32_t jsplit = plan_jsplit(p);
 	const uint32_t grid_j = jsplit * std::min<uint32_t>(nblocks, (uint32_t)p->sm_count / jsplit);
 	assign_tc_kernel<<<jsplit > 1 ? grid_j : grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
 		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,

@@ -211,30 +211,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			const uint32_t a_empty_peer_base = ptx::map_to_cta(ptx::smem_u32(&bars->a_empty[0]), peer);
 			const uint32_t acc_full_own = ptx::smem_u32(&bars->acc_full[0]);
 			const uint32_t acc_full_peer = ptx::map_to_cta(acc_full_own, peer);
-#ifdef BKM_TC_TIMING
-			long long t_a = 0, t_acc = 0, t_issue = 0;
-			const long long t_start = clock64();
-#endif
 			bool ok = pair_wait(&bars->b_full, 0, abort_flag, peer_abort_addr);
-			TC_T(tb);
 			uint32_t it = 0, c = 0;                 // c counts units: accumulator c % 4, use c / 4
 			for (uint32_t step = pair; step < steps_total && ok; step += n_pairs, ++it) {
 				const uint32_t buf = it % n_abuf, ua = it / n_abuf;
-				TC_T(c0);
 				ok = pair_wait(&bars->a_full[buf], ua & 1u, abort_flag, peer_abort_addr);
 				if (!ok) break;
-				TC_T(c1);
-				TC_ACC(t_a, c0, c1);
 				// descriptor halves (see desc_lo_sw128): +2 in the address field = 32 bytes = one K step
 				const uint32_t a_addr = ptx::smem_u32(smem + a_off + buf * a_tile);
 				const uint32_t a_hi = desc_lo_sw128(a_addr), a_lo = desc_lo_sw128(a_addr + a_plane);
 				for (uint32_t u = 0; u < n_units; ++u, ++c) {
 					const uint32_t acc = c % P2_ACCS;
-					TC_T(c2);
 					ok = pair_wait<200>(&bars->acc_empty[acc], ((c / P2_ACCS) & 1u) ^ 1u, abort_flag, peer_abort_addr);
 					if (!ok) break;
-					TC_T(c3);
-					TC_ACC(t_acc, c2, c3);
 					ptx::tc_fence_after();
 					// rows [h*64, h*64+64) of this CTA's (and, at the same offset, the other CTA's) half of tile j
 					const uint32_t j = u >> 1, h = u & 1u;
@@ -263,15 +252,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 						}
 					}
 					__syncwarp();
-					TC_T(c4);
-					TC_ACC(t_issue, c3, c4);
 				}
 			}
-#ifdef BKM_TC_TIMING
-			if (blockIdx.x == 6 && lane == 0)
-				printf("pair mma warp: total %lld  wait_b %lld  wait_a %lld  wait_acc %lld  issue %lld  (units %u)\n",
-					clock64() - t_start, tb - t_start, t_a, t_acc, t_issue, c);
-#endif
 		}
 	} else {
 		// ---------------- epilogue (both CTAs, own accumulator rows) ----------------
@@ -321,10 +303,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			if (lane == 0) ptx::mbar_arrive(&bars->a_empty[pend_it % n_abuf]);
 			pending = false;
 		};
-#ifdef BKM_TC_TIMING
-		long long e_wait = 0, e_work = 0, e_merge = 0;
-		const long long e_start = clock64();
-#endif
 		for (uint32_t step = pair; step < steps_total; step += n_pairs, ++it) {
 			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
 			const uint64_t p = (uint64_t)(2 * step + rank) * TC_MTILE + row;
@@ -339,14 +317,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				const uint32_t c = c_step + u;
 				const uint32_t acc = c % P2_ACCS;
 				const uint32_t acc_release = acc_empty_base + acc * 8u;
-				TC_T(e0);
 				if (ok) {
 					bool w = true;
 					if (lane == 0) w = pair_wait(&bars->acc_full[acc], (c / P2_ACCS) & 1u, abort_flag, peer_abort_addr);
 					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
 				}
-				TC_T(e1);
-				TC_ACC(e_wait, e0, e1);
 				if (ok) {
 					ptx::tc_fence_after();
 					const uint32_t j = u >> 1, h = u & 1u;
@@ -367,11 +342,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 					if (lane == 0) ptx::mbar_arrive_cluster(acc_release);
 				}
 				if (pending) flush_sums();
-				TC_T(e2);
-				TC_ACC(e_work, e1, e2);
 			}
 			if (pending) flush_sums();                    // a step without an accumulator for this warp
-			TC_T(e3);
 			// Three warps of a quarter hand their state to the fourth through shared memory and go on
 			// without waiting (bar.arrive); the fourth waits for them (bar.sync), merges and writes the
 			// results.  Slots and barrier numbers alternate with the step count.  No warp can be a whole
@@ -421,14 +393,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				pending = true;
 				pend_it = it;
 			}
-			TC_T(e4);
-			TC_ACC(e_merge, e3, e4);
 		}
 		if (pending) flush_sums();
-#ifdef BKM_TC_TIMING
-		if ((blockIdx.x == 6 || blockIdx.x == 7) && lane == 0 && (warp == 2 || warp == 7 || warp == 12 || warp == 17))
-			printf("pair epi cta %u warp %u: total %lld  wait %lld  work %lld  merge %lld\n", blockIdx.x, warp, clock64() - e_start, e_wait, e_work, e_merge);
-#endif
 	}
 
 	// Both CTAs stay until neither can touch the other's shared memory or barriers any more.
@@ -446,14 +412,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 // persistent: launching more pairs than are co-resident would make the surplus run as a second
 // wave after the first has finished all its work.  Not every SM can be paired (pairs do not span
 // GPCs, and a GPC may have an odd number of SMs), so the answer can be less than SMs / 2.
-cudaError_t assign_tc_pair_prepare(int* max_pairs)
+cudaError_t assign_tc_pair_prepare(int sm_count, int* max_pairs)
 {
 	cudaError_t e = cudaFuncSetAttribute(assign_tc_pair_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_ALLOC);
 	if (e != cudaSuccess) return e;
 	e = cudaFuncSetAttribute(assign_tc_pair_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_ALLOC);
 	if (e != cudaSuccess) return e;
 	cudaLaunchConfig_t cfg = {};
-	cfg.gridDim = dim3(2 * 74, 1, 1);
+	cfg.gridDim = dim3(2 * (uint32_t)(sm_count / 2), 1, 1);
 	cfg.blockDim = dim3(TC_THREADS, 1, 1);
 	cfg.dynamicSmemBytes = P2_ALLOC;
 	cudaLaunchAttribute attr;

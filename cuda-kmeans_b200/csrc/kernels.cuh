@@ -37,6 +37,9 @@ struct TcPoints {
 };
 constexpr uint32_t TC_JSPLIT = 2;   // CTAs that can share the mean tiles of one point block in the K loop
 
+// SM count of the current device (cached per device ordinal; 1 if the query fails).
+int current_sm_count();
+
 // ---- means preparation + divide (update.cu) ----
 
 // means (given layout) -> CUDA-core rows and/or tensor-core operands; cmax2 -> ctl slot.
@@ -103,6 +106,9 @@ bool tc_plan_uses_pair(const TcPlan* plan);
 // the size of the cluster it picked, so that no separate update pass is needed; points that the
 // exact re-check moves afterwards are corrected there.
 bool tc_plan_can_fuse(const TcPlan* plan, const FusedAcc& f);
+// out[0] = BKM_PLAN_* code of the kernel the plan launches, out[1] = mean tiles, out[2] = CTAs that
+// share one point block (1 = no split; > 1 implies the partial-result merge kernel).
+void tc_plan_describe(const TcPlan* plan, uint32_t out[4]);
 cudaError_t launch_assign_tc(TcPlan* plan, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
 	float margin_scale, cudaStream_t stream, const FusedAcc* fused = nullptr);
 

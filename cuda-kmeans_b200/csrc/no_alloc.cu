@@ -24,6 +24,23 @@ uint32_t* g_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per
 // defined in api.cu
 int bkm_internal_fail(int code, const char* fmt, ...);
 
+// Device address of the built-in array on `device` (looked up once per device, with that device
+// current: the array's name is only a host-side handle, the kernels need the address the runtime
+// resolves it to on this device).
+static int scratch_base(int device, uint32_t** base)
+{
+	if (device < 0 || device >= MAX_DEVICES) return bkm_internal_fail(BKM_ERR_UNSUPPORTED, "device ordinal %d out of range", device);
+	std::lock_guard<std::mutex> lock(g_setup_mutex);
+	if (!g_scratch_ptr[device]) {
+		void* p = nullptr;
+		const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+		if (e != cudaSuccess || !p) return bkm_internal_fail(BKM_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+		g_scratch_ptr[device] = static_cast<uint32_t*>(p);
+	}
+	*base = g_scratch_ptr[device];
+	return BKM_OK;
+}
+
 extern "C" int bkm_update_noalloc_f32(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
 	uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means, void* stream)
 {
@@ -41,20 +58,9 @@ extern "C" int bkm_update_noalloc_f32(const float* points, const uint32_t* assig
 	int device = 0;
 	cudaError_t e = cudaGetDevice(&device);
 	if (e != cudaSuccess) return bkm_internal_fail(BKM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-	if (device < 0 || device >= MAX_DEVICES) return bkm_internal_fail(BKM_ERR_UNSUPPORTED, "device ordinal %d out of range", device);
 	uint32_t* base = nullptr;
-	{
-		// Once per device, with that device current: the array's name is only a host-side handle,
-		// the kernels need the address the runtime resolves it to on this device.
-		std::lock_guard<std::mutex> lock(g_setup_mutex);
-		if (!g_scratch_ptr[device]) {
-			void* p = nullptr;
-			e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-			if (e != cudaSuccess || !p) return bkm_internal_fail(BKM_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-			g_scratch_ptr[device] = static_cast<uint32_t*>(p);
-		}
-		base = g_scratch_ptr[device];
-	}
+	const int rc = scratch_base(device, &base);
+	if (rc != BKM_OK) return rc;
 	int sm_count = 0;
 	e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
 	if (e != cudaSuccess) return bkm_internal_fail(BKM_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
@@ -81,5 +87,24 @@ extern "C" int bkm_update_noalloc_f32(const float* points, const uint32_t* assig
 	bkm::launch_finalize(acc, counts, replicas, means, sizes, s, nullptr, nullptr, ctl, 1, st);
 	e = cudaGetLastError();
 	if (e != cudaSuccess) return bkm_internal_fail(BKM_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+	return BKM_OK;
+}
+
+// Reads the status word the kernels of the last bkm_update_noalloc_f32 call on the current device
+// left at the head of the built-in array (after waiting for `stream`).
+extern "C" int bkm_noalloc_check(void* stream)
+{
+	int device = 0;
+	cudaError_t e = cudaGetDevice(&device);
+	if (e != cudaSuccess) return bkm_internal_fail(BKM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+	uint32_t* base = nullptr;
+	const int rc = scratch_base(device, &base);
+	if (rc != BKM_OK) return rc;
+	bkm::Control c;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	e = cudaMemcpyAsync(&c, base, sizeof(c), cudaMemcpyDeviceToHost, st);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+	if (e != cudaSuccess) return bkm_internal_fail(BKM_ERR_CUDA, "reading the status word: %s", cudaGetErrorString(e));
+	if (c.status) return bkm_internal_fail(BKM_ERR_DEVICE, "kernel status 0x%x (2=assignment out of range)", c.status);
 	return BKM_OK;
 }

@@ -8,20 +8,6 @@
 #include "kernels.cuh"
 #include "ptx.cuh"
 
-// Optional stage timing for development builds (-DBKM_TC_TIMING): one CTA prints how its MMA warp
-// and three of its epilogue warps spent their cycles.
-#ifdef BKM_TC_TRACE
-#include <cstdio>
-#endif
-#ifdef BKM_TC_TIMING
-#include <cstdio>
-#define TC_T(var) const long long var = clock64()
-#define TC_ACC(sum, from, to) sum += (to) - (from)
-#else
-#define TC_T(var)
-#define TC_ACC(sum, from, to)
-#endif
-
 namespace bkm {
 
 constexpr uint32_t TC_MA = 2;            // point tiles per block (= TMEM accumulators)
@@ -214,7 +200,7 @@ __device__ __forceinline__ void fill_a_aug(float* a_aug, float offset_c, uint32_
 
 // ---- the CTA-pair kernel (assign_tc_pair.cu), used through the plan of assign_tc.cu ----
 bool assign_tc_pair_supported(uint32_t k, uint32_t k_pad, uint32_t d_pad, uint32_t nt_cols, int sm_count);
-cudaError_t assign_tc_pair_prepare(int* max_pairs);
+cudaError_t assign_tc_pair_prepare(int sm_count, int* max_pairs);
 cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_lo, const CUtensorMap& b_hi, const CUtensorMap& b_lo,
 	const float* b_aug, const float* xnorm, uint32_t* asg, uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t d_pad,
 	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream,

@@ -32,6 +32,18 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 	asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+int current_sm_count()
+{
+	static int cache[64] = {};
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 1; }
+	if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+	int sms = 0;
+	if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) { cudaGetLastError(); return 1; }
+	if (dev >= 0 && dev < 64) cache[dev] = sms;
+	return sms;
+}
+
 constexpr int UPD_THREADS = 512;
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
@@ -151,7 +163,7 @@ static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t repl
 	if (tc) rows_total = std::max(rows_total, tc->k_pad);
 	const uint32_t wpb = 8;
 	uint32_t grid = (rows_total + wpb - 1) / wpb;
-	grid = std::min<uint32_t>(std::max<uint32_t>(grid, 1), 148 * 8);
+	grid = std::min<uint32_t>(std::max<uint32_t>(grid, 1), (uint32_t)current_sm_count() * 8);
 	float* bh = tc ? tc->b_hi : nullptr;
 	float* bl = tc ? tc->b_lo : nullptr;
 	float* cn = tc ? tc->cnorm : nullptr;
@@ -200,7 +212,7 @@ void launch_merge_replicas(float* acc, uint32_t* counts, uint32_t replicas, cons
 {
 	if (replicas <= 1) return;
 	const size_t kd = (size_t)s.k * s.dim;
-	const uint32_t grid = (uint32_t)std::min<size_t>((kd + s.k + 255) / 256, 148 * 8);
+	const uint32_t grid = (uint32_t)std::min<size_t>((kd + s.k + 255) / 256, (size_t)current_sm_count() * 8);
 	merge_replicas_kernel<<<grid, 256, 0, stream>>>(acc, counts, replicas, acc_replica_stride(s.k, s.dim), kd, s.k);
 }
 

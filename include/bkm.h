@@ -127,6 +127,12 @@ int bkm_iterate_f32(const float* points, const float* means_in, float* means_out
 int bkm_update_noalloc_f32(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
                            uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means, void* stream);
 
+/* The bkm_workspace_check of bkm_update_noalloc_f32 (likewise without a counterpart in the
+ * reference): waits for `stream` and returns BKM_ERR_DEVICE if the last such call on the current
+ * device met an assignment value >= k (the point is then left out of sums and sizes).  Allocates
+ * nothing; reads the status word at the head of the built-in array. */
+int bkm_noalloc_check(void* stream);
+
 /* Waits for `stream` and returns BKM_ERR_DEVICE if a kernel of the calls issued on this
  * workspace since its last check recorded an error (a bounded wait that ran out, an assignment
  * value >= k fed to the update).  The counterpart of the reference's CUCH(cudaGetLastError())
@@ -232,6 +238,19 @@ int bkm_phase_ms(bkm_handle_t h, float out[6]);
  * out[1]=kernels launched per iteration, out[2]=assignment variant used,
  * out[3]=update variant used. */
 int bkm_counters(bkm_handle_t h, uint64_t out[4]);
+
+/* Which assignment kernel the handle launches and how (for tests and tuning; no counterpart in the
+ * reference, whose runner is fixed by the ASGN_KERNEL template argument): out[0] = BKM_PLAN_* code,
+ * out[1] = tiles of up to 256 means the tensor-core kernels walk (0 otherwise), out[2] = CTAs that
+ * share one block of points and split its mean tiles between them (1 = none; > 1 means the partial
+ * results are combined by a small merge kernel), out[3] = 1 when the last iteration's assignment
+ * pass also accumulated the update sums.  Valid after bkm_initialize. */
+#define BKM_PLAN_EXACT 0        /* CUDA cores, reference arithmetic */
+#define BKM_PLAN_SIMT 1         /* CUDA cores, small-dim fast pass */
+#define BKM_PLAN_TC_RESIDENT 2  /* tcgen05, one CTA per SM, point tiles resident (dim <= 32) */
+#define BKM_PLAN_TC_KLOOP 3     /* tcgen05, one CTA per SM, both operands stream in slices (dim > 32) */
+#define BKM_PLAN_TC_PAIR 4      /* tcgen05 on CTA pairs, all means resident in shared memory */
+int bkm_assign_plan(bkm_handle_t h, uint32_t out[4]);
 
 /* ---- multi-GPU (one process per GPU) ------------------------------------------------------ */
 

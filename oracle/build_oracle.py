@@ -9,15 +9,16 @@ Builds two shared libraries:
   experimental/k-means/k-means/Makefile:1-3).  Skipped when the reference checkout is absent
   (the prebuilt file is then used if it exists).
 
-Run ``python oracle/build_oracle.py``; the reference location can be overridden with the
-environment variable ``KMEANS_REFERENCE_DIR``.
+Run ``python oracle/build_oracle.py``.  The reference checkout is looked for in the directory
+named by the environment variable ``KMEANS_REFERENCE_DIR``, else in a directory ``reference``
+beside this repository.
 """
 import os
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("KMEANS_REFERENCE_DIR", "/root/reference")
+REF_DIR = os.environ.get("KMEANS_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_HEADERS = os.path.join(REF_DIR, "experimental", "k-means", "k-means", "headers")
 
 ORACLE_SO = os.path.join(HERE, "libkmoracle.so")

@@ -12,7 +12,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "tests", "cpp", "adaptor_check")
-REF_HEADERS = os.path.join(os.environ.get("KMEANS_REFERENCE_DIR", "/root/reference"),
+REF_HEADERS = os.path.join(os.environ.get("KMEANS_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference"),
                            "experimental", "k-means", "k-means", "headers")
 
 

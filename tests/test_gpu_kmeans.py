@@ -199,3 +199,66 @@ def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
     want64, _ = oracle_mod.update_f64(data, asg, n, k, d, lay, lay)
     ok, err = means_close(cur, want64)
     assert ok, err
+
+
+def test_c4_tile_structure_split_k_loop(pkg, torch_cuda, oracle_mod, workloads):
+    """dim 512 with 4096 means - the benchmarked c4 structure: 16 mean tiles through the K loop,
+    neighbouring CTAs sharing a point block (split 2) and the partial-result merge kernel, then the
+    dim-512 exact re-check.  Step-wise against the oracle (serial.hpp:21-73): assignment bit for bit,
+    sizes exactly, means within 1e-4.  n is not a multiple of the 128-point tile."""
+    n, k, d = 6007, 4096, 512
+    rows = workloads.generate_rows("sphere", n, d, k, seed=17)
+    data, means = workloads.to_layout(rows, 0), workloads.to_layout(rows[:k], 0)
+    km = pkg.KMeans(layout=0)
+    km.initialize(d, k, n, 2, data, means)
+    plan = km.assign_plan()
+    assert plan["kernel"] == "tc_kloop" and plan["mean_tiles"] == 16 and plan["block_split"] == 2, plan
+    prev = means.copy()
+    for it in range(2):
+        km.run(1)
+        asg, cur, sizes = km.getAssignment(), km.getMeans(), km.getSizes()
+        want = oracle_mod.assign(data, prev, n, k, d, 0, 0, threads=8)
+        assert np.array_equal(asg, want), (it, int((asg != want).sum()))
+        want_means, want_sizes = oracle_mod.update(data, asg, n, k, d, 0, 0)
+        assert np.array_equal(sizes, want_sizes), it
+        ok, err = means_close(cur, want_means)
+        assert ok, (it, err)
+        prev = cur
+    km.cleanup()
+
+
+def test_c4_structure_with_a_recheck_list_longer_than_the_grid(pkg, torch_cuda, oracle_mod, workloads):
+    """The same structure with the near-tie band widened until (nearly) every point is queued: the
+    exact re-check then walks a list longer than its grid (blocks loop over groups instead of sharing
+    them) and must still reproduce the oracle's assignment bit for bit."""
+    n, k, d = 8192, 4096, 512
+    rows = workloads.generate_rows("sphere", n, d, k, seed=19)
+    data, means = workloads.to_layout(rows, 0), workloads.to_layout(rows[:k], 0)
+    km = pkg.KMeans(layout=0)
+    km.set_option("margin_scale", 1.0e6)
+    km.initialize(d, k, n, 1, data, means)
+    km.run(1)
+    asg = km.getAssignment()
+    info = km.counters()
+    km.cleanup()
+    assert info["rechecked"] > 148 * 8 * 4, info
+    want = oracle_mod.assign(data, means, n, k, d, 0, 0, threads=8)
+    assert np.array_equal(asg, want), int((asg != want).sum())
+
+
+def test_legacy_default_stream_with_many_iterations(pkg, torch_cuda, oracle_mod, workloads):
+    """bkm_set_stream(h, NULL) selects the legacy default stream (the reference drivers' stream,
+    headers/cuda.hpp:70-88), which cannot be captured into a CUDA graph: a launch-bound problem with
+    enough iterations for graph replay must fall back to plain launches there."""
+    data, means, spec = workloads.make("c1", n=1 << 13)
+    k, d, lay = spec["k"], spec["dim"], spec["layout"]
+    km = pkg.KMeans(layout=lay)
+    km.set_stream(0)
+    km.initialize(d, k, 1 << 13, 8, data, means)
+    km.run(8)
+    got_means, got_asg = km.getMeans(), km.getAssignment()
+    km.cleanup()
+    want_means, want_asg = oracle_mod.kmeans(data, means, 1 << 13, k, d, 8, lay, lay)
+    ok, err = means_close(got_means, want_means)
+    assert ok, err
+    assert (got_asg != want_asg).mean() <= 1e-3
