@@ -37,7 +37,8 @@ SYMBOLS = [
     "bkm_device_means", "bkm_device_assignment", "bkm_set_means", "bkm_iterations_done",
     "bkm_phase_ms", "bkm_counters", "bkm_comm_unique_id", "bkm_comm_init", "bkm_shard_range",
     "bkm_kmeans_host_f32", "bkm_update_noalloc_f32", "bkm_selftest_wait_timeout", "bkm_assign_plan",
-    "bkm_noalloc_check",
+    "bkm_noalloc_check", "bkm_peer_export", "bkm_peer_open", "bkm_peer_buffer", "bkm_peer_attach", "bkm_peer_enable",
+    "bkm_peer_layout", "bkm_run_ready",
 ]
 
 
@@ -106,6 +107,13 @@ def lib():
     L.bkm_selftest_wait_timeout.argtypes = [vp, u32, vp]
     L.bkm_assign_plan.argtypes = [vp, ctypes.POINTER(u32)]
     L.bkm_noalloc_check.argtypes = [vp]
+    L.bkm_peer_export.argtypes = [vp, vp, sz]
+    L.bkm_peer_open.argtypes = [vp, vp, sz, ci, ci]
+    L.bkm_peer_buffer.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(sz)]
+    L.bkm_peer_attach.argtypes = [vp, ctypes.POINTER(vp), ci, ci]
+    L.bkm_peer_enable.argtypes = [vp, ci]
+    L.bkm_peer_layout.argtypes = [u32, u32, ctypes.POINTER(u64)]
+    L.bkm_run_ready.argtypes = [vp]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("bkm_last_error", "bkm_workspace_bytes"):
@@ -151,6 +159,26 @@ def _preload_nccl():
             except OSError:
                 pass
             return
+
+
+def agree(dist, torch, code, device="cpu"):
+    """Host-side agreement of all ranks of a torch.distributed process group on one status code:
+    every rank passes its own (OK or an error code) and receives the largest.  Used before a
+    step in which one failing rank would leave the others waiting for it: when the result is not
+    OK, no rank may enter that step."""
+    t = torch.tensor([int(code)], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(t.item())
+
+
+PEER_BLOB_BYTES = 128
+
+
+def peer_layout(k, dim):
+    """dict with the layout of an exchange buffer (bkm_peer_layout)."""
+    arr = (ctypes.c_uint64 * 4)()
+    check(lib().bkm_peer_layout(k, dim, arr))
+    return {"bytes": int(arr[0]), "flag_words": int(arr[1]), "slot0_offset": int(arr[2]), "slot_stride": int(arr[3])}
 
 
 def comm_unique_id():
@@ -309,6 +337,57 @@ class KMeans:
         _preload_nccl()
         buf = ctypes.create_string_buffer(bytes(unique_id), 128)
         check(lib().bkm_comm_init(self._need(), buf, 128, world_size, rank))
+
+    # -- exchange through peer memory (see bkm.h) --
+    def peer_export(self):
+        buf = ctypes.create_string_buffer(PEER_BLOB_BYTES)
+        check(lib().bkm_peer_export(self._need(), buf, PEER_BLOB_BYTES))
+        return buf.raw
+
+    def peer_open(self, blobs, world_size, rank):
+        data = bytes(blobs)
+        if len(data) != PEER_BLOB_BYTES * world_size:
+            raise ValueError("expected %d blobs of %d bytes" % (world_size, PEER_BLOB_BYTES))
+        check(lib().bkm_peer_open(self._need(), ctypes.create_string_buffer(data, len(data)), PEER_BLOB_BYTES, world_size, rank))
+
+    def peer_buffer(self):
+        p, n = ctypes.c_void_p(), ctypes.c_size_t()
+        check(lib().bkm_peer_buffer(self._need(), ctypes.byref(p), ctypes.byref(n)))
+        return p.value, n.value
+
+    def peer_attach(self, bases, rank):
+        arr = (ctypes.c_void_p * len(bases))(*[ctypes.c_void_p(b) for b in bases])
+        check(lib().bkm_peer_attach(self._need(), arr, len(bases), rank))
+
+    def peer_enable(self, on=True):
+        check(lib().bkm_peer_enable(self._need(), 1 if on else 0))
+
+    def run_ready(self):
+        """Status code of bkm_run_ready (OK = an iteration could start now); never raises."""
+        return lib().bkm_run_ready(self._h) if self._h is not None else ERR_STATE
+
+    def peer_exchange_init(self, dist, torch, device="cuda"):
+        """Sets the peer-memory exchange up over a torch.distributed process group: gathers every
+        rank's blob, opens the peers' buffers, and switches the exchange on only if EVERY rank
+        succeeded (the ranks agree through the process group); returns whether it is on."""
+        world, rank = dist.get_world_size(), dist.get_rank()
+        ok = 1
+        try:
+            mine = torch.frombuffer(bytearray(self.peer_export()), dtype=torch.uint8).to(device)
+        except BkmError:
+            ok = 0
+            mine = torch.zeros(PEER_BLOB_BYTES, dtype=torch.uint8, device=device)
+        blobs = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(blobs, mine)
+        if ok:
+            try:
+                self.peer_open(b"".join(bytes(b.cpu().numpy().tobytes()) for b in blobs), world, rank)
+            except BkmError:
+                ok = 0
+        if agree(dist, torch, 0 if ok else ERR_CUDA, device) != OK:
+            return False
+        self.peer_enable(True)
+        return True
 
     def device_means(self):
         p = ctypes.c_void_p()

@@ -287,6 +287,14 @@ struct bkm_handle_s {
 	// NCCL
 	void* comm = nullptr;
 	int world = 1, rank = 0;
+	// peer-memory exchange: this rank's buffer, every rank's buffer as addressable from this device
+	void* d_xbuf = nullptr;
+	void* peer_base[bkm::EXCHANGE_MAX_RANKS] = {};
+	bool peer_ipc[bkm::EXCHANGE_MAX_RANKS] = {};   // opened with cudaIpcOpenMemHandle (to be closed)
+	int peer_world = 0;
+	bool peer_on = false;
+	uint32_t epoch = 0;                            // iterations exchanged so far (the same on every rank)
+	uint64_t exchange_wait_ns = 10000000000ull;
 	// phase events of the most recent run
 	static constexpr int EV_RING = 256, EV_PER = 6;
 	cudaEvent_t ev[EV_RING][EV_PER] = {};
@@ -520,6 +528,9 @@ int bkm_destroy(bkm_handle_t h)
 	if (h->stream) cudaStreamSynchronize(h->stream);
 	drop_graph(h);
 	if (h->comm && nccl()->ok) nccl()->CommDestroy(h->comm);
+	for (uint32_t r = 0; r < bkm::EXCHANGE_MAX_RANKS; ++r)
+		if (h->peer_ipc[r] && h->peer_base[r]) cudaIpcCloseMemHandle(h->peer_base[r]);
+	cudaFree(h->d_xbuf);
 	if (h->plan) bkm::tc_plan_destroy(h->plan);
 	for (int i = 0; i < bkm_handle_s::EV_RING; ++i)
 		for (int j = 0; j < bkm_handle_s::EV_PER; ++j)
@@ -563,6 +574,11 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value)
 	if (!strcmp(name, "fuse_update")) {
 		h->fuse_update = value != 0.0;
 		drop_graph(h);
+		return BKM_OK;
+	}
+	if (!strcmp(name, "exchange_wait_ms")) {
+		if (!(value >= 1.0 && value <= 600000.0)) return fail(BKM_ERR_INVALID, "exchange_wait_ms must be 1..600000");
+		h->exchange_wait_ns = (uint64_t)(value * 1.0e6);
 		return BKM_OK;
 	}
 	if (!strcmp(name, "tc_pair")) {
@@ -665,6 +681,19 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 	if (!fused)
 		bkm::launch_update(h->d_points, h->d_asg, h->ws.acc, h->ws.counts, h->ws.replicas, s, h->update_variant, h->ws.ctl, h->sm_count, st);
 	if (ev) CUDA_TRY(cudaEventRecord(ev[3], st));
+	if (h->peer_on) {
+		// one kernel: publish this rank's sums, read the peers', add in rank order, divide, next operands
+		++h->epoch;
+		CUDA_TRY(bkm::launch_exchange_finalize(h->ws.acc, h->ws.counts, h->ws.replicas, h->peer_base, (uint32_t)h->peer_world,
+			(uint32_t)h->rank, h->epoch, h->exchange_wait_ns, h->d_means[next], h->d_sizes, s,
+			h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+			h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st));
+		if (ev) { CUDA_TRY(cudaEventRecord(ev[4], st)); CUDA_TRY(cudaEventRecord(ev[5], st)); }
+		h->cur = next;
+		h->slot ^= 1;
+		++h->iters_done;
+		return BKM_OK;
+	}
 	if (h->comm) {
 		bkm::launch_merge_replicas(h->ws.acc, h->ws.counts, h->ws.replicas, s, st);
 		Nccl* nc = nccl();
@@ -695,7 +724,7 @@ static void drop_graph(bkm_handle_t h)
 // replayed.  The graph is rebuilt when the starting buffers differ from the captured ones.
 static bool graph_wanted(bkm_handle_t h, uint32_t iters)
 {
-	if (h->comm || iters < 4) return false;
+	if (h->comm || h->peer_on || iters < 4) return false;
 	if (h->use_graph == 0) return false;
 	// the legacy default stream (what bkm_set_stream(h, NULL) selects) and the per-thread default
 	// stream cannot be captured: plain launches there
@@ -894,6 +923,147 @@ int bkm_comm_init(bkm_handle_t h, const void* id, size_t id_bytes, int world_siz
 	NCCL_TRY(nc->CommInitRank(&h->comm, world_size, uid, rank));
 	h->world = world_size;
 	h->rank = rank;
+	return BKM_OK;
+}
+
+// ---- peer-memory exchange -------------------------------------------------------------------------
+
+namespace {
+
+struct PeerBlob {                 // what one rank tells the others about its exchange buffer
+	cudaIpcMemHandle_t handle;    // 64 bytes
+	uint32_t k, dim;
+	uint64_t bytes;
+	uint32_t magic;
+	uint32_t pad[11];
+};
+static_assert(sizeof(PeerBlob) == BKM_PEER_BLOB_BYTES, "blob size is part of the ABI");
+constexpr uint32_t PEER_MAGIC = 0x626b6d78u;
+
+int own_exchange_buffer(bkm_handle_t h)
+{
+	if (h->d_xbuf) return BKM_OK;
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	const size_t bytes = bkm::exchange_buffer_bytes(h->shape.k, h->shape.dim);
+	CUDA_TRY(cudaMalloc(&h->d_xbuf, bytes));
+	CUDA_TRY(cudaMemset(h->d_xbuf, 0, bytes));
+	return BKM_OK;
+}
+
+} // namespace
+
+int bkm_peer_layout(uint32_t k, uint32_t dim, uint64_t out[4])
+{
+	if (!out || k == 0 || dim == 0) return fail(BKM_ERR_INVALID, "bad argument");
+	out[0] = bkm::exchange_buffer_bytes(k, dim);
+	out[1] = bkm::EXCHANGE_MAX_BLOCKS;                        // flag words at the start
+	out[2] = bkm::EXCHANGE_MAX_BLOCKS * sizeof(uint32_t);     // byte offset of publication slot 0
+	out[3] = bkm::exchange_slot_words(k, dim) * sizeof(uint32_t);   // bytes from slot 0 to slot 1
+	return BKM_OK;
+}
+
+int bkm_peer_buffer(bkm_handle_t h, void** base, size_t* bytes)
+{
+	if (!h || !base) return fail(BKM_ERR_INVALID, "null argument");
+	int rc = own_exchange_buffer(h);
+	if (rc) return rc;
+	*base = h->d_xbuf;
+	if (bytes) *bytes = bkm::exchange_buffer_bytes(h->shape.k, h->shape.dim);
+	return BKM_OK;
+}
+
+int bkm_peer_export(bkm_handle_t h, void* blob, size_t blob_bytes)
+{
+	if (!h || !blob || blob_bytes < sizeof(PeerBlob)) return fail(BKM_ERR_INVALID, "blob buffer must hold %d bytes", (int)BKM_PEER_BLOB_BYTES);
+	int rc = own_exchange_buffer(h);
+	if (rc) return rc;
+	PeerBlob b;
+	memset(&b, 0, sizeof(b));
+	CUDA_TRY(cudaIpcGetMemHandle(&b.handle, h->d_xbuf));
+	b.k = h->shape.k; b.dim = h->shape.dim;
+	b.bytes = bkm::exchange_buffer_bytes(h->shape.k, h->shape.dim);
+	b.magic = PEER_MAGIC;
+	memcpy(blob, &b, sizeof(b));
+	return BKM_OK;
+}
+
+static int peer_world_check(bkm_handle_t h, int world_size, int rank)
+{
+	if (world_size < 2 || world_size > (int)bkm::EXCHANGE_MAX_RANKS || rank < 0 || rank >= world_size)
+		return fail(BKM_ERR_UNSUPPORTED, "the peer exchange handles 2..%d ranks (world_size=%d rank=%d)", (int)bkm::EXCHANGE_MAX_RANKS, world_size, rank);
+	if (h->comm && (h->world != world_size || h->rank != rank))
+		return fail(BKM_ERR_INVALID, "world_size/rank differ from the NCCL communicator's");
+	if (h->peer_world) return fail(BKM_ERR_STATE, "peer buffers already attached");
+	return BKM_OK;
+}
+
+int bkm_peer_open(bkm_handle_t h, const void* blobs, size_t blob_bytes, int world_size, int rank)
+{
+	if (!h || !blobs || blob_bytes != sizeof(PeerBlob)) return fail(BKM_ERR_INVALID, "bad argument");
+	int rc = peer_world_check(h, world_size, rank);
+	if (rc) return rc;
+	if ((rc = own_exchange_buffer(h))) return rc;
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	const char* p = static_cast<const char*>(blobs);
+	for (int r = 0; r < world_size; ++r) {
+		PeerBlob b;
+		memcpy(&b, p + (size_t)r * sizeof(PeerBlob), sizeof(b));
+		if (b.magic != PEER_MAGIC || b.k != h->shape.k || b.dim != h->shape.dim)
+			return fail(BKM_ERR_INVALID, "rank %d exports an exchange buffer for another problem (k=%u dim=%u)", r, b.k, b.dim);
+		if (r == rank) { h->peer_base[r] = h->d_xbuf; continue; }
+		void* ptr = nullptr;
+		cudaError_t e = cudaIpcOpenMemHandle(&ptr, b.handle, cudaIpcMemLazyEnablePeerAccess);
+		if (e != cudaSuccess) {
+			cudaGetLastError();
+			for (int q = 0; q < r; ++q) if (h->peer_ipc[q]) { cudaIpcCloseMemHandle(h->peer_base[q]); h->peer_ipc[q] = false; h->peer_base[q] = nullptr; }
+			return fail(BKM_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d: %s", r, cudaGetErrorString(e));
+		}
+		h->peer_base[r] = ptr;
+		h->peer_ipc[r] = true;
+	}
+	h->peer_world = world_size;
+	h->world = world_size;
+	h->rank = rank;
+	return BKM_OK;
+}
+
+int bkm_peer_attach(bkm_handle_t h, void* const* bases, int world_size, int rank)
+{
+	if (!h || !bases) return fail(BKM_ERR_INVALID, "null argument");
+	int rc = peer_world_check(h, world_size, rank);
+	if (rc) return rc;
+	if ((rc = own_exchange_buffer(h))) return rc;
+	for (int r = 0; r < world_size; ++r) {
+		if (r != rank && !bases[r]) return fail(BKM_ERR_INVALID, "buffer of rank %d is null", r);
+		h->peer_base[r] = r == rank ? h->d_xbuf : bases[r];
+	}
+	h->peer_world = world_size;
+	h->world = world_size;
+	h->rank = rank;
+	return BKM_OK;
+}
+
+int bkm_peer_enable(bkm_handle_t h, int enable)
+{
+	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	if (enable && !h->peer_world) return fail(BKM_ERR_STATE, "no peer buffers attached (bkm_peer_open / bkm_peer_attach first)");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	h->peer_on = enable != 0;
+	drop_graph(h);
+	return BKM_OK;
+}
+
+int bkm_run_ready(bkm_handle_t h)
+{
+	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	if (!h->initialized) return fail(BKM_ERR_STATE, "not initialized");
+	if (h->assign_variant == BKM_ASSIGN_TC && !h->plan) return fail(BKM_ERR_STATE, "the tensor-core plan is missing");
+	CUDA_TRY(cudaSetDevice(h->cfg.device));
+	bkm::Control c;
+	CUDA_TRY(cudaStreamSynchronize(h->stream));
+	CUDA_TRY(cudaMemcpy(&c, h->ws.ctl, sizeof(c), cudaMemcpyDeviceToHost));
+	if (c.status) return fail(BKM_ERR_DEVICE, "kernel status 0x%x is pending", c.status);
 	return BKM_OK;
 }
 

@@ -58,124 +58,305 @@ __device__ __forceinline__ float tf32_rna(float x)
 // finalize / prepare
 // ------------------------------------------------------------------------------------------
 
+// Where the rows of the fresh means go: the means themselves (in their layout), the cluster sizes,
+// and the operands the next assignment pass reads.
+struct RowSinks {
+	float* means_out; uint32_t* sizes_out;
+	uint32_t k, d; int soa_means;
+	float* cprep; uint32_t rs, srows;
+	float* b_hi; float* b_lo; float* cnorm; float* b_aug; const float* center; uint32_t k_pad, d_pad;
+	Control* ctl; int slot;
+};
+
+// One warp finishes row c < k.  `mean_of(j)` yields coordinate j of the mean (lane-strided calls).
+template<class MEAN>
+__device__ __forceinline__ void finish_row(const RowSinks& o, uint32_t c, uint32_t lane, bool write_means, uint32_t cnt, MEAN mean_of)
+{
+	float s2 = 0.0f;
+	for (uint32_t j = lane; j < o.d; j += 32) {
+		const float mean = mean_of(j);
+		if (write_means) o.means_out[at_rt(o.soa_means, c, j, o.k, o.d)] = mean;
+		// the tensor-core operands and the norms use the mean relative to the common centre
+		const float shifted = o.center ? mean - o.center[j] : mean;
+		s2 = fmaf(shifted, shifted, s2);
+		const float b = -2.0f * shifted;
+		if (o.cprep) o.cprep[(size_t)c * o.rs + 1 + j] = mean;
+		if (o.b_hi) {
+			const float hi = tf32_rna(b);
+			const float lo = tf32_rna(b - hi);
+			o.b_hi[(size_t)c * o.d_pad + j] = hi;
+			o.b_lo[(size_t)c * o.d_pad + j] = lo;
+		}
+	}
+	#pragma unroll
+	for (int off = 16; off > 0; off >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+	__syncwarp();
+	if (lane == 0) {
+		if (o.cprep) o.cprep[(size_t)c * o.rs] = 0.0f;
+		if (o.cnorm) o.cnorm[c] = s2;
+		if (o.b_aug) {
+			const float hi = tf32_rna(s2);
+			const float lo = tf32_rna(s2 - hi);
+			float4* dst = reinterpret_cast<float4*>(o.b_aug + aug_offset(c, 0));
+			dst[0] = make_float4(hi, lo, 1.0f, 1.0f);
+			dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);    // columns 4..7 sit 32 floats further
+		}
+		atomicMax(reinterpret_cast<int*>(&o.ctl->cmax2[o.slot]), __float_as_int(s2));
+		if (write_means) o.sizes_out[c] = cnt;
+	}
+}
+
+// Rows behind the last mean: padding that can never win (their additive term is +inf, the coordinates stay zero).
+__device__ __forceinline__ void finish_padding_row(const RowSinks& o, uint32_t c)
+{
+	if (o.cprep && c < o.srows) o.cprep[(size_t)c * o.rs] = INFINITY;
+	if (o.cnorm && c < o.k_pad) o.cnorm[c] = INFINITY;
+	if (o.b_aug && c < o.k_pad) {
+		float4* dst = reinterpret_cast<float4*>(o.b_aug + aug_offset(c, 0));
+		dst[0] = make_float4(0.0f, 0.0f, 1.0f, 1.0f);
+		dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+	}
+}
+
+__device__ __forceinline__ void finish_control(Control* ctl, int slot)
+{
+	ctl->last_flag_count = ctl->flag_count;
+	ctl->flag_count = 0;
+	ctl->cmax2[slot ^ 1] = 0.0f;
+}
+
+__device__ __forceinline__ uint32_t rows_to_finish(const RowSinks& o)
+{
+	uint32_t rows_total = o.k;
+	if (o.cprep && o.srows > rows_total) rows_total = o.srows;
+	if (o.cnorm && o.k_pad > rows_total) rows_total = o.k_pad;
+	return rows_total;
+}
+
+// Sum over the `replicas` copies of one accumulator word (copies `rep_stride` words apart), clearing them.
+__device__ __forceinline__ float sum_and_clear(float* src, uint32_t replicas, size_t rep_stride)
+{
+	float sum = 0.0f;
+	uint32_t r = 0;
+	for (; r + 4 <= replicas; r += 4) {
+		// four independent loads in flight
+		const float s0 = src[(r + 0) * rep_stride], s1 = src[(r + 1) * rep_stride];
+		const float s2b = src[(r + 2) * rep_stride], s3 = src[(r + 3) * rep_stride];
+		src[(r + 0) * rep_stride] = 0.0f; src[(r + 1) * rep_stride] = 0.0f;
+		src[(r + 2) * rep_stride] = 0.0f; src[(r + 3) * rep_stride] = 0.0f;
+		sum += (s0 + s1) + (s2b + s3);
+	}
+	for (; r < replicas; ++r) { sum += src[r * rep_stride]; src[r * rep_stride] = 0.0f; }
+	return sum;
+}
+
 // `replicas` copies of (sums, sizes) lie `rep_stride` 32-bit words apart; all are added up and cleared.
 template<bool FINALIZE>
 __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict__ acc, uint32_t* __restrict__ counts,
-	uint32_t replicas, size_t rep_stride,
-	const float* __restrict__ means_in, float* __restrict__ means_out, uint32_t* __restrict__ sizes_out,
-	uint32_t k, uint32_t d, int soa_means,
-	float* __restrict__ cprep, uint32_t rs, uint32_t srows,
-	float* __restrict__ b_hi, float* __restrict__ b_lo, float* __restrict__ cnorm, float* __restrict__ b_aug,
-	const float* __restrict__ center, uint32_t k_pad, uint32_t d_pad, Control* __restrict__ ctl, int slot)
+	uint32_t replicas, size_t rep_stride, const float* __restrict__ means_in, RowSinks o)
 {
 	const uint32_t lane = threadIdx.x & 31u;
 	const uint32_t wpb = blockDim.x >> 5;
-	uint32_t rows_total = k;
-	if (cprep && srows > rows_total) rows_total = srows;
-	if (cnorm && k_pad > rows_total) rows_total = k_pad;
-
+	const uint32_t rows_total = rows_to_finish(o);
 	for (uint32_t c = blockIdx.x * wpb + (threadIdx.x >> 5); c < rows_total; c += gridDim.x * wpb) {
-		if (c < k) {
-			uint32_t cnt = 0;
+		if (c < o.k) {
 			if (FINALIZE) {
+				uint32_t cnt = 0;
 				for (uint32_t r = 0; r < replicas; ++r) cnt += counts[c + r * rep_stride];
-			}
-			const float divisor = (float)cnt;
-			float s2 = 0.0f;
-			for (uint32_t j = lane; j < d; j += 32) {
-				float mean;
-				const size_t mi = at_rt(soa_means, c, j, k, d);
-				if (FINALIZE) {
-					float sum = 0.0f;
-					float* src = acc + (size_t)c * d + j;
-					uint32_t r = 0;
-					for (; r + 4 <= replicas; r += 4) {
-						// four independent loads in flight
-						const float s0 = src[(r + 0) * rep_stride], s1 = src[(r + 1) * rep_stride];
-						const float s2b = src[(r + 2) * rep_stride], s3 = src[(r + 3) * rep_stride];
-						src[(r + 0) * rep_stride] = 0.0f; src[(r + 1) * rep_stride] = 0.0f;
-						src[(r + 2) * rep_stride] = 0.0f; src[(r + 3) * rep_stride] = 0.0f;
-						sum += (s0 + s1) + (s2b + s3);
-					}
-					for (; r < replicas; ++r) { sum += src[r * rep_stride]; src[r * rep_stride] = 0.0f; }
-					mean = cnt ? __fdiv_rn(sum, divisor) : 0.0f;
-					means_out[mi] = mean;
-				} else {
-					mean = means_in[mi];
-				}
-				// the tensor-core operands and the norms use the mean relative to the common centre
-				const float shifted = center ? mean - center[j] : mean;
-				s2 = fmaf(shifted, shifted, s2);
-				const float b = -2.0f * shifted;
-				if (cprep) cprep[(size_t)c * rs + 1 + j] = mean;
-				if (b_hi) {
-					const float hi = tf32_rna(b);
-					const float lo = tf32_rna(b - hi);
-					b_hi[(size_t)c * d_pad + j] = hi;
-					b_lo[(size_t)c * d_pad + j] = lo;
-				}
-			}
-			#pragma unroll
-			for (int off = 16; off > 0; off >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, off);
-			__syncwarp();
-			if (lane == 0) {
-				if (cprep) cprep[(size_t)c * rs] = 0.0f;
-				if (cnorm) cnorm[c] = s2;
-				if (b_aug) {
-					const float hi = tf32_rna(s2);
-					const float lo = tf32_rna(s2 - hi);
-					float4* dst = reinterpret_cast<float4*>(b_aug + aug_offset(c, 0));
-					dst[0] = make_float4(hi, lo, 1.0f, 1.0f);
-					dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);    // columns 4..7 sit 32 floats further
-				}
-				atomicMax(reinterpret_cast<int*>(&ctl->cmax2[slot]), __float_as_int(s2));
-				if (FINALIZE) {
-					sizes_out[c] = cnt;
-					for (uint32_t r = 0; r < replicas; ++r) counts[c + r * rep_stride] = 0;
-				}
+				const float divisor = (float)cnt;
+				finish_row(o, c, lane, true, cnt, [&](uint32_t j) {
+					const float sum = sum_and_clear(acc + (size_t)c * o.d + j, replicas, rep_stride);
+					return cnt ? __fdiv_rn(sum, divisor) : 0.0f;
+				});
+				__syncwarp();
+				if (lane == 0) for (uint32_t r = 0; r < replicas; ++r) counts[c + r * rep_stride] = 0;
+			} else {
+				finish_row(o, c, lane, false, 0u, [&](uint32_t j) { return means_in[at_rt(o.soa_means, c, j, o.k, o.d)]; });
 			}
 		} else if (lane == 0) {
-			// padding rows can never win: their additive term is +inf (the coordinates stay zero)
-			if (cprep && c < srows) cprep[(size_t)c * rs] = INFINITY;
-			if (cnorm && c < k_pad) cnorm[c] = INFINITY;
-			if (b_aug && c < k_pad) {
-				float4* dst = reinterpret_cast<float4*>(b_aug + aug_offset(c, 0));
-				dst[0] = make_float4(0.0f, 0.0f, 1.0f, 1.0f);
-				dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-			}
+			finish_padding_row(o, c);
 		}
 	}
-	if (blockIdx.x == 0 && threadIdx.x == 0) {
-		ctl->last_flag_count = ctl->flag_count;
-		ctl->flag_count = 0;
-		ctl->cmax2[slot ^ 1] = 0.0f;
+	if (blockIdx.x == 0 && threadIdx.x == 0) finish_control(o.ctl, o.slot);
+}
+
+// ------------------------------------------------------------------------------------------
+// exchange between ranks + finalize, in one kernel
+// ------------------------------------------------------------------------------------------
+//
+// Every rank owns one exchange buffer that its peers can read (mapped into their address space):
+//   [ flags: EXCHANGE_MAX_BLOCKS words | two publication slots of (k*dim sums, k sizes) ]
+// Block b of every rank is responsible for the same rows.  It adds up this rank's accumulator
+// copies for its rows, writes the totals into the slot of this iteration (epoch & 1) and then sets
+// its flag to the epoch with a system-scope release.  It waits, with a time limit, until block b
+// of every peer has done the same, reads the peers' totals for its rows with plain peer loads,
+// adds all ranks' values in rank order - so every rank computes bit-identical means - divides,
+// and writes the means and the next assignment's operands as finalize_prepare_kernel does.
+// No block waits for another block of its own grid, and the grid is never larger than the number
+// of SMs, so all blocks of all ranks are resident while they wait for each other.  Two slots are
+// enough: a rank can reach the publication of iteration t+2 only after every peer has published
+// t+1, which a peer does after it has finished reading iteration t.
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
+{
+	uint32_t v;
+	asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+	return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+{
+	asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p)
+{
+	float v;
+	asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+	return v;
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p)
+{
+	uint32_t v;
+	asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+	return v;
+}
+
+struct ExchangePeers {
+	const uint32_t* base[EXCHANGE_MAX_RANKS];   // exchange buffer of every rank (own one included), as seen from this GPU
+};
+
+__global__ void __launch_bounds__(256) exchange_finalize_kernel(float* __restrict__ acc, uint32_t* __restrict__ counts,
+	uint32_t replicas, size_t rep_stride, ExchangePeers peers, uint32_t world, uint32_t rank, uint32_t epoch,
+	uint32_t rows_per_block, uint64_t wait_limit_ns, RowSinks o)
+{
+	__shared__ uint32_t s_timeout;
+	const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+	const uint32_t rows_total = rows_to_finish(o);
+	const uint32_t row0 = blockIdx.x * rows_per_block;
+	const uint32_t row1 = min(rows_total, row0 + rows_per_block);
+	const uint32_t krow1 = min(o.k, row1);                        // rows that carry sums
+	const size_t kd = (size_t)o.k * o.d;
+	const size_t slot_words = exchange_slot_words(o.k, o.d);
+	const size_t slot_off = EXCHANGE_MAX_BLOCKS + (size_t)(epoch & 1u) * slot_words;
+	uint32_t* mine = const_cast<uint32_t*>(peers.base[rank]);
+	float* pub_sums = reinterpret_cast<float*>(mine + slot_off);
+	uint32_t* pub_counts = mine + slot_off + kd;
+	if (threadIdx.x == 0) s_timeout = 0;
+
+	// 1. this rank's totals for the block's rows
+	for (uint32_t c = row0 + warp; c < krow1; c += wpb) {
+		for (uint32_t j = lane; j < o.d; j += 32)
+			pub_sums[(size_t)c * o.d + j] = sum_and_clear(acc + (size_t)c * o.d + j, replicas, rep_stride);
+		if (lane == 0) {
+			uint32_t cnt = 0;
+			for (uint32_t r = 0; r < replicas; ++r) { cnt += counts[c + r * rep_stride]; counts[c + r * rep_stride] = 0; }
+			pub_counts[c] = cnt;
+		}
 	}
+	__threadfence_system();
+	__syncthreads();
+	if (threadIdx.x == 0) st_release_sys(&mine[blockIdx.x], epoch);
+
+	// 2. wait for the same block of every peer (one thread per peer)
+	if (threadIdx.x < world && threadIdx.x != rank && row0 < o.k) {
+		const uint32_t* flag = peers.base[threadIdx.x] + blockIdx.x;
+		uint64_t t0 = 0;
+		uint32_t spins = 0;
+		// epochs only grow; a peer that is already one iteration ahead has left this iteration's slot intact
+		while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+			if ((++spins & 63u) == 0) {
+				uint64_t now;
+				asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+				if (t0 == 0) t0 = now;
+				else if (now - t0 > wait_limit_ns) { s_timeout = 1; break; }
+			}
+			__nanosleep(64);
+		}
+	}
+	__syncthreads();
+	if (s_timeout && threadIdx.x == 0) atomicOr(&o.ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
+
+	// 3. all ranks' totals in rank order, divide, next operands
+	for (uint32_t c = row0 + warp; c < row1; c += wpb) {
+		if (c < o.k) {
+			uint32_t cnt = 0;
+			for (uint32_t r = 0; r < world; ++r) cnt += ld_relaxed_sys_u32(peers.base[r] + slot_off + kd + c);
+			const float divisor = (float)cnt;
+			finish_row(o, c, lane, true, cnt, [&](uint32_t j) {
+				float part[EXCHANGE_MAX_RANKS];
+				#pragma unroll
+				for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r)      // all peer loads in flight together
+					part[r] = r < world ? ld_relaxed_sys_f32(reinterpret_cast<const float*>(peers.base[r] + slot_off) + (size_t)c * o.d + j) : 0.0f;
+				float sum = 0.0f;
+				#pragma unroll
+				for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) if (r < world) sum += part[r];
+				return cnt ? __fdiv_rn(sum, divisor) : 0.0f;
+			});
+		} else if (lane == 0) {
+			finish_padding_row(o, c);
+		}
+	}
+	if (blockIdx.x == 0 && threadIdx.x == 0) finish_control(o.ctl, o.slot);
+}
+
+static RowSinks make_sinks(float* means_out, uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot)
+{
+	RowSinks o;
+	o.means_out = means_out; o.sizes_out = sizes_out;
+	o.k = s.k; o.d = s.dim; o.soa_means = s.soa_means;
+	o.cprep = cprep; o.rs = simt_row_stride(s.dim); o.srows = simt_rows(s.k);
+	o.b_hi = tc ? tc->b_hi : nullptr; o.b_lo = tc ? tc->b_lo : nullptr;
+	o.cnorm = tc ? tc->cnorm : nullptr; o.b_aug = tc ? tc->b_aug : nullptr;
+	o.center = tc ? tc->center : nullptr;
+	o.k_pad = tc ? tc->k_pad : 0; o.d_pad = tc ? tc->d_pad : 0;
+	o.ctl = ctl; o.slot = slot;
+	return o;
+}
+
+static uint32_t sink_rows(const Shape& s, float* cprep, const TcMeans* tc)
+{
+	uint32_t rows_total = s.k;
+	if (cprep) rows_total = std::max(rows_total, simt_rows(s.k));
+	if (tc) rows_total = std::max(rows_total, tc->k_pad);
+	return rows_total;
+}
+
+size_t exchange_buffer_bytes(uint32_t k, uint32_t dim)
+{
+	return (EXCHANGE_MAX_BLOCKS + 2 * exchange_slot_words(k, dim)) * sizeof(uint32_t);
+}
+
+cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, const void* const* peer_bases, uint32_t world,
+	uint32_t rank, uint32_t epoch, uint64_t wait_limit_ns, float* means_out, uint32_t* sizes_out, const Shape& s,
+	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
+{
+	if (world < 1 || world > EXCHANGE_MAX_RANKS || rank >= world) return cudaErrorInvalidValue;
+	ExchangePeers peers;
+	for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) peers.base[r] = r < world ? static_cast<const uint32_t*>(peer_bases[r]) : nullptr;
+	const uint32_t rows_total = sink_rows(s, cprep, tc);
+	// the same split of the rows on every rank: it depends on the shape only, and the grid stays
+	// below the SM count of any GPU this library runs on so that all blocks are resident together
+	const uint32_t rows_per_block = (rows_total + EXCHANGE_MAX_BLOCKS - 1) / EXCHANGE_MAX_BLOCKS;
+	const uint32_t grid = (rows_total + rows_per_block - 1) / rows_per_block;
+	exchange_finalize_kernel<<<grid, 256, 0, stream>>>(acc, counts, replicas, acc_replica_stride(s.k, s.dim), peers, world, rank, epoch,
+		rows_per_block, wait_limit_ns, make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot));
+	return cudaGetLastError();
 }
 
 static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t replicas, const float* means_in, float* means_out,
 	uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
 	const size_t rep_stride = acc_replica_stride(s.k, s.dim);
-	const uint32_t rs = simt_row_stride(s.dim);
-	const uint32_t srows = simt_rows(s.k);
-	uint32_t rows_total = s.k;
-	if (cprep) rows_total = std::max(rows_total, srows);
-	if (tc) rows_total = std::max(rows_total, tc->k_pad);
+	const uint32_t rows_total = sink_rows(s, cprep, tc);
 	const uint32_t wpb = 8;
 	uint32_t grid = (rows_total + wpb - 1) / wpb;
 	grid = std::min<uint32_t>(std::max<uint32_t>(grid, 1), (uint32_t)current_sm_count() * 8);
-	float* bh = tc ? tc->b_hi : nullptr;
-	float* bl = tc ? tc->b_lo : nullptr;
-	float* cn = tc ? tc->cnorm : nullptr;
-	float* ba = tc ? tc->b_aug : nullptr;
-	const float* ce = tc ? tc->center : nullptr;
-	uint32_t kp = tc ? tc->k_pad : 0, dp = tc ? tc->d_pad : 0;
+	const RowSinks o = make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot);
 	if (finalize)
-		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, means_out, sizes_out,
-			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, ce, kp, dp, ctl, slot);
+		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, o);
 	else
-		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, means_out, sizes_out,
-			s.k, s.dim, s.soa_means, cprep, rs, srows, bh, bl, cn, ba, ce, kp, dp, ctl, slot);
+		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, o);
 }
 
 void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,

@@ -187,7 +187,8 @@ int bkm_set_stream(bkm_handle_t h, void* stream);
  * latency; single GPU only), "tc_pair" (0/1, default 1: let the tensor-core assignment run on CTA
  * pairs with all means resident in shared memory where the shape allows, i.e. 257..1024 means
  * of 17..32 dimensions), "fuse_update" (0/1, default 1: let that kernel add every point to the sum
- * of the cluster it picks, which replaces the row-wise update pass of bkm_run; needs dim % 4 == 0).
+ * of the cluster it picks, which replaces the row-wise update pass of bkm_run; needs dim % 4 == 0),
+ * "exchange_wait_ms" (1..600000, default 10000: how long the peer-memory exchange waits for a peer).
  * Unknown names fail with BKM_ERR_INVALID. */
 int bkm_set_option(bkm_handle_t h, const char* name, double value);
 
@@ -265,6 +266,41 @@ int bkm_comm_init(bkm_handle_t h, const void* id, size_t id_bytes, int world_siz
 /* [begin, begin+count) of the points rank `rank` of `world_size` holds when `n_total` points
  * are split into contiguous, near-equal shards (pure host arithmetic, no GPU needed). */
 int bkm_shard_range(uint64_t n_total, int world_size, int rank, uint64_t* begin, uint64_t* count);
+
+/* ---- exchange through peer memory (instead of the NCCL all-reduce) ---------------------------
+ * The sums and sizes of one iteration are k*dim + k words: a latency problem, not a bandwidth
+ * problem.  With this exchange every rank publishes its totals in a small device buffer that the
+ * other ranks map into their address space, and ONE kernel per iteration publishes, waits for the
+ * peers (bounded), reads their totals with ordinary loads over NVLink, adds all ranks' values in
+ * rank order (bit-identical means everywhere), divides and prepares the next operands - in place
+ * of merge + grouped all-reduce + finalize.  2..8 ranks; the reference has no counterpart.
+ * All ranks must make the same sequence of bkm_run calls (the kernels count iterations).
+ *
+ * Several processes: every rank calls bkm_peer_export, the launcher gathers the blobs of all
+ * ranks in rank order, every rank calls bkm_peer_open with the concatenation, the launcher makes
+ * sure that ALL ranks succeeded (otherwise stay with NCCL), then every rank calls
+ * bkm_peer_enable(h, 1).  One process driving several GPUs: bkm_peer_buffer of every handle,
+ * bkm_peer_attach with the raw pointers (peer access enabled by the caller), bkm_peer_enable.
+ * A wait that runs out ("exchange_wait_ms" option, default 10000) sets the status word: the run
+ * returns BKM_ERR_DEVICE instead of hanging when a rank has died or made a different call. */
+#define BKM_PEER_BLOB_BYTES 128
+int bkm_peer_export(bkm_handle_t h, void* blob, size_t blob_bytes);
+int bkm_peer_open(bkm_handle_t h, const void* blobs, size_t blob_bytes_each, int world_size, int rank);
+int bkm_peer_buffer(bkm_handle_t h, void** base, size_t* bytes);
+int bkm_peer_attach(bkm_handle_t h, void* const* bases, int world_size, int rank);
+int bkm_peer_enable(bkm_handle_t h, int enable);
+/* Layout of an exchange buffer (for tests and for hosts that inspect it): out[0] = bytes,
+ * out[1] = number of 32-bit flag words at its start (one per block of the exchange kernel, holding
+ * the last iteration count that block has published), out[2] = byte offset of publication slot 0
+ * (k*dim float sums in row-major cluster order, then k 32-bit sizes), out[3] = bytes from slot 0 to
+ * slot 1 (iteration t uses slot t & 1, t counted from 1).  Pure host arithmetic. */
+int bkm_peer_layout(uint32_t k, uint32_t dim, uint64_t out[4]);
+
+/* BKM_OK when the handle could start an iteration now (initialized, kernels set up, no error
+ * pending).  For multi-rank launchers: reduce the codes of all ranks on the host BEFORE calling
+ * bkm_run, and skip the run everywhere when any rank is not ready - a rank that fails before its
+ * collective would otherwise leave its peers waiting for it. */
+int bkm_run_ready(bkm_handle_t h);
 
 /* ---- host-buffer convenience --------------------------------------------------------------
  * The whole job with HOST buffers in one call: create, initialize (host->device), run,

@@ -1,5 +1,6 @@
-"""GPU, 2 ranks (needs two devices): the sharded driver - contiguous point shards, per-iteration
-NCCL all-reduce of sums and sizes inside libbkm - against the single-GPU run and the oracle."""
+"""GPU, 2 ranks (needs two devices): the sharded driver - contiguous point shards, the sums and
+sizes of every iteration exchanged inside libbkm, by NCCL all-reduce or by the peer-memory
+exchange kernel - against the single-GPU run and the oracle."""
 import os
 import socket
 import sys
@@ -20,7 +21,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out_dir, name, n_total, iters):
+def _worker(rank, world, port, out_dir, name, n_total, iters, mode):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
@@ -47,6 +48,9 @@ def _worker(rank, world, port, out_dir, name, n_total, iters):
             uid.copy_(torch.frombuffer(bytearray(pkg.comm_unique_id()), dtype=torch.uint8))
         dist.broadcast(uid, 0)
         km.comm_init(uid.numpy().tobytes(), world, rank)
+        if mode == "peer":
+            assert km.peer_exchange_init(dist, torch, device="cpu")
+        assert pkg.agree(dist, torch, km.run_ready()) == pkg.OK
         km.run()
         np.save(os.path.join(out_dir, "means_%d.npy" % rank), km.getMeans())
         np.save(os.path.join(out_dir, "asg_%d.npy" % rank), km.getAssignment())
@@ -57,13 +61,14 @@ def _worker(rank, world, port, out_dir, name, n_total, iters):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("name,n_total,iters", [("c1", 50001, 4), ("c2", 40000, 3)])
-def test_two_ranks_match_single_gpu_and_oracle(tmp_path, pkg, torch_cuda, workloads, oracle_mod, name, n_total, iters):
+@pytest.mark.parametrize("name,n_total,iters,mode", [("c1", 50001, 4, "nccl"), ("c2", 40000, 3, "nccl"),
+                                                     ("c1", 50001, 4, "peer"), ("c2", 40000, 3, "peer")])
+def test_two_ranks_match_single_gpu_and_oracle(tmp_path, pkg, torch_cuda, workloads, oracle_mod, name, n_total, iters, mode):
     if torch_cuda.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), name, n_total, iters), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), name, n_total, iters, mode), nprocs=world, join=True)
     spec = dict(workloads.CONFIGS[name])
     k, d, lay = spec["k"], spec["dim"], spec["layout"]
     rows = workloads.generate_rows(spec["kind"], n_total, d, k, 5, spec.get("sigma", 0.05), spec.get("zipf"), chunk=4096)

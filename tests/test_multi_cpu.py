@@ -72,6 +72,57 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+def _agree_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        entered = []
+        # step 1: every rank is ready -> all enter the collective step
+        if pkg.agree(dist, torch, pkg.OK) == pkg.OK:
+            entered.append(1)
+            t = torch.ones(1)
+            dist.all_reduce(t)
+        # step 2: rank 1's set-up failed (its local code is an error) -> NO rank may enter
+        local = pkg.ERR_CUDA if rank == 1 else pkg.OK
+        verdict = pkg.agree(dist, torch, local)
+        if verdict == pkg.OK:
+            entered.append(2)
+        # a handle that was never initialised reports "not ready" without raising
+        km = pkg.KMeans()
+        assert km.run_ready() == pkg.ERR_STATE
+        with open(os.path.join(out_dir, "agree_%d.txt" % rank), "w") as f:
+            f.write("%s %d" % (",".join(map(str, entered)), verdict))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_failing_rank_keeps_every_rank_out_of_the_collective(tmp_path, pkg):
+    """Host-side agreement before a step that would strand the peers of a failed rank: the ranks
+    reduce their readiness codes over the launcher's process group; one error code makes every
+    rank skip the step."""
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    mp.spawn(_agree_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for rank in range(world):
+        entered, verdict = open(tmp_path / ("agree_%d.txt" % rank)).read().split()
+        assert entered == "1"                            # step 1 entered, step 2 entered by nobody
+        assert int(verdict) == pkg.ERR_CUDA              # every rank learned of the failure
+
+
+def test_peer_exchange_layout(pkg):
+    lay = pkg.peer_layout(1024, 32)
+    words = 1024 * 32 + 1024
+    assert lay["flag_words"] == 128 and lay["slot0_offset"] == 512
+    assert lay["slot_stride"] >= words * 4 and lay["slot_stride"] % 256 == 0
+    assert lay["bytes"] == lay["slot0_offset"] + 2 * lay["slot_stride"]
+
+
 def test_two_rank_protocol_matches_unsharded_oracle(tmp_path, pkg, workloads, oracle_mod):
     import torch.multiprocessing as mp
     world, port = 2, _free_port()
