@@ -178,7 +178,7 @@ def peer_layout(k, dim):
     """dict with the layout of an exchange buffer (bkm_peer_layout)."""
     arr = (ctypes.c_uint64 * 4)()
     check(lib().bkm_peer_layout(k, dim, arr))
-    return {"bytes": int(arr[0]), "flag_words": int(arr[1]), "slot0_offset": int(arr[2]), "slot_stride": int(arr[3])}
+    return {"bytes": int(arr[0]), "packets_per_sender": int(arr[1]), "senders": int(arr[2]), "slot_bytes": int(arr[3])}
 
 
 def comm_unique_id():

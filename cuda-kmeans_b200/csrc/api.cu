@@ -943,6 +943,9 @@ constexpr uint32_t PEER_MAGIC = 0x626b6d78u;
 int own_exchange_buffer(bkm_handle_t h)
 {
 	if (h->d_xbuf) return BKM_OK;
+	if ((uint64_t)h->shape.k * h->shape.dim + h->shape.k > bkm::EXCHANGE_MAX_WORDS)
+		return fail(BKM_ERR_UNSUPPORTED, "k*dim + k = %llu exceeds the %llu words the peer exchange is meant for (use the NCCL all-reduce)",
+			(unsigned long long)h->shape.k * h->shape.dim + h->shape.k, (unsigned long long)bkm::EXCHANGE_MAX_WORDS);
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	const size_t bytes = bkm::exchange_buffer_bytes(h->shape.k, h->shape.dim);
 	CUDA_TRY(cudaMalloc(&h->d_xbuf, bytes));
@@ -956,9 +959,9 @@ int bkm_peer_layout(uint32_t k, uint32_t dim, uint64_t out[4])
 {
 	if (!out || k == 0 || dim == 0) return fail(BKM_ERR_INVALID, "bad argument");
 	out[0] = bkm::exchange_buffer_bytes(k, dim);
-	out[1] = bkm::EXCHANGE_MAX_BLOCKS;                        // flag words at the start
-	out[2] = bkm::EXCHANGE_MAX_BLOCKS * sizeof(uint32_t);     // byte offset of publication slot 0
-	out[3] = bkm::exchange_slot_words(k, dim) * sizeof(uint32_t);   // bytes from slot 0 to slot 1
+	out[1] = bkm::exchange_slot_words(k, dim);                          // packets per sender
+	out[2] = bkm::EXCHANGE_MAX_RANKS;                                    // senders per slot
+	out[3] = (uint64_t)bkm::EXCHANGE_MAX_RANKS * bkm::exchange_slot_words(k, dim) * sizeof(uint64_t);   // bytes per slot
 	return BKM_OK;
 }
 

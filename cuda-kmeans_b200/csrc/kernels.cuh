@@ -54,17 +54,19 @@ void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* mea
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
 
 // ---- exchange between ranks (update.cu) ----
-// Every rank owns an exchange buffer of exchange_buffer_bytes(k, dim) that all ranks can read:
-// EXCHANGE_MAX_BLOCKS flag words, then two publication slots of (k*dim float sums | k sizes).
+// Every rank owns a receive buffer of exchange_buffer_bytes(k, dim) that all ranks can write: two
+// slots x EXCHANGE_MAX_RANKS senders x exchange_slot_words 8-byte packets (k*dim float sums, then
+// k sizes; value in the low half of a packet, iteration count in the high half).
 constexpr uint32_t EXCHANGE_MAX_RANKS = 8;
-constexpr uint32_t EXCHANGE_MAX_BLOCKS = 128;
+constexpr uint64_t EXCHANGE_MAX_WORDS = 1ull << 19;     // larger sum sets are a bandwidth problem: NCCL's job
 __host__ __device__ __forceinline__ size_t exchange_slot_words(uint32_t k, uint32_t dim) { return ((size_t)k * dim + k + 63) / 64 * 64; }
 size_t exchange_buffer_bytes(uint32_t k, uint32_t dim);
-// One kernel instead of merge + all-reduce + finalize: publishes this rank's sums and sizes in its
-// exchange buffer, waits (at most wait_limit_ns) for the peers, adds all ranks' values in rank
-// order, divides and prepares the next operands.  `peer_bases[r]` = exchange buffer of rank r as
-// addressable from this device (own buffer at [rank]); `epoch` grows by one per call on every rank.
-cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, const void* const* peer_bases, uint32_t world,
+// One kernel instead of merge + all-reduce + finalize: sends this rank's sums and sizes to every
+// rank's receive buffer, waits (at most wait_limit_ns) for all senders' packets in its own, adds
+// them in rank order, divides and prepares the next operands.  `peer_bases[r]` = receive buffer of
+// rank r as addressable from this device (own buffer at [rank]); `epoch` grows by one per call on
+// every rank, starting at 1.
+cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, void* const* peer_bases, uint32_t world,
 	uint32_t rank, uint32_t epoch, uint64_t wait_limit_ns, float* means_out, uint32_t* sizes_out, const Shape& s,
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
 

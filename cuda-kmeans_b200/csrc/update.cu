@@ -184,119 +184,116 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 // exchange between ranks + finalize, in one kernel
 // ------------------------------------------------------------------------------------------
 //
-// Every rank owns one exchange buffer that its peers can read (mapped into their address space):
-//   [ flags: EXCHANGE_MAX_BLOCKS words | two publication slots of (k*dim sums, k sizes) ]
-// Block b of every rank is responsible for the same rows.  It adds up this rank's accumulator
-// copies for its rows, writes the totals into the slot of this iteration (epoch & 1) and then sets
-// its flag to the epoch with a system-scope release.  It waits, with a time limit, until block b
-// of every peer has done the same, reads the peers' totals for its rows with plain peer loads,
-// adds all ranks' values in rank order - so every rank computes bit-identical means - divides,
-// and writes the means and the next assignment's operands as finalize_prepare_kernel does.
-// No block waits for another block of its own grid, and the grid is never larger than the number
-// of SMs, so all blocks of all ranks are resident while they wait for each other.  Two slots are
-// enough: a rank can reach the publication of iteration t+2 only after every peer has published
-// t+1, which a peer does after it has finished reading iteration t.
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
+// Every rank owns one receive buffer that its peers can write (mapped into their address space):
+//   two slots x EXCHANGE_MAX_RANKS senders x (k*dim sums, k sizes), every word an 8-byte packet
+//   (value in the low half, iteration count in the high half).
+// A rank adds up its accumulator copies and stores each total, tagged with the iteration count,
+// straight into the receive buffers of ALL ranks (its own included) with single 64-bit stores:
+// value and tag arrive together, so no separate flag and no fence is needed, and the data cross
+// NVLink once, as posted writes.  It then polls its OWN buffer, word by word, until the packets
+// of every sender carry this iteration's count, adds the values in rank order - so every rank
+// computes bit-identical means - divides, and writes the means and the next assignment's operands
+// as finalize_prepare_kernel does.  Every block sends all its words before it waits for any, and
+// the grid never exceeds the number of SMs, so no rank can wait for a word that its sender has not
+// been able to send.  Two slots (iteration count & 1) are enough: a rank can send iteration t+2
+// only after it has received every peer's t+1, which a peer sends after it has consumed t.
+// Waits are bounded; one that runs out sets STATUS_WAIT_TIMEOUT and the kernel carries on.
+__device__ __forceinline__ void st_packet(uint64_t* p, uint64_t v)
 {
-	uint32_t v;
-	asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-	return v;
+	asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+__device__ __forceinline__ uint64_t ld_packet(const uint64_t* p)
 {
-	asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p)
-{
-	float v;
-	asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-	return v;
-}
-
-__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p)
-{
-	uint32_t v;
-	asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+	uint64_t v;
+	asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
 	return v;
 }
 
 struct ExchangePeers {
-	const uint32_t* base[EXCHANGE_MAX_RANKS];   // exchange buffer of every rank (own one included), as seen from this GPU
+	uint64_t* base[EXCHANGE_MAX_RANKS];   // receive buffer of every rank (own one included), as seen from this GPU
 };
+
+// Packets of word `w` from all `world` senders, once each carries `epoch` (or the time limit has passed).
+__device__ __forceinline__ void poll_packets(const uint64_t* slot, size_t words, size_t w, uint32_t world, uint32_t epoch,
+	uint64_t wait_limit_ns, uint32_t* timed_out, uint32_t (&value)[EXCHANGE_MAX_RANKS])
+{
+	uint64_t v[EXCHANGE_MAX_RANKS];
+	#pragma unroll
+	for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) v[r] = r < world ? ld_packet(slot + (size_t)r * words + w) : 0ull;
+	uint64_t t0 = 0;
+	uint32_t spins = 0;
+	while (true) {
+		bool missing = false;
+		#pragma unroll
+		for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r)
+			if (r < world && (uint32_t)(v[r] >> 32) != epoch) { missing = true; v[r] = ld_packet(slot + (size_t)r * words + w); }
+		if (!missing) break;
+		if ((++spins & 31u) == 0) {
+			uint64_t now;
+			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+			if (t0 == 0) t0 = now;
+			else if (now - t0 > wait_limit_ns || *reinterpret_cast<volatile uint32_t*>(timed_out)) { *timed_out = 1; break; }
+		}
+	}
+	#pragma unroll
+	for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) value[r] = (uint32_t)v[r];
+}
 
 __global__ void __launch_bounds__(256) exchange_finalize_kernel(float* __restrict__ acc, uint32_t* __restrict__ counts,
 	uint32_t replicas, size_t rep_stride, ExchangePeers peers, uint32_t world, uint32_t rank, uint32_t epoch,
-	uint32_t rows_per_block, uint64_t wait_limit_ns, RowSinks o)
+	uint64_t wait_limit_ns, RowSinks o)
 {
 	__shared__ uint32_t s_timeout;
-	const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+	const uint32_t lane = threadIdx.x & 31u, wpb = blockDim.x >> 5;
+	const uint32_t gwarp = blockIdx.x * wpb + (threadIdx.x >> 5), gwarps = gridDim.x * wpb;
 	const uint32_t rows_total = rows_to_finish(o);
-	const uint32_t row0 = blockIdx.x * rows_per_block;
-	const uint32_t row1 = min(rows_total, row0 + rows_per_block);
-	const uint32_t krow1 = min(o.k, row1);                        // rows that carry sums
 	const size_t kd = (size_t)o.k * o.d;
-	const size_t slot_words = exchange_slot_words(o.k, o.d);
-	const size_t slot_off = EXCHANGE_MAX_BLOCKS + (size_t)(epoch & 1u) * slot_words;
-	uint32_t* mine = const_cast<uint32_t*>(peers.base[rank]);
-	float* pub_sums = reinterpret_cast<float*>(mine + slot_off);
-	uint32_t* pub_counts = mine + slot_off + kd;
+	const size_t words = exchange_slot_words(o.k, o.d);
+	const size_t slot_off = (size_t)(epoch & 1u) * EXCHANGE_MAX_RANKS * words;
+	const uint64_t tag = (uint64_t)epoch << 32;
 	if (threadIdx.x == 0) s_timeout = 0;
-
-	// 1. this rank's totals for the block's rows
-	for (uint32_t c = row0 + warp; c < krow1; c += wpb) {
-		for (uint32_t j = lane; j < o.d; j += 32)
-			pub_sums[(size_t)c * o.d + j] = sum_and_clear(acc + (size_t)c * o.d + j, replicas, rep_stride);
-		if (lane == 0) {
-			uint32_t cnt = 0;
-			for (uint32_t r = 0; r < replicas; ++r) { cnt += counts[c + r * rep_stride]; counts[c + r * rep_stride] = 0; }
-			pub_counts[c] = cnt;
-		}
-	}
-	__threadfence_system();
 	__syncthreads();
-	if (threadIdx.x == 0) st_release_sys(&mine[blockIdx.x], epoch);
 
-	// 2. wait for the same block of every peer (one thread per peer)
-	if (threadIdx.x < world && threadIdx.x != rank && row0 < o.k) {
-		const uint32_t* flag = peers.base[threadIdx.x] + blockIdx.x;
-		uint64_t t0 = 0;
-		uint32_t spins = 0;
-		// epochs only grow; a peer that is already one iteration ahead has left this iteration's slot intact
-		while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
-			if ((++spins & 63u) == 0) {
-				uint64_t now;
-				asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-				if (t0 == 0) t0 = now;
-				else if (now - t0 > wait_limit_ns) { s_timeout = 1; break; }
-			}
-			__nanosleep(64);
+	// 1. send this rank's totals of the block's rows to every rank
+	for (uint32_t c = gwarp; c < o.k; c += gwarps) {
+		for (uint32_t j = lane; j < o.d; j += 32) {
+			const size_t w = (size_t)c * o.d + j;
+			const uint64_t pkt = tag | __float_as_uint(sum_and_clear(acc + w, replicas, rep_stride));
+			for (uint32_t r = 0; r < world; ++r) st_packet(peers.base[r] + slot_off + (size_t)rank * words + w, pkt);
 		}
+		// sizes: the lanes share the accumulator copies, then lane r sends to rank r
+		uint32_t cnt = 0;
+		for (uint32_t r = lane; r < replicas; r += 32) { cnt += counts[c + r * rep_stride]; counts[c + r * rep_stride] = 0; }
+		#pragma unroll
+		for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+		if (lane < world) st_packet(peers.base[lane] + slot_off + (size_t)rank * words + kd + c, tag | cnt);
 	}
-	__syncthreads();
-	if (s_timeout && threadIdx.x == 0) atomicOr(&o.ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
 
-	// 3. all ranks' totals in rank order, divide, next operands
-	for (uint32_t c = row0 + warp; c < row1; c += wpb) {
+	// 2. receive all ranks' totals (from this rank's own buffer), add in rank order, divide, next operands
+	const uint64_t* slot = peers.base[rank] + slot_off;
+	for (uint32_t c = gwarp; c < rows_total; c += gwarps) {
 		if (c < o.k) {
+			uint32_t part[EXCHANGE_MAX_RANKS];
+			poll_packets(slot, words, kd + c, world, epoch, wait_limit_ns, &s_timeout, part);
 			uint32_t cnt = 0;
-			for (uint32_t r = 0; r < world; ++r) cnt += ld_relaxed_sys_u32(peers.base[r] + slot_off + kd + c);
+			#pragma unroll
+			for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) if (r < world) cnt += part[r];
 			const float divisor = (float)cnt;
 			finish_row(o, c, lane, true, cnt, [&](uint32_t j) {
-				float part[EXCHANGE_MAX_RANKS];
-				#pragma unroll
-				for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r)      // all peer loads in flight together
-					part[r] = r < world ? ld_relaxed_sys_f32(reinterpret_cast<const float*>(peers.base[r] + slot_off) + (size_t)c * o.d + j) : 0.0f;
+				uint32_t bits[EXCHANGE_MAX_RANKS];
+				poll_packets(slot, words, (size_t)c * o.d + j, world, epoch, wait_limit_ns, &s_timeout, bits);
 				float sum = 0.0f;
 				#pragma unroll
-				for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) if (r < world) sum += part[r];
+				for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) if (r < world) sum += __uint_as_float(bits[r]);
 				return cnt ? __fdiv_rn(sum, divisor) : 0.0f;
 			});
 		} else if (lane == 0) {
 			finish_padding_row(o, c);
 		}
 	}
+	__syncthreads();
+	if (threadIdx.x == 0 && s_timeout) atomicOr(&o.ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
 	if (blockIdx.x == 0 && threadIdx.x == 0) finish_control(o.ctl, o.slot);
 }
 
@@ -324,23 +321,22 @@ static uint32_t sink_rows(const Shape& s, float* cprep, const TcMeans* tc)
 
 size_t exchange_buffer_bytes(uint32_t k, uint32_t dim)
 {
-	return (EXCHANGE_MAX_BLOCKS + 2 * exchange_slot_words(k, dim)) * sizeof(uint32_t);
+	return 2 * (size_t)EXCHANGE_MAX_RANKS * exchange_slot_words(k, dim) * sizeof(uint64_t);
 }
 
-cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, const void* const* peer_bases, uint32_t world,
+cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, void* const* peer_bases, uint32_t world,
 	uint32_t rank, uint32_t epoch, uint64_t wait_limit_ns, float* means_out, uint32_t* sizes_out, const Shape& s,
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
 	if (world < 1 || world > EXCHANGE_MAX_RANKS || rank >= world) return cudaErrorInvalidValue;
 	ExchangePeers peers;
-	for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) peers.base[r] = r < world ? static_cast<const uint32_t*>(peer_bases[r]) : nullptr;
+	for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) peers.base[r] = r < world ? static_cast<uint64_t*>(peer_bases[r]) : nullptr;
 	const uint32_t rows_total = sink_rows(s, cprep, tc);
-	// the same split of the rows on every rank: it depends on the shape only, and the grid stays
-	// below the SM count of any GPU this library runs on so that all blocks are resident together
-	const uint32_t rows_per_block = (rows_total + EXCHANGE_MAX_BLOCKS - 1) / EXCHANGE_MAX_BLOCKS;
-	const uint32_t grid = (rows_total + rows_per_block - 1) / rows_per_block;
-	exchange_finalize_kernel<<<grid, 256, 0, stream>>>(acc, counts, replicas, acc_replica_stride(s.k, s.dim), peers, world, rank, epoch,
-		rows_per_block, wait_limit_ns, make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot));
+	// never more blocks than SMs: all of them are resident together (see the kernel)
+	const uint32_t wpb = 8;
+	const uint32_t grid = std::min<uint32_t>(std::max<uint32_t>((rows_total + wpb - 1) / wpb, 1), (uint32_t)current_sm_count());
+	exchange_finalize_kernel<<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, acc_replica_stride(s.k, s.dim), peers, world, rank, epoch,
+		wait_limit_ns, make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot));
 	return cudaGetLastError();
 }
 

@@ -269,12 +269,15 @@ int bkm_shard_range(uint64_t n_total, int world_size, int rank, uint64_t* begin,
 
 /* ---- exchange through peer memory (instead of the NCCL all-reduce) ---------------------------
  * The sums and sizes of one iteration are k*dim + k words: a latency problem, not a bandwidth
- * problem.  With this exchange every rank publishes its totals in a small device buffer that the
- * other ranks map into their address space, and ONE kernel per iteration publishes, waits for the
- * peers (bounded), reads their totals with ordinary loads over NVLink, adds all ranks' values in
- * rank order (bit-identical means everywhere), divides and prepares the next operands - in place
- * of merge + grouped all-reduce + finalize.  2..8 ranks; the reference has no counterpart.
- * All ranks must make the same sequence of bkm_run calls (the kernels count iterations).
+ * problem.  With this exchange every rank owns a small receive buffer that the other ranks map
+ * into their address space, and ONE kernel per iteration stores this rank's totals, each tagged
+ * with the iteration count in the same 8-byte store, into the buffers of all ranks over NVLink,
+ * polls its own buffer until every sender's packets of this iteration are there (bounded), adds
+ * all ranks' values in rank order (bit-identical means everywhere), divides and prepares the next
+ * operands - in place of merge + grouped all-reduce + finalize.  2..8 ranks, k*dim + k <= 2^19
+ * (beyond that the exchange is bandwidth-bound and stays with NCCL); no counterpart in the
+ * reference.  All ranks must make the same sequence of bkm_run calls (the packets carry the
+ * iteration count).
  *
  * Several processes: every rank calls bkm_peer_export, the launcher gathers the blobs of all
  * ranks in rank order, every rank calls bkm_peer_open with the concatenation, the launcher makes
@@ -289,11 +292,12 @@ int bkm_peer_open(bkm_handle_t h, const void* blobs, size_t blob_bytes_each, int
 int bkm_peer_buffer(bkm_handle_t h, void** base, size_t* bytes);
 int bkm_peer_attach(bkm_handle_t h, void* const* bases, int world_size, int rank);
 int bkm_peer_enable(bkm_handle_t h, int enable);
-/* Layout of an exchange buffer (for tests and for hosts that inspect it): out[0] = bytes,
- * out[1] = number of 32-bit flag words at its start (one per block of the exchange kernel, holding
- * the last iteration count that block has published), out[2] = byte offset of publication slot 0
- * (k*dim float sums in row-major cluster order, then k 32-bit sizes), out[3] = bytes from slot 0 to
- * slot 1 (iteration t uses slot t & 1, t counted from 1).  Pure host arithmetic. */
+/* Layout of a receive buffer (for tests and for hosts that inspect it): out[0] = bytes, out[1] =
+ * 8-byte packets per sender (k*dim sums in row-major cluster order, then k sizes, padded), out[2] =
+ * senders per slot, out[3] = bytes per slot.  The packet of word w from sender r in iteration t
+ * (t = 1 for the first bkm_run iteration after bkm_create) lies at byte
+ * (t & 1) * out[3] + (r * out[1] + w) * 8 and holds t in its high and the value in its low 32 bits.
+ * Pure host arithmetic. */
 int bkm_peer_layout(uint32_t k, uint32_t dim, uint64_t out[4]);
 
 /* BKM_OK when the handle could start an iteration now (initialized, kernels set up, no error

@@ -118,9 +118,9 @@ def test_failing_rank_keeps_every_rank_out_of_the_collective(tmp_path, pkg):
 def test_peer_exchange_layout(pkg):
     lay = pkg.peer_layout(1024, 32)
     words = 1024 * 32 + 1024
-    assert lay["flag_words"] == 128 and lay["slot0_offset"] == 512
-    assert lay["slot_stride"] >= words * 4 and lay["slot_stride"] % 256 == 0
-    assert lay["bytes"] == lay["slot0_offset"] + 2 * lay["slot_stride"]
+    assert lay["senders"] == 8 and lay["packets_per_sender"] >= words and lay["packets_per_sender"] % 64 == 0
+    assert lay["slot_bytes"] == lay["senders"] * lay["packets_per_sender"] * 8
+    assert lay["bytes"] == 2 * lay["slot_bytes"]
 
 
 def test_two_rank_protocol_matches_unsharded_oracle(tmp_path, pkg, workloads, oracle_mod):
