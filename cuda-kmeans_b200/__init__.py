@@ -38,7 +38,7 @@ SYMBOLS = [
     "bkm_phase_ms", "bkm_counters", "bkm_comm_unique_id", "bkm_comm_init", "bkm_shard_range",
     "bkm_kmeans_host_f32", "bkm_update_noalloc_f32", "bkm_selftest_wait_timeout", "bkm_assign_plan",
     "bkm_noalloc_check", "bkm_peer_export", "bkm_peer_open", "bkm_peer_buffer", "bkm_peer_attach", "bkm_peer_enable",
-    "bkm_peer_layout", "bkm_run_ready",
+    "bkm_peer_layout", "bkm_run_ready", "bkm_bucket_sums_f32", "bkm_probe_atomics_f32",
 ]
 
 
@@ -114,6 +114,8 @@ def lib():
     L.bkm_peer_enable.argtypes = [vp, ci]
     L.bkm_peer_layout.argtypes = [u32, u32, ctypes.POINTER(u64)]
     L.bkm_run_ready.argtypes = [vp]
+    L.bkm_bucket_sums_f32.argtypes = [vp, vp, vp, u64, u32, u32, ci, ci, vp, sz, vp]
+    L.bkm_probe_atomics_f32.argtypes = [vp, u64, u32, u32, ci, ci, u32, vp]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("bkm_last_error", "bkm_workspace_bytes"):
@@ -201,6 +203,16 @@ def update(points, assignment, means, sizes, n, k, dim, layout, layout_means, wo
            variant=UPDATE_AUTO, stream=0):
     check(lib().bkm_update_f32(points, assignment, means, sizes, n, k, dim, layout, layout_means, variant,
                                workspace, workspace_size, stream))
+
+
+def bucket_sums(points, indices, sums, n, k, dim, layout, workspace, workspace_size, variant=UPDATE_AUTO, stream=0):
+    """bkm_bucket_sums_f32: per-bucket sums (no sizes, no divide), result in the points' layout."""
+    check(lib().bkm_bucket_sums_f32(points, indices, sums, n, k, dim, layout, variant, workspace, workspace_size, stream))
+
+
+def probe_atomics(result, n, k, dim, layout, shared_cache=False, items_per_thread=1, stream=0):
+    """bkm_probe_atomics_f32: the write-only atomic-add probe."""
+    check(lib().bkm_probe_atomics_f32(result, n, k, dim, layout, 1 if shared_cache else 0, items_per_thread, stream))
 
 
 def update_noalloc(points, assignment, means, sizes, n, k, dim, layout, layout_means, stream=0):

@@ -17,6 +17,9 @@ SOURCES = ["api.cu", "assign_simt.cu", "assign_tc.cu", "assign_tc_pair.cu", "upd
 HEADERS = ["common.cuh", "kernels.cuh", "ptx.cuh", "tc_common.cuh", os.path.join("..", "..", "include", "bkm.h")]
 CLI_SRC = os.path.join(HERE, "cli", "bkm_kmeans.cpp")
 CLI = os.path.join(HERE, "bkm-kmeans")
+CLI2_SRC = os.path.join(HERE, "cli", "bkm_bucketing.cpp")
+CLI2 = os.path.join(HERE, "bkm-bucketing")
+CLI_HEADERS = [os.path.join(HERE, "cli", "reference_data.hpp")]
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -62,14 +65,17 @@ def build(force=False, verbose=False):
 
 
 def build_cli(force=False):
-    """Compiles the command-line harness (cli/bkm_kmeans.cpp) next to the library; returns its path."""
+    """Compiles the two command-line harnesses (cli/bkm_kmeans.cpp, cli/bkm_bucketing.cpp) next to the
+    library; returns the path of the k-means one."""
     lib = build()
-    if not force and os.path.exists(CLI) and os.path.getmtime(CLI) >= max(os.path.getmtime(CLI_SRC), os.path.getmtime(lib)):
-        return CLI
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(HERE, "..", "include"), CLI_SRC, "-L", HERE, "-lbkm",
-           "-Xlinker", "-rpath=$ORIGIN", "-o", CLI]
-    subprocess.check_call(cmd)
+    for src, exe in ((CLI_SRC, CLI), (CLI2_SRC, CLI2)):
+        newest = max([os.path.getmtime(src), os.path.getmtime(lib)] + [os.path.getmtime(h) for h in CLI_HEADERS])
+        if not force and os.path.exists(exe) and os.path.getmtime(exe) >= newest:
+            continue
+        cmd = [nvcc, "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(HERE, "..", "include"), src,
+               "-L", HERE, "-lbkm", "-Xlinker", "-rpath=$ORIGIN", "-o", exe]
+        subprocess.check_call(cmd)
     return CLI
 
 

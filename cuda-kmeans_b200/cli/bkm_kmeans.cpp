@@ -11,11 +11,12 @@
  * single-thread check, small sizes only).  Flags that tune the reference's own kernels
  * (--cudaBlockSize, --cudaBlockCount, --cudaSharedMemorySize, --privatizedCopies,
  * --itemsPerThread, --regsCache) are accepted and ignored; --double and --Rscript are refused.
- * The data are generated the way the reference generates them (k uniform centres, normal
- * offsets with sigma 0.025, initial means = k distinct random points; data.hpp:33-81) but not
- * from the same random stream.
+ * The inputs are the reference executable's own for the same --N --k --dim --seed --layout
+ * (reference_data.hpp restates its generator call for call); without --seed the reference draws a
+ * random seed, this harness uses 42.  --dumpInputs <file> writes them out (with --dryRun: and stops).
  */
 #include "bkm.h"
+#include "reference_data.hpp"
 
 #include <cuda_runtime.h>
 
@@ -39,7 +40,7 @@ struct Options {
 	uint64_t n = 10240;
 	uint32_t k = 128, dim = 20, iterations = 1, seed = 42;
 	bool assignment_only = false, verify = false, dry_run = false;
-	std::string algorithm = "b200", layout = "aos", layout_means;
+	std::string algorithm = "b200", layout = "aos", layout_means, dump_inputs;
 };
 
 [[noreturn]] void usage_error(const std::string& what)
@@ -47,7 +48,7 @@ struct Options {
 	std::cout << "Invalid arguments: " << what << std::endl << std::endl
 		<< "Usage: bkm-kmeans [--N n] [--k k] [--dim d] [--iterations i | --assignmentOnly] [--seed s]\n"
 		<< "                  [--algorithm b200|b200_exact|b200_simt|b200_tc|serial] [--layout aos|soa]\n"
-		<< "                  [--layoutMeans aos|soa] [--verify] [--dryRun]\n"
+		<< "                  [--layoutMeans aos|soa] [--verify] [--dryRun] [--dumpInputs file]\n"
 		<< "Integers take the suffixes k, M, G (powers of 1024)." << std::endl;
 	std::exit(1);
 }
@@ -93,6 +94,7 @@ Options parse(int argc, char** argv)
 		else if (a == "algorithm") o.algorithm = value();
 		else if (a == "layout") o.layout = value();
 		else if (a == "layoutMeans") o.layout_means = value();
+		else if (a == "dumpInputs") o.dump_inputs = value();
 		else if (a == "cudaBlockSize" || a == "cudaBlockCount" || a == "cudaSharedMemorySize" || a == "privatizedCopies" ||
 			a == "itemsPerThread" || a == "regsCache") (void)value();
 		else if (a == "double") usage_error("--double: the B200 kernels are fp32 only");
@@ -109,37 +111,24 @@ Options parse(int argc, char** argv)
 
 inline size_t at(bool soa, uint64_t i, uint32_t j, uint64_t rows, uint32_t dim) { return soa ? (size_t)j * rows + i : (size_t)i * dim + j; }
 
+// The reference executable's inputs for these arguments (k-means.cpp:205-210): see reference_data.hpp.
 void generate(const Options& o, bool soa, bool soa_means, std::vector<float>& data, std::vector<float>& means)
 {
-	std::mt19937 gen(o.seed);
-	std::uniform_real_distribution<float> uni(0.0f, 1.0f);
-	std::normal_distribution<float> noise(0.0f, 0.025f);
-	std::vector<float> centres((size_t)o.k * o.dim);
-	for (auto& c : centres) c = uni(gen);
-	std::uniform_int_distribution<uint32_t> pick(0, o.k - 1);
-	data.resize((size_t)o.n * o.dim);
-	for (uint64_t i = 0; i < o.n; ++i) {
-		const uint32_t c = pick(gen);
-		for (uint32_t j = 0; j < o.dim; ++j) data[at(soa, i, j, o.n, o.dim)] = centres[(size_t)c * o.dim + j] + noise(gen);
-	}
-	// k distinct points as initial means
-	std::vector<uint64_t> idx;
-	if (o.n <= (1ull << 24)) {
-		idx.resize(o.n);
-		std::iota(idx.begin(), idx.end(), 0ull);
-		std::shuffle(idx.begin(), idx.end(), gen);
-		idx.resize(std::min<uint64_t>(o.k, o.n));
-	} else {
-		std::uniform_int_distribution<uint64_t> any(0, o.n - 1);
-		while (idx.size() < o.k) {
-			const uint64_t c = any(gen);
-			if (std::find(idx.begin(), idx.end(), c) == idx.end()) idx.push_back(c);
-		}
-	}
-	means.assign((size_t)o.k * o.dim, 0.0f);
-	for (uint32_t m = 0; m < o.k; ++m)
-		for (uint32_t j = 0; j < o.dim; ++j)
-			means[at(soa_means, m, j, o.k, o.dim)] = data[at(soa, idx[m % idx.size()], j, o.n, o.dim)];
+	refdata::clustered_points(data, o.n, o.k, o.dim, o.seed, soa);
+	refdata::shuffled_means(data, means, o.n, o.k, o.dim, o.seed, soa, soa_means);
+}
+
+// Raw dump of the generated inputs (for comparing them with the reference's): three 64-bit
+// integers n, k, dim, then the data and the initial means as 32-bit floats in their layouts.
+void dump_inputs(const std::string& path, const Options& o, const std::vector<float>& data, const std::vector<float>& means)
+{
+	FILE* f = std::fopen(path.c_str(), "wb");
+	if (!f) throw std::runtime_error("cannot open '" + path + "' for writing");
+	const uint64_t head[3] = {o.n, o.k, o.dim};
+	bool ok = std::fwrite(head, sizeof(head), 1, f) == 1 && std::fwrite(data.data(), sizeof(float), data.size(), f) == data.size() &&
+		std::fwrite(means.data(), sizeof(float), means.size(), f) == means.size();
+	ok = std::fclose(f) == 0 && ok;
+	if (!ok) throw std::runtime_error("writing '" + path + "' failed");
 }
 
 // Single-thread Lloyd iterations with the semantics of the reference's serial algorithm
@@ -198,7 +187,7 @@ int run(const Options& o)
 	else if (o.algorithm == "b200_tc") variant = BKM_ASSIGN_TC;
 	else if (o.algorithm != "serial") throw std::runtime_error("Unkown algorithm '" + o.algorithm + "'.");
 	std::cerr << "Selected k-means algorithm: " << o.algorithm << std::endl;
-	if (o.dry_run) {
+	if (o.dry_run && o.dump_inputs.empty()) {
 		std::cout << "N=" << o.n << " k=" << o.k << " dim=" << o.dim << " iterations=" << o.iterations << " seed=" << o.seed
 			<< " layout=" << o.layout << " layoutMeans=" << o.layout_means << " assignmentOnly=" << o.assignment_only
 			<< " verify=" << o.verify << std::endl;
@@ -207,7 +196,13 @@ int run(const Options& o)
 
 	std::vector<float> data, means, got_means;
 	std::vector<uint32_t> got_asg;
+	std::cerr << "Generating input data (" << o.n << " x " << o.dim << ") ..." << std::endl;
+	std::cerr << "Seed is set to " << o.seed << std::endl;
 	generate(o, soa, soa_means, data, means);
+	if (!o.dump_inputs.empty()) {
+		dump_inputs(o.dump_inputs, o, data, means);
+		if (o.dry_run) return 0;
+	}
 	uint32_t iters = o.iterations;
 	double init_ms = 0.0, run_ms = 0.0;
 

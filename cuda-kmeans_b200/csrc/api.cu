@@ -423,6 +423,33 @@ int bkm_update_f32(const float* points, const uint32_t* assignment, float* means
 	return stateless_update(points, assignment, means, sizes, s, w, variant, device, sm, static_cast<cudaStream_t>(stream), true);
 }
 
+int bkm_bucket_sums_f32(const float* points, const uint32_t* indices, float* sums,
+	uint64_t n, uint32_t k, uint32_t dim, int layout, int variant, void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!points || !indices || !sums) return fail(BKM_ERR_INVALID, "null pointer argument");
+	bkm::Shape s; Workspace w; int device = 0, sm = 0;
+	int rc = stateless_common(n, k, dim, layout, layout, workspace, workspace_bytes, &s, &w, &device, &sm);
+	if (rc) return rc;
+	int v = 0;
+	if ((rc = resolve_update(variant, s, device, &v))) return rc;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
+	bkm::launch_update(points, indices, w.acc, w.counts, w.replicas, s, v, w.ctl, sm, st);
+	bkm::launch_finalize_sums(w.acc, w.counts, w.replicas, sums, s, w.ctl, st);
+	CUDA_TRY(cudaGetLastError());
+	return BKM_OK;
+}
+
+int bkm_probe_atomics_f32(float* result, uint64_t n, uint32_t k, uint32_t dim, int layout, int shared_cache, uint32_t items_per_thread, void* stream)
+{
+	if (!result) return fail(BKM_ERR_INVALID, "null pointer argument");
+	if (n == 0 || k == 0 || dim == 0 || items_per_thread == 0) return fail(BKM_ERR_INVALID, "n, k, dim and items_per_thread must be positive");
+	if (!layout_ok(layout)) return fail(BKM_ERR_INVALID, "unknown layout code");
+	CUDA_TRY(bkm::launch_probe_atomics(result, n, k, dim, layout == BKM_LAYOUT_SOA, shared_cache != 0, items_per_thread, static_cast<cudaStream_t>(stream)));
+	return BKM_OK;
+}
+
 int bkm_iterate_f32(const float* points, const float* means_in, float* means_out, uint32_t* sizes,
 	uint32_t* assignment, uint64_t n, uint32_t k, uint32_t dim, int layout,
 	int layout_means, int variant_assign, int variant_update,

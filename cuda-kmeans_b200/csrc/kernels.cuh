@@ -70,6 +70,12 @@ cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t repl
 	uint32_t rank, uint32_t epoch, uint64_t wait_limit_ns, float* means_out, uint32_t* sizes_out, const Shape& s,
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
 
+// acc/counts -> sums_out in the means layout of `s`, NOT divided (the bucketing study's result); clears acc and counts.
+void launch_finalize_sums(float* acc, uint32_t* counts, uint32_t replicas, float* sums_out, const Shape& s, Control* ctl, cudaStream_t stream);
+// Write-only atomic-add probe: n*dim additions of 0.1 into result[(i / dim) % k][i % dim] (result layout `soa`).
+cudaError_t launch_probe_atomics(float* result, uint64_t n, uint32_t k, uint32_t dim, int soa, bool shared_cache, uint32_t items_per_thread,
+	cudaStream_t stream);
+
 // ---- update (update.cu) ----
 // variant: BKM_UPDATE_SHARED or BKM_UPDATE_GLOBAL (already resolved).  acc/counts must be zero.
 // Returns false when the shared variant cannot hold k*dim in shared memory.

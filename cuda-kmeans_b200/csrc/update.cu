@@ -66,6 +66,7 @@ struct RowSinks {
 	float* cprep; uint32_t rs, srows;
 	float* b_hi; float* b_lo; float* cnorm; float* b_aug; const float* center; uint32_t k_pad, d_pad;
 	Control* ctl; int slot;
+	int divide;            // 0: the rows are written as sums (bucketing), 1: as means
 };
 
 // One warp finishes row c < k.  `mean_of(j)` yields coordinate j of the mean (lane-strided calls).
@@ -102,7 +103,7 @@ __device__ __forceinline__ void finish_row(const RowSinks& o, uint32_t c, uint32
 			dst[8] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);    // columns 4..7 sit 32 floats further
 		}
 		atomicMax(reinterpret_cast<int*>(&o.ctl->cmax2[o.slot]), __float_as_int(s2));
-		if (write_means) o.sizes_out[c] = cnt;
+		if (write_means && o.sizes_out) o.sizes_out[c] = cnt;
 	}
 }
 
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(256) finalize_prepare_kernel(float* __restrict
 				const float divisor = (float)cnt;
 				finish_row(o, c, lane, true, cnt, [&](uint32_t j) {
 					const float sum = sum_and_clear(acc + (size_t)c * o.d + j, replicas, rep_stride);
+					if (!o.divide) return sum;
 					return cnt ? __fdiv_rn(sum, divisor) : 0.0f;
 				});
 				__syncwarp();
@@ -308,6 +310,7 @@ static RowSinks make_sinks(float* means_out, uint32_t* sizes_out, const Shape& s
 	o.center = tc ? tc->center : nullptr;
 	o.k_pad = tc ? tc->k_pad : 0; o.d_pad = tc ? tc->d_pad : 0;
 	o.ctl = ctl; o.slot = slot;
+	o.divide = 1;
 	return o;
 }
 
@@ -341,14 +344,15 @@ cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t repl
 }
 
 static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t replicas, const float* means_in, float* means_out,
-	uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
+	uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream, bool divide = true)
 {
 	const size_t rep_stride = acc_replica_stride(s.k, s.dim);
 	const uint32_t rows_total = sink_rows(s, cprep, tc);
 	const uint32_t wpb = 8;
 	uint32_t grid = (rows_total + wpb - 1) / wpb;
 	grid = std::min<uint32_t>(std::max<uint32_t>(grid, 1), (uint32_t)current_sm_count() * 8);
-	const RowSinks o = make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot);
+	RowSinks o = make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot);
+	o.divide = divide ? 1 : 0;
 	if (finalize)
 		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, o);
 	else
@@ -365,6 +369,60 @@ void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* mea
 	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
 	launch_fp(true, acc, counts, replicas, nullptr, means_out, sizes_out, s, cprep, tc, ctl, slot, stream);
+}
+
+void launch_finalize_sums(float* acc, uint32_t* counts, uint32_t replicas, float* sums_out, const Shape& s, Control* ctl, cudaStream_t stream)
+{
+	launch_fp(true, acc, counts, replicas, nullptr, sums_out, nullptr, s, nullptr, nullptr, ctl, 1, stream, false);
+}
+
+// ------------------------------------------------------------------------------------------
+// write-only probes of the atomic-add throughput
+// ------------------------------------------------------------------------------------------
+//
+// The counterparts of atomicFakeKernel / atomicShmFakeKernel of the reference's bucketing study
+// (experimental/bucketing-cuda/bucketing-cuda/kernels/kernels.cu:455-469, 496-531): one thread per
+// input value that reads nothing and adds the constant 0.1 to bucket (i / dim) % k, dimension
+// i % dim - the cost of the reductions alone.  The shared variant keeps the first `cached` buckets
+// in shared memory and flushes them at the end of the block.
+template<bool SOA>
+__global__ void __launch_bounds__(256) probe_atomics_kernel(float* __restrict__ result, uint64_t total, uint32_t k, uint32_t d, uint32_t cached)
+{
+	extern __shared__ float cache[];
+	for (uint32_t e = threadIdx.x; e < cached * d; e += blockDim.x) cache[e] = 0.0f;
+	if (cached) __syncthreads();
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+		const uint32_t j = (uint32_t)(i % d);
+		const uint32_t target = (uint32_t)((i / d) % k);
+		if (target < cached) atomicAdd(&cache[target * d + j], 0.1f);
+		else atomicAdd(&result[at<SOA>(target, j, k, d)], 0.1f);
+	}
+	if (cached) {
+		__syncthreads();
+		for (uint32_t e = threadIdx.x; e < cached * d; e += blockDim.x) atomicAdd(&result[at<SOA>(e / d, e % d, k, d)], cache[e]);
+	}
+}
+
+cudaError_t launch_probe_atomics(float* result, uint64_t n, uint32_t k, uint32_t dim, int soa, bool shared_cache, uint32_t items_per_thread,
+	cudaStream_t stream)
+{
+	const uint64_t total = n * dim;
+	const uint64_t threads = (total + items_per_thread - 1) / items_per_thread;
+	const uint64_t blocks = std::min<uint64_t>(std::max<uint64_t>((threads + 255) / 256, 1), 0x7fffffffull);
+	uint32_t cached = 0;
+	size_t smem = 0;
+	if (shared_cache) {
+		cached = (uint32_t)std::min<size_t>(k, (96 * 1024) / ((size_t)dim * sizeof(float)));
+		smem = (size_t)cached * dim * sizeof(float);
+	}
+	if (soa) {
+		if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(probe_atomics_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+		probe_atomics_kernel<true><<<(uint32_t)blocks, 256, smem, stream>>>(result, total, k, dim, cached);
+	} else {
+		if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(probe_atomics_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+		probe_atomics_kernel<false><<<(uint32_t)blocks, 256, smem, stream>>>(result, total, k, dim, cached);
+	}
+	return cudaGetLastError();
 }
 
 // Adds replicas 1.. into replica 0 and clears them (needed before the sums leave the GPU).

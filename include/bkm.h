@@ -91,6 +91,24 @@ int bkm_update_f32(const float* points, const uint32_t* assignment, float* means
                    uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_means,
                    int variant, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The update step of the reference's separate bucketing study: sums[c][:] = SUM of the points with
+ * index c - no sizes, no divide - with `sums` in the same layout as the points (items = k) and
+ * fully overwritten.  Replaces KERNEL::run(const ProblemInstance<F>&, CudaExecParameters&) there
+ * (experimental/bucketing-cuda/bucketing-cuda/headers/kernels.cuh; runners kernels/kernels.cu:
+ * 180-186, 214-226, 254-266, 296-308, 357-372, 425-444 incl. their trailing reducePrivCopies).
+ * `variant` is a BKM_UPDATE_* code, workspace as above. */
+int bkm_bucket_sums_f32(const float* points, const uint32_t* indices, float* sums,
+                        uint64_t n, uint32_t k, uint32_t dim, int layout, int variant,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Write-only probe of the atomic-add throughput: n*dim additions of the constant 0.1, value i going
+ * to result[(i / dim) % k][i % dim], nothing read; `result` (k*dim floats in `layout`) is added to,
+ * not cleared.  shared_cache != 0 keeps the first buckets (as many as fit 96 KiB) in shared memory
+ * and flushes them per block.  Replaces AtomicFakeKernel::run / AtomicShmFakeKernel::run of the
+ * bucketing study (kernels/kernels.cu:455-486, 496-549); items_per_thread as in their runners. */
+int bkm_probe_atomics_f32(float* result, uint64_t n, uint32_t k, uint32_t dim, int layout,
+                          int shared_cache, uint32_t items_per_thread, void* stream);
+
 /* One whole iteration: means_out/sizes from means_in.  `assignment` may be NULL when the
  * caller does not want it, as in the reference's fused runners.
  * Replaces KERNEL::run(const FusedProblemInstance<F,IDX_T>&, CudaExecParameters&)

@@ -182,6 +182,48 @@ class _Ref:
         return out_asg
 
 
+class _RefData:
+    """The reference project's own input generators (headers/data.hpp, compiled)."""
+
+    def __init__(self, path):
+        lib = ctypes.CDLL(path)
+        lib.ref_make_inputs_f32.argtypes = [_int, _int, _u64, _u64, _u64, _u64, _f32p, _f32p]
+        lib.ref_make_inputs_f32.restype = _int
+        lib.ref_make_bucketing_inputs_f32.argtypes = [_u64, _u64, _u32, _u64, _f32p, _u32p]
+        lib.ref_make_bucketing_inputs_f32.restype = _int
+        self._lib = lib
+        self.path = path
+
+    def kmeans_inputs(self, n, k, d, seed, layout=AOS, layout_means=None):
+        """(data, initial means) the reference's k-means executable generates for these arguments."""
+        layout_means = layout if layout_means is None else layout_means
+        data = np.empty(n * d, dtype=np.float32)
+        means = np.empty(k * d, dtype=np.float32)
+        if self._lib.ref_make_inputs_f32(layout, layout_means, n, k, d, seed, data, means) != 0:
+            raise RuntimeError("ref_make_inputs_f32 failed")
+        return data, means
+
+    def bucketing_inputs(self, count, count_idx, k, seed):
+        """(data, indices) the reference's bucketing executable generates: `count` floats, `count_idx` indices."""
+        data = np.empty(count, dtype=np.float32)
+        idx = np.empty(count_idx, dtype=np.uint32)
+        if self._lib.ref_make_bucketing_inputs_f32(count, count_idx, k, seed, data, idx) != 0:
+            raise RuntimeError("ref_make_bucketing_inputs_f32 failed")
+        return data, idx
+
+
+_ref_data_lib = False
+
+
+def ref_data():
+    """The compiled reference generators, or None if they are neither buildable nor prebuilt here."""
+    global _ref_data_lib
+    if _ref_data_lib is False:
+        path = _b.build_ref_data()
+        _ref_data_lib = _RefData(path) if path else None
+    return _ref_data_lib
+
+
 def ref():
     """The compiled reference, or None if it is neither buildable nor prebuilt here."""
     global _ref_lib

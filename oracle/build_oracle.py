@@ -1,13 +1,15 @@
 """TEST INFRASTRUCTURE - build recipe for the CPU checkers.
 
-Builds two shared libraries:
+Builds three shared libraries:
 
 * ``oracle/libkmoracle.so`` from ``oracle/kmeans_oracle.c`` (the plain-C restatement), and
 * ``oracle/_ref/libkmref.so`` from ``oracle/ref_shim.cpp`` + the reference project's own
   headers, compiled where they lie (``-I <reference>/experimental/k-means/k-means/headers``)
   with the flags of the reference Makefile (``-O3 -std=c++14 -DNDEBUG``,
   experimental/k-means/k-means/Makefile:1-3).  Skipped when the reference checkout is absent
-  (the prebuilt file is then used if it exists).
+  (the prebuilt file is then used if it exists);
+* ``oracle/_ref/libkmrefdata.so`` from ``oracle/ref_data_shim.cpp`` + the reference's
+  ``headers/data.hpp`` (its input generators), same flags, same rule.
 
 Run ``python oracle/build_oracle.py``.  The reference checkout is looked for in the directory
 named by the environment variable ``KMEANS_REFERENCE_DIR``, else in a directory ``reference``
@@ -23,6 +25,7 @@ REF_HEADERS = os.path.join(REF_DIR, "experimental", "k-means", "k-means", "heade
 
 ORACLE_SO = os.path.join(HERE, "libkmoracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libkmref.so")
+REF_DATA_SO = os.path.join(HERE, "_ref", "libkmrefdata.so")
 
 
 def _newer(target, sources):
@@ -57,7 +60,25 @@ def build_ref(force=False):
     return REF_SO
 
 
+def build_ref_data(force=False):
+    """The reference's input generators (headers/data.hpp) behind C entry points, or None when the
+    reference checkout is absent and no prebuilt library exists.  oracle/bpp_stub stands in for the
+    one header of the external bpplib that data.hpp includes for its (unused) R-script export."""
+    src = os.path.join(HERE, "ref_data_shim.cpp")
+    stub = os.path.join(HERE, "bpp_stub")
+    if not os.path.isfile(os.path.join(REF_HEADERS, "data.hpp")):
+        return REF_DATA_SO if os.path.exists(REF_DATA_SO) else None
+    if not force and _newer(REF_DATA_SO, [src, os.path.join(stub, "system", "file.hpp")]):
+        return REF_DATA_SO
+    os.makedirs(os.path.dirname(REF_DATA_SO), exist_ok=True)
+    cmd = ["g++", "-O3", "-std=c++14", "-DNDEBUG", "-fPIC", "-shared", "-I", stub, "-I", REF_HEADERS,
+           "-o", REF_DATA_SO, src]
+    subprocess.check_call(cmd)
+    return REF_DATA_SO
+
+
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
     print(build_ref(force))
+    print(build_ref_data(force))
