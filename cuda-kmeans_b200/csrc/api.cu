@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 
@@ -110,7 +111,7 @@ struct Workspace {
 	uint32_t* counts = nullptr;    // k sizes (directly behind the sums of each replica)
 	uint32_t replicas = 1;
 	size_t acc_bytes = 0;
-	float* cprep = nullptr;        // CUDA-core rows
+	bkm::SimtMeans sm{};           // CUDA-core rows (+ the centre vector, shared with the tensor-core operands)
 	size_t cprep_bytes = 0;
 	bkm::TcMeans tm{};
 	size_t tm_bytes = 0;           // b_hi + b_lo
@@ -141,7 +142,7 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 	w.acc = reinterpret_cast<float*>(accp);
 	w.counts = accp ? reinterpret_cast<uint32_t*>(accp + kd * sizeof(float)) : nullptr;
 	w.cprep_bytes = (size_t)bkm::simt_rows(k) * bkm::simt_row_stride(dim) * sizeof(float);
-	w.cprep = reinterpret_cast<float*>(take(w.cprep_bytes));
+	w.sm.rows = reinterpret_cast<float*>(take(w.cprep_bytes));
 	w.tm.k_pad = bkm::tc_kpad(k);
 	w.tm.d_pad = bkm::tc_dpad(dim);
 	const size_t plane = (size_t)w.tm.k_pad * w.tm.d_pad * sizeof(float);
@@ -151,6 +152,7 @@ Workspace carve(char* base, uint64_t n, uint32_t k, uint32_t dim, bool with_tc_p
 	w.tm.cnorm = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * sizeof(float)));
 	w.tm.b_aug = reinterpret_cast<float*>(take((size_t)w.tm.k_pad * 8 * sizeof(float)));
 	w.tm.center = reinterpret_cast<float*>(take((size_t)w.tm.d_pad * sizeof(float)));
+	w.sm.center = w.tm.center;
 	w.flag_list = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
 	w.asg_scratch = reinterpret_cast<uint32_t*>(take(n * sizeof(uint32_t)));
 	if (with_tc_points) {
@@ -251,7 +253,7 @@ int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* 
 		return BKM_OK;
 	}
 	if (variant == BKM_ASSIGN_SIMT) {
-		CUDA_TRY(bkm::launch_assign_simt(pts, w.cprep, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream));
+		CUDA_TRY(bkm::launch_assign_simt(pts, w.sm, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream));
 	} else {
 		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream, fused));
 	}
@@ -294,7 +296,7 @@ struct bkm_handle_s {
 	int peer_world = 0;
 	bool peer_on = false;
 	uint32_t epoch = 0;                            // iterations exchanged so far (the same on every rank)
-	uint64_t exchange_wait_ns = 10000000000ull;
+	uint64_t exchange_wait_ns = 2000000000ull;
 	// phase events of the most recent run
 	static constexpr int EV_RING = 256, EV_PER = 6;
 	cudaEvent_t ev[EV_RING][EV_PER] = {};
@@ -360,31 +362,80 @@ static int stateless_common(uint64_t n, uint32_t k, uint32_t dim, int layout, in
 	return device_sm_count(*device, sm_count);
 }
 
+// Bytes of the control block that every stateless call clears: status, flag count and the two
+// max |c|^2 slots.  last_flag_count and xmax2 behind them survive (xmax2 belongs to the points).
+constexpr size_t CONTROL_CLEAR_BYTES = 16;
+
+// Tensor maps are a function of the workspace address and the shape, so the stateless calls keep
+// the few most recent plans instead of encoding six maps per call.
+struct PlanSlot {
+	void* ws = nullptr; uint64_t n = 0; uint32_t k = 0, dim = 0; int soa = 0, soa_means = 0, device = -1;
+	bkm::TcPlan* plan = nullptr; uint64_t stamp = 0;
+};
+static std::mutex g_plan_mutex;
+static PlanSlot g_plan_slots[8];
+static uint64_t g_plan_clock = 0;
+
+static bkm::TcPlan* cached_plan(const bkm::Shape& s, const Workspace& w, int device, const char** err)
+{
+	std::lock_guard<std::mutex> lock(g_plan_mutex);
+	PlanSlot* victim = &g_plan_slots[0];
+	for (PlanSlot& p : g_plan_slots) {
+		if (p.plan && p.ws == (void*)w.ctl && p.n == s.n && p.k == s.k && p.dim == s.dim && p.soa == s.soa && p.soa_means == s.soa_means && p.device == device) {
+			p.stamp = ++g_plan_clock;
+			return p.plan;
+		}
+		if (p.stamp < victim->stamp) victim = &p;
+	}
+	bkm::TcPlan* plan = bkm::tc_plan_create(s, w.tp, w.tm, device, err);
+	if (!plan) return nullptr;
+	if (victim->plan) bkm::tc_plan_destroy(victim->plan);
+	victim->ws = (void*)w.ctl; victim->n = s.n; victim->k = s.k; victim->dim = s.dim; victim->soa = s.soa; victim->soa_means = s.soa_means;
+	victim->device = device; victim->plan = plan; victim->stamp = ++g_plan_clock;
+	return plan;
+}
+
+// One assignment pass on a caller's workspace.  The operands derived from the (immutable) points -
+// centre vector, largest norm, tf32 planes - stay in the workspace; a call that finds the same
+// point set there (address, shape and a fingerprint of a sample of the values) skips them.
+// With `fa` given and the shape allowing it, the pass also accumulates the update sums (*fused).
 static int stateless_assign(const float* points, const float* means, uint32_t* assignment, const bkm::Shape& s,
-	const Workspace& w, int variant, int device, int sm_count, cudaStream_t st)
+	const Workspace& w, int variant, int device, int sm_count, cudaStream_t st, const bkm::FusedAcc* fa = nullptr, bool* fused_out = nullptr)
 {
 	int v = 0;
 	int rc = resolve_assign(variant, s, &v);
 	if (rc) return rc;
-	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	if (fused_out) *fused_out = false;
+	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, CONTROL_CLEAR_BYTES, st));
 	CUDA_TRY(cudaMemsetAsync(w.split_scratch, 0, bkm::list_split_scratch_bytes(), st));
 	bkm::TcPlan* plan = nullptr;
-	if (v == BKM_ASSIGN_SIMT) {
-		CUDA_TRY(cudaMemsetAsync(w.cprep, 0, w.cprep_bytes, st));
-		bkm::launch_prepare_means(means, s, w.cprep, nullptr, w.ctl, 0, st);
-	} else if (v == BKM_ASSIGN_TC) {
-		CUDA_TRY(cudaMemsetAsync(w.tm.b_hi, 0, w.tm_bytes, st));
-		CUDA_TRY(bkm::launch_compute_center(points, s, w.tm.center, st));
-		bkm::launch_prepare_means(means, s, nullptr, &w.tm, w.ctl, 0, st);
-		CUDA_TRY(bkm::launch_split_points(points, s, w.tp, w.tm.center, w.ctl, st));
-		const char* err = nullptr;
-		plan = bkm::tc_plan_create(s, w.tp, w.tm, device, &err);
-		if (!plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
+	bool fused = false;
+	if (v == BKM_ASSIGN_SIMT || v == BKM_ASSIGN_TC) {
+		bkm::PointsKey* key = reinterpret_cast<bkm::PointsKey*>(reinterpret_cast<char*>(w.ctl) + bkm::POINTS_KEY_OFFSET);
+		const uint32_t* skip = &key->valid;
+		CUDA_TRY(cudaMemsetAsync(&key->fp_new, 0, sizeof(key->fp_new), st));
+		CUDA_TRY(bkm::launch_points_fingerprint(points, s.n * s.dim, key, sm_count, st));
+		CUDA_TRY(bkm::launch_points_key_decide(key, points, s, v, w.ctl, st));
+		CUDA_TRY(bkm::launch_compute_center(points, s, w.tm.center, st, skip));
+		if (v == BKM_ASSIGN_SIMT) {
+			CUDA_TRY(cudaMemsetAsync(w.sm.rows, 0, w.cprep_bytes, st));
+			CUDA_TRY(bkm::launch_points_norm_max(points, s, w.tm.center, w.ctl, sm_count, st, skip));
+			bkm::launch_prepare_means(means, s, &w.sm, nullptr, w.ctl, 0, st);
+		} else {
+			CUDA_TRY(cudaMemsetAsync(w.tm.b_hi, 0, w.tm_bytes, st));
+			bkm::launch_prepare_means(means, s, nullptr, &w.tm, w.ctl, 0, st);
+			CUDA_TRY(bkm::launch_split_points(points, s, w.tp, w.tm.center, w.ctl, st, skip));
+			const char* err = nullptr;
+			plan = cached_plan(s, w, device, &err);
+			if (!plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
+			bkm::tc_plan_allow_pair(plan, true);
+			fused = fa != nullptr && bkm::tc_plan_can_fuse(plan, *fa) && (size_t)s.dim * sizeof(float) * 4 <= 120 * 1024;
+			if (fused) CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
+		}
 	}
 	CUDA_TRY(cudaGetLastError());
-	rc = enqueue_assign(v, points, means, assignment, s, w, 0, plan, 1.0f, sm_count, st, nullptr);
-	if (plan) bkm::tc_plan_destroy(plan);   // tensor maps are copied into the launch parameters
-	return rc;
+	if (fused_out) *fused_out = fused;
+	return enqueue_assign(v, points, means, assignment, s, w, 0, plan, 1.0f, sm_count, st, nullptr, fused ? fa : nullptr);
 }
 
 static int stateless_update(const float* points, const uint32_t* assignment, float* means, uint32_t* sizes,
@@ -393,7 +444,7 @@ static int stateless_update(const float* points, const uint32_t* assignment, flo
 	int v = 0;
 	int rc = resolve_update(variant, s, device, &v);
 	if (rc) return rc;
-	if (clear_ctl) CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	if (clear_ctl) CUDA_TRY(cudaMemsetAsync(w.ctl, 0, CONTROL_CLEAR_BYTES, st));
 	CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
 	bkm::launch_update(points, assignment, w.acc, w.counts, w.replicas, s, v, w.ctl, sm_count, st);
 	bkm::launch_finalize(w.acc, w.counts, w.replicas, means, sizes, s, nullptr, nullptr, w.ctl, 1, st);
@@ -433,7 +484,7 @@ int bkm_bucket_sums_f32(const float* points, const uint32_t* indices, float* sum
 	int v = 0;
 	if ((rc = resolve_update(variant, s, device, &v))) return rc;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
-	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, sizeof(bkm::Control), st));
+	CUDA_TRY(cudaMemsetAsync(w.ctl, 0, CONTROL_CLEAR_BYTES, st));
 	CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
 	bkm::launch_update(points, indices, w.acc, w.counts, w.replicas, s, v, w.ctl, sm, st);
 	bkm::launch_finalize_sums(w.acc, w.counts, w.replicas, sums, s, w.ctl, st);
@@ -462,8 +513,19 @@ int bkm_iterate_f32(const float* points, const float* means_in, float* means_out
 	if (rc) return rc;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	uint32_t* asg = assignment ? assignment : w.asg_scratch;
-	rc = stateless_assign(points, means_in, asg, s, w, variant_assign, device, sm, st);
+	// Where the assignment pass can accumulate the sums itself (the shapes of the CTA-pair kernel with
+	// an update that would otherwise be the row-wise kernel) the points are read once.
+	int vu = 0;
+	if ((rc = resolve_update(variant_update, s, device, &vu))) return rc;
+	bkm::FusedAcc fa{w.acc, w.counts, w.replicas, bkm::acc_replica_stride(k, dim), w.tm.center};
+	bool fused = false;
+	rc = stateless_assign(points, means_in, asg, s, w, variant_assign, device, sm, st, vu == BKM_UPDATE_ROWS ? &fa : nullptr, &fused);
 	if (rc) return rc;
+	if (fused) {
+		bkm::launch_finalize(w.acc, w.counts, w.replicas, means_out, sizes, s, nullptr, nullptr, w.ctl, 1, st);
+		CUDA_TRY(cudaGetLastError());
+		return BKM_OK;
+	}
 	return stateless_update(points, asg, means_out, sizes, s, w, variant_update, device, sm, st, false);
 }
 
@@ -628,6 +690,10 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 	CUDA_TRY(cudaMemsetAsync(h->d_ws, 0, (size_t)(reinterpret_cast<char*>(h->ws.flag_list) - h->d_ws), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_asg, 0, s.n * sizeof(uint32_t), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_sizes, 0, (size_t)s.k * sizeof(uint32_t), st));
+	if (h->assign_variant == BKM_ASSIGN_SIMT) {
+		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
+		CUDA_TRY(bkm::launch_points_norm_max(h->d_points, s, h->ws.tm.center, h->ws.ctl, h->sm_count, st));
+	}
 	if (h->assign_variant == BKM_ASSIGN_TC) {
 		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
 		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, st));
@@ -638,7 +704,7 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 		bkm::tc_plan_allow_pair(h->plan, h->tc_pair);
 	}
 	bkm::launch_prepare_means(h->d_means[0], s,
-		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+		h->assign_variant == BKM_ASSIGN_SIMT ? &h->ws.sm : nullptr,
 		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot, st);
 	CUDA_TRY(cudaGetLastError());
 	CUDA_TRY(cudaStreamSynchronize(st));
@@ -676,7 +742,7 @@ int bkm_set_means(bkm_handle_t h, const float* host_means)
 	// the preparation fills cmax2[slot] with atomicMax, so the slot starts from zero
 	CUDA_TRY(cudaMemsetAsync(&h->ws.ctl->cmax2[h->slot], 0, sizeof(float), st));
 	bkm::launch_prepare_means(h->d_means[h->cur], s,
-		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+		h->assign_variant == BKM_ASSIGN_SIMT ? &h->ws.sm : nullptr,
 		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot, st);
 	CUDA_TRY(cudaGetLastError());
 	CUDA_TRY(cudaStreamSynchronize(st));
@@ -713,7 +779,7 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 		++h->epoch;
 		CUDA_TRY(bkm::launch_exchange_finalize(h->ws.acc, h->ws.counts, h->ws.replicas, h->peer_base, (uint32_t)h->peer_world,
 			(uint32_t)h->rank, h->epoch, h->exchange_wait_ns, h->d_means[next], h->d_sizes, s,
-			h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+			h->assign_variant == BKM_ASSIGN_SIMT ? &h->ws.sm : nullptr,
 			h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st));
 		if (ev) { CUDA_TRY(cudaEventRecord(ev[4], st)); CUDA_TRY(cudaEventRecord(ev[5], st)); }
 		h->cur = next;
@@ -731,7 +797,7 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 	}
 	if (ev) CUDA_TRY(cudaEventRecord(ev[4], st));
 	bkm::launch_finalize(h->ws.acc, h->ws.counts, h->comm ? 1u : h->ws.replicas, h->d_means[next], h->d_sizes, s,
-		h->assign_variant == BKM_ASSIGN_SIMT ? h->ws.cprep : nullptr,
+		h->assign_variant == BKM_ASSIGN_SIMT ? &h->ws.sm : nullptr,
 		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot ^ 1, st);
 	if (ev) CUDA_TRY(cudaEventRecord(ev[5], st));
 	CUDA_TRY(cudaGetLastError());

@@ -6,16 +6,14 @@
 //    for the queued near-ties of the fast passes.  Replaces baseAssignmentKernel
 //    (kernels/kernels.cu:182-199 of the reference) and follows serial.hpp:21-35.
 //
-//  * assign_simt_kernel<D>: small-d fast pass.  The means are staged into shared memory with a
-//    bulk TMA copy; every thread keeps P points in registers and evaluates sum (x-c)^2 with a
-//    subtract and a fused multiply-add per dimension (the difference form keeps its relative
-//    accuracy for tight clusters far from the origin, where |c|^2 - 2 x.c would cancel),
-//    tracking the best and second-best value.  A point whose two best values are closer than
-//    the rounding band (of this pass, of the reference's own sum, and of its square root) is
-//    queued for the exact kernel, so the final result equals the reference's for every point.  Covers the shape range of cachedFixedAssignmentKernel
-//    (kernels/kernels.cu:218-273) and cachedAllMeansAssignmentKernel (:330-374).
+//  * assign_simt_kernel<D, SOA, P>: small-d fast pass (see the comment above the kernel): the
+//    means staged into shared memory with a bulk TMA copy, P points per thread in registers,
+//    |c|^2 - 2 x.c on the FMA pipe, arg-min on integer keys, near-ties queued for the exact
+//    kernel.  Covers the shape range of cachedFixedAssignmentKernel (kernels/kernels.cu:218-273)
+//    and cachedAllMeansAssignmentKernel (:330-374).
 #include "kernels.cuh"
 #include "ptx.cuh"
+#include "keys.cuh"
 
 #include <cmath>
 
@@ -327,6 +325,56 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	}
 }
 
+// The same arithmetic with one THREAD per queued point and all means in shared memory, for mean sets
+// of a few hundred floats (the regime of the small-d fast pass): there a block per four points
+// leaves most of its threads without a mean, while a thread walks the whole set in microseconds.
+constexpr uint32_t LIST_SMALL_MAX_FLOATS = 2048;
+
+template<int D, bool SOA, bool SOAM>
+__global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const float* __restrict__ pts, const float* __restrict__ means,
+	uint32_t* __restrict__ asg, uint64_t n, uint32_t k, const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
+{
+	__shared__ float sm[LIST_SMALL_MAX_FLOATS];          // [mean][dimension]
+	for (uint32_t e = threadIdx.x; e < k * D; e += blockDim.x) {
+		const uint32_t m = e / D, j = e - m * D;
+		sm[e] = means[at<SOAM>(m, j, k, D)];
+	}
+	__syncthreads();
+	uint64_t total = *list_count;
+	if (total > n) total = n;
+	for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (uint64_t)gridDim.x * blockDim.x) {
+		const uint64_t i = list[w];
+		float x[D];
+		#pragma unroll
+		for (int j = 0; j < D; ++j) x[j] = pts[at<SOA>(i, j, n, D)];
+		float best = 0.0f;
+		uint32_t bidx = 0;
+		for (uint32_t m = 0; m < k; ++m) {
+			float sum = 0.0f;
+			#pragma unroll
+			for (int j = 0; j < D; ++j) {
+				const float diff = __fsub_rn(x[j], sm[m * D + j]);
+				sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+			}
+			const float dist = __fsqrt_rn(sum);
+			if (m == 0 || dist < best) { best = dist; bidx = m; }
+		}
+		asg[i] = bidx;
+	}
+}
+
+template<int D>
+static cudaError_t launch_list_small(const float* pts, const float* means, uint32_t* asg, const Shape& s,
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
+{
+	const uint32_t grid = (uint32_t)sm_count * 4;
+	if (s.soa && s.soa_means) assign_exact_list_small_kernel<D, true, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
+	else if (s.soa) assign_exact_list_small_kernel<D, true, false><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
+	else if (s.soa_means) assign_exact_list_small_kernel<D, false, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
+	else assign_exact_list_small_kernel<D, false, false><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
+	return cudaGetLastError();
+}
+
 size_t list_split_scratch_bytes()
 {
 	return (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB * sizeof(unsigned long long) + (size_t)LIST_SPLIT_MAX_BLOCKS * sizeof(uint32_t);
@@ -338,6 +386,18 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 	unsigned long long* split_keys = reinterpret_cast<unsigned long long*>(split_scratch);
 	uint32_t* split_arrive = split_scratch ? reinterpret_cast<uint32_t*>(split_keys + (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB) : nullptr;
 	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
+	if (list != nullptr && fix == nullptr && s.dim <= 8 && (uint64_t)s.k * s.dim <= LIST_SMALL_MAX_FLOATS) {
+		switch (s.dim) {
+		case 1: return launch_list_small<1>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 2: return launch_list_small<2>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 3: return launch_list_small<3>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 4: return launch_list_small<4>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 5: return launch_list_small<5>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 6: return launch_list_small<6>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 7: return launch_list_small<7>(pts, means, asg, s, list, list_count, sm_count, stream);
+		default: return launch_list_small<8>(pts, means, asg, s, list, list_count, sm_count, stream);
+		}
+	}
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
 		const size_t points_bytes = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float);
 		size_t lsmem = points_bytes + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
@@ -385,27 +445,46 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 // ------------------------------------------------------------------------------------------
 // small-d fast pass
 // ------------------------------------------------------------------------------------------
+//
+// Every thread keeps P points in registers (shifted by the common centre vector) and walks the
+// means in chunks of 32.  A mean's row in shared memory is [ |c|^2 + C, -2c_0 .. -2c_{D-1} ], so a
+// point's value |c|^2 - 2 x.c + C costs D fused multiply-adds per mean; the constant C (from the
+// largest |x|^2 and |c|^2, see make_key_consts) puts all values into one binade, where their bit
+// patterns order like the values.  The 32 values of a chunk become integer keys (bits * M + column)
+// and are reduced to the smallest and second smallest with plain integer minima (chunk_update):
+// about 1.75 integer instructions per point and mean where a (best, second, index) tournament on
+// floats takes five, and D instead of 2D arithmetic instructions.  The form cancels where the
+// difference form does not, so a point whose best and second-best keys are closer than the
+// rounding band of the pass (and of the reference's own sum and square root) is queued for the
+// exact kernel; the final assignment is the reference's for every point.
 
 constexpr int SIMT_THREADS = 256;
-constexpr int SIMT_P = 2;            // points per thread
-constexpr int SIMT_TILE_ROWS = 1024; // means per shared-memory tile
+constexpr int SIMT_TILE_ROWS = 1024; // means per shared-memory tile (a multiple of the 32-mean chunk)
 
-template<int D, bool SOA>
+template<int D, bool SOA, int P>
 __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* __restrict__ pts,
-	const float* __restrict__ cprep, uint32_t* __restrict__ asg, uint64_t n, uint32_t rows,
-	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef, int vec_ok)
+	const float* __restrict__ cprep, const float* __restrict__ center, uint32_t* __restrict__ asg, uint64_t n, uint32_t rows,
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_ulps, int vec_ok)
 {
 	constexpr int RS = (D + 1 + 3) / 4 * 4;
-	constexpr int P = SIMT_P;
 	extern __shared__ __align__(128) float tile[];
 	__shared__ __align__(8) uint64_t bar;
+	__shared__ uint32_t flag_bufs[SIMT_THREADS / 32][FLAG_BUFFER];     // per warp: near-ties on their way to the list
+	uint32_t* flag_buf = flag_bufs[threadIdx.x >> 5];
+	uint32_t flag_cnt = 0;
 
 	const uint32_t tid = threadIdx.x;
 	const uint32_t ntiles = (rows + SIMT_TILE_ROWS - 1) / SIMT_TILE_ROWS;
 	const uint64_t per_block = (uint64_t)SIMT_THREADS * P;
 	const uint64_t nblocks = (n + per_block - 1) / per_block;
+	const KeyConsts kc = make_key_consts(ctl->xmax2, ctl->cmax2[slot]);
+	const uint32_t key_mult = kc.key_mult, key_base = kc.key_base, key_magic = kc.key_magic;
+	const float pad_value = kc.pow2 * (2.0f - 1.0f / 32.0f);     // padding rows: above every real value, inside [P, 2P)
 	uint32_t phase = 0;
 	bool ok = true;
+	float cen[D];
+	#pragma unroll
+	for (int j = 0; j < D; ++j) cen[j] = center[j];
 
 	if (tid == 0) {
 		ptx::mbar_init(&bar, 1);
@@ -413,33 +492,46 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 	}
 	__syncthreads();
 
-	if (ntiles == 1) {
+	// Brings tile t of the prepared means into shared memory and adds the offset constant to its
+	// |c|^2 column (padding rows, marked by +inf there, get the top of the value band).
+	auto load_tile = [&](uint32_t t) -> uint32_t {
+		uint32_t trows = rows - t * SIMT_TILE_ROWS;
+		if (trows > SIMT_TILE_ROWS) trows = SIMT_TILE_ROWS;
 		if (tid == 0) {
-			uint32_t bytes = rows * RS * (uint32_t)sizeof(float);
+			const uint32_t bytes = trows * RS * (uint32_t)sizeof(float);
 			ptx::mbar_arrive_expect_tx(&bar, bytes);
-			ptx::bulk_g2s(tile, cprep, bytes, &bar);
+			ptx::bulk_g2s(tile, cprep + (size_t)t * SIMT_TILE_ROWS * RS, bytes, &bar);
 		}
-		ok = ptx::mbar_wait(&bar, phase);
+		ok = ptx::mbar_wait(&bar, phase) && ok;
 		phase ^= 1;
-	}
+		for (uint32_t r = tid; r < trows; r += SIMT_THREADS) {
+			const float c2 = tile[(size_t)r * RS];
+			tile[(size_t)r * RS] = c2 > 3.0e38f ? pad_value : c2 + kc.offset_c;
+		}
+		__syncthreads();
+		return trows;
+	};
 
-	for (uint64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
-		float x[P][D];
-		uint64_t idx[P];
+	uint32_t trows0 = 0;
+	if (ntiles == 1) trows0 = load_tile(0);
+
+	// The points of a block of work, as they lie in memory (slots behind the last point read as the
+	// centre).  The next block's points are fetched while the current block is being evaluated.
+	float raw[P][D];
+	auto load_points = [&](uint64_t blk) {
 		const uint64_t base = blk * per_block;
 		if (SOA) {
 			#pragma unroll
 			for (int p = 0; p < P; ++p) {
-				idx[p] = base + (uint64_t)p * SIMT_THREADS + tid;
+				const uint64_t i = base + (uint64_t)p * SIMT_THREADS + tid;
 				#pragma unroll
-				for (int j = 0; j < D; ++j) x[p][j] = idx[p] < n ? pts[(size_t)j * n + idx[p]] : 0.0f;
+				for (int j = 0; j < D; ++j) raw[p][j] = i < n ? pts[(size_t)j * n + i] : cen[j];
 			}
 		} else {
-			#pragma unroll
-			for (int p = 0; p < P; ++p) idx[p] = base + (uint64_t)tid * P + p;
-			if ((P * D) % 4 == 0 && vec_ok && idx[P - 1] < n) {
+			const uint64_t i0 = base + (uint64_t)tid * P;
+			if ((P * D) % 4 == 0 && vec_ok && i0 + P - 1 < n) {
 				// 128-bit loads: the thread's P points are P*D consecutive floats
-				const float4* src = reinterpret_cast<const float4*>(pts + (size_t)idx[0] * D);
+				const float4* src = reinterpret_cast<const float4*>(pts + (size_t)i0 * D);
 				float buf[P * D];
 				#pragma unroll
 				for (int q = 0; q < (P * D) / 4; ++q) {
@@ -449,69 +541,79 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 				#pragma unroll
 				for (int p = 0; p < P; ++p)
 					#pragma unroll
-					for (int j = 0; j < D; ++j) x[p][j] = buf[p * D + j];
+					for (int j = 0; j < D; ++j) raw[p][j] = buf[p * D + j];
 			} else {
 				#pragma unroll
 				for (int p = 0; p < P; ++p)
 					#pragma unroll
-					for (int j = 0; j < D; ++j) x[p][j] = idx[p] < n ? pts[(size_t)idx[p] * D + j] : 0.0f;
+					for (int j = 0; j < D; ++j) raw[p][j] = i0 + p < n ? pts[(size_t)(i0 + p) * D + j] : cen[j];
 			}
 		}
-		float best[P], second[P];
-		uint32_t bidx[P];
+	};
+	if (blockIdx.x < nblocks) load_points(blockIdx.x);
+
+	for (uint64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+		float x[P][D];
+		uint64_t idx[P];
+		const uint64_t base = blk * per_block;
 		#pragma unroll
 		for (int p = 0; p < P; ++p) {
-			best[p] = INFINITY; second[p] = INFINITY; bidx[p] = 0;
+			idx[p] = SOA ? base + (uint64_t)p * SIMT_THREADS + tid : base + (uint64_t)tid * P + p;
+			#pragma unroll
+			for (int j = 0; j < D; ++j) x[p][j] = raw[p][j] - cen[j];
 		}
+		if (blk + gridDim.x < nblocks) load_points(blk + gridDim.x);
+
+		uint32_t best[P], second[P], bchunk[P];
+		#pragma unroll
+		for (int p = 0; p < P; ++p) { best[p] = 0xFFFFFFFFu; second[p] = 0xFFFFFFFFu; bchunk[p] = 0; }
 
 		for (uint32_t t = 0; t < ntiles; ++t) {
-			uint32_t trows = rows - t * SIMT_TILE_ROWS;
-			if (trows > SIMT_TILE_ROWS) trows = SIMT_TILE_ROWS;
+			uint32_t trows = trows0;
 			if (ntiles > 1) {
 				__syncthreads();   // everyone is done reading the previous tile
-				if (tid == 0) {
-					uint32_t bytes = trows * RS * (uint32_t)sizeof(float);
-					ptx::mbar_arrive_expect_tx(&bar, bytes);
-					ptx::bulk_g2s(tile, cprep + (size_t)t * SIMT_TILE_ROWS * RS, bytes, &bar);
-				}
-				ok = ptx::mbar_wait(&bar, phase) && ok;
-				phase ^= 1;
+				trows = load_tile(t);
 			}
-			const uint32_t mbase = t * SIMT_TILE_ROWS;
-			#pragma unroll 4
-			for (uint32_t m = 0; m < trows; ++m) {
-				float r[RS];
-				const float4* row = reinterpret_cast<const float4*>(tile + (size_t)m * RS);
+			const uint32_t chunk_base = t * (SIMT_TILE_ROWS / 32);
+			#pragma unroll 1
+			for (uint32_t ch = 0; ch < trows / 32; ++ch) {
+				uint32_t v[P][32];
+				const float4* rowp = reinterpret_cast<const float4*>(tile + (size_t)ch * 32 * RS);
 				#pragma unroll
-				for (int q = 0; q < RS / 4; ++q) {
-					float4 v = row[q];
-					r[4 * q + 0] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
-				}
-				#pragma unroll
-				for (int p = 0; p < P; ++p) {
-					float v = r[0];
+				for (int m = 0; m < 32; ++m) {
+					float r[RS];
 					#pragma unroll
-					for (int j = 0; j < D; ++j) { const float diff = x[p][j] - r[1 + j]; v = fmaf(diff, diff, v); }
-					const bool lt = v < best[p];
-					second[p] = fminf(second[p], fmaxf(best[p], v));
-					best[p] = fminf(best[p], v);
-					bidx[p] = lt ? (mbase + m) : bidx[p];
+					for (int q = 0; q < RS / 4; ++q) {
+						const float4 w = rowp[m * (RS / 4) + q];
+						r[4 * q + 0] = w.x; r[4 * q + 1] = w.y; r[4 * q + 2] = w.z; r[4 * q + 3] = w.w;
+					}
+					#pragma unroll
+					for (int p = 0; p < P; ++p) {
+						float val = r[0];
+						#pragma unroll
+						for (int j = 0; j < D; ++j) val = fmaf(x[p][j], r[1 + j], val);
+						v[p][m] = __float_as_uint(val);
+					}
 				}
+				#pragma unroll
+				for (int p = 0; p < P; ++p) chunk_update<false>(v[p], key_mult, chunk_base + ch, 32, best[p], second[p], bchunk[p]);
 			}
 		}
 
 		#pragma unroll
 		for (int p = 0; p < P; ++p) {
+			bool flag = false;
 			if (idx[p] < n) {
-				asg[idx[p]] = bidx[p];
-				if (second[p] - best[p] <= margin_coef * second[p]) {
-					uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-					if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)idx[p];
-					else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
-				}
+				// key - key_base = M * mantissa + column
+				const uint32_t bm = div_key(best[p] - key_base, key_magic);
+				asg[idx[p]] = bchunk[p] * 32u + ((best[p] - key_base) - bm * key_mult);
+				const float gap = second[p] == 0xFFFFFFFFu ? INFINITY : (float)(div_key(second[p] - key_base, key_magic) - bm);
+				flag = gap <= margin_ulps;
 			}
+			buffered_append(flag, (uint32_t)idx[p], flag_buf, flag_cnt, ctl, flag_list, n);
 		}
 	}
+	flush_flag_buffer(flag_buf, flag_cnt, ctl, flag_list, n);
 	if (!ok && tid == 0) atomicOr(&ctl->status, (uint32_t)STATUS_WAIT_TIMEOUT);
 }
 
@@ -520,22 +622,25 @@ bool assign_simt_supported(const Shape& s)
 	return s.dim >= 1 && s.dim <= 8 && s.n < (1ull << 32);
 }
 
-template<int D>
-static cudaError_t launch_simt_d(const float* pts, const float* cprep, uint32_t* asg, const Shape& s,
+template<int D, int P>
+static cudaError_t launch_simt_d(const float* pts, const float* cprep, const float* center, uint32_t* asg, const Shape& s,
 	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream)
 {
 	constexpr int RS = (D + 1 + 3) / 4 * 4;
 	const uint32_t rows = simt_rows(s.k);
 	const uint32_t trows = rows < (uint32_t)SIMT_TILE_ROWS ? rows : (uint32_t)SIMT_TILE_ROWS;
 	const size_t smem = (size_t)trows * RS * sizeof(float);
-	const uint64_t per_block = (uint64_t)SIMT_THREADS * SIMT_P;
+	const uint64_t per_block = (uint64_t)SIMT_THREADS * P;
 	const uint64_t nblocks = (s.n + per_block - 1) / per_block;
 	// persistent grid: a whole number of resident blocks per SM
 	int per_sm = 1;
-	const float margin_coef = margin_scale * (float)(2 * D + 8) * 1.1920929e-07f;    // (2D+8) * 2^-23, relative
+	// Near-tie band in value spacings (ulps of the common binade): roundings of this pass (|c|^2,
+	// the offset, D fused steps, the centring of both operands), doubled for a difference of two
+	// values, plus the reference's own sum and the collapse of its square root.
+	const float margin_ulps = margin_scale * (float)(4 * D + 16);
 	const int vec_ok = ((reinterpret_cast<uintptr_t>(pts) & 15u) == 0) ? 1 : 0;
 #define BKM_LAUNCH_SIMT(SOA) do { \
-		auto kern = assign_simt_kernel<D, SOA>; \
+		auto kern = assign_simt_kernel<D, SOA, P>; \
 		cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
 		if (e != cudaSuccess) return e; \
 		e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, SIMT_THREADS, smem); \
@@ -543,27 +648,58 @@ static cudaError_t launch_simt_d(const float* pts, const float* cprep, uint32_t*
 		if (per_sm < 1) per_sm = 1; \
 		uint32_t grid = (uint32_t)std::min<uint64_t>(nblocks, (uint64_t)sm_count * per_sm); \
 		if (grid < 1) grid = 1; \
-		kern<<<grid, SIMT_THREADS, smem, stream>>>(pts, cprep, asg, s.n, rows, ctl, slot, flag_list, margin_coef, vec_ok); \
+		kern<<<grid, SIMT_THREADS, smem, stream>>>(pts, cprep, center, asg, s.n, rows, ctl, slot, flag_list, margin_ulps, vec_ok); \
 	} while (0)
 	if (s.soa) BKM_LAUNCH_SIMT(true); else BKM_LAUNCH_SIMT(false);
 #undef BKM_LAUNCH_SIMT
 	return cudaGetLastError();
 }
 
-cudaError_t launch_assign_simt(const float* pts, const float* cprep, uint32_t* asg, const Shape& s,
+cudaError_t launch_assign_simt(const float* pts, const SimtMeans& sm, uint32_t* asg, const Shape& s,
 	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream)
 {
 	switch (s.dim) {
-	case 1: return launch_simt_d<1>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 2: return launch_simt_d<2>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 3: return launch_simt_d<3>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 4: return launch_simt_d<4>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 5: return launch_simt_d<5>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 6: return launch_simt_d<6>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 7: return launch_simt_d<7>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 8: return launch_simt_d<8>(pts, cprep, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 1: return launch_simt_d<1, 4>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 2: return launch_simt_d<2, 4>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 3: return launch_simt_d<3, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 4: return launch_simt_d<4, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 5: return launch_simt_d<5, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 6: return launch_simt_d<6, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 7: return launch_simt_d<7, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 8: return launch_simt_d<8, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
 	default: return cudaErrorInvalidValue;
 	}
+}
+
+// max over the points of |x - center|^2 -> ctl->xmax2 (which must start at zero): one pass over
+// the points, done once per data set (the key constants of the fast pass need the bound).
+template<bool SOA>
+__global__ void __launch_bounds__(256) points_norm_max_kernel(const float* __restrict__ pts, const float* __restrict__ center,
+	uint64_t n, uint32_t d, Control* __restrict__ ctl, const uint32_t* __restrict__ skip_if)
+{
+	if (skip_if && *skip_if) return;
+	float local = 0.0f;
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+		float s = 0.0f;
+		for (uint32_t j = 0; j < d; ++j) {
+			const float v = pts[at<SOA>(i, j, n, d)] - center[j];
+			s = fmaf(v, v, s);
+		}
+		local = fmaxf(local, s);
+	}
+	#pragma unroll
+	for (int off = 16; off > 0; off >>= 1) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, off));
+	// non-negative floats order like their bit patterns
+	if ((threadIdx.x & 31u) == 0) atomicMax(reinterpret_cast<int*>(&ctl->xmax2), __float_as_int(local));
+}
+
+cudaError_t launch_points_norm_max(const float* pts, const Shape& s, const float* center, Control* ctl, int sm_count, cudaStream_t stream,
+	const uint32_t* skip_if)
+{
+	const uint32_t grid = (uint32_t)std::min<uint64_t>((s.n + 255) / 256, (uint64_t)sm_count * 8);
+	if (s.soa) points_norm_max_kernel<true><<<grid, 256, 0, stream>>>(pts, center, s.n, s.dim, ctl, skip_if);
+	else points_norm_max_kernel<false><<<grid, 256, 0, stream>>>(pts, center, s.n, s.dim, ctl, skip_if);
+	return cudaGetLastError();
 }
 
 } // namespace bkm

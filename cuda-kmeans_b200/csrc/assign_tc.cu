@@ -70,7 +70,8 @@ constexpr uint32_t SM_BAUG_OFF = SM_B_OFF + TC_NB * B_STAGE_BYTES; // |c|^2 K st
 constexpr uint32_t SM_AAUG_OFF = SM_BAUG_OFF + TC_NB * AUG_BYTES;  // constant ones tile (128 rows)
 constexpr uint32_t SM_MERGE_OFF = SM_AAUG_OFF + TC_MTILE * 8 * 4;
 constexpr uint32_t MERGE_BYTES = 2 * 3 * TC_MA * TC_MTILE * 4;   // (best, second, chunk) of the upper column half, two slots
-constexpr uint32_t SM_BAR_OFF = SM_MERGE_OFF + MERGE_BYTES;
+constexpr uint32_t SM_FLAG_OFF = SM_MERGE_OFF + MERGE_BYTES;       // per epilogue warp: near-ties on their way to the list
+constexpr uint32_t SM_BAR_OFF = SM_FLAG_OFF + TC_EPI_WARPS * FLAG_BUFFER * 4;
 constexpr uint32_t SM_TOTAL = SM_BAR_OFF + 256;
 constexpr uint32_t SM_ALLOC = SM_TOTAL + 1024;                   // slack for 1024-byte alignment
 
@@ -91,8 +92,9 @@ bool assign_tc_supported(const Shape& s)
 template<bool SOA>
 __global__ void __launch_bounds__(256) split_points_kernel(const float* __restrict__ pts, float* __restrict__ a_hi,
 	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t n_pad, uint32_t d, uint32_t d_pad,
-	const float* __restrict__ center, Control* __restrict__ ctl)
+	const float* __restrict__ center, Control* __restrict__ ctl, const uint32_t* __restrict__ skip_if)
 {
+	if (skip_if && *skip_if) return;
 	float local_max = 0.0f;
 	__shared__ float tile[32][33];
 	const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
@@ -144,8 +146,9 @@ __global__ void __launch_bounds__(256) split_points_kernel(const float* __restri
 // One block per dimension: mean of that coordinate over at most 65536 evenly spaced points.
 template<bool SOA>
 __global__ void __launch_bounds__(256) compute_center_kernel(const float* __restrict__ pts, float* __restrict__ center,
-	uint64_t n, uint32_t d)
+	uint64_t n, uint32_t d, const uint32_t* __restrict__ skip_if)
 {
+	if (skip_if && *skip_if) return;
 	__shared__ float part[256];
 	const uint32_t j = blockIdx.x;
 	const uint64_t samples = n < 65536 ? n : 65536;
@@ -164,19 +167,20 @@ __global__ void __launch_bounds__(256) compute_center_kernel(const float* __rest
 	if (threadIdx.x == 0) center[j] = part[0] / (float)samples;
 }
 
-cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream)
+cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream, const uint32_t* skip_if)
 {
-	if (s.soa) compute_center_kernel<true><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim);
-	else compute_center_kernel<false><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim);
+	if (s.soa) compute_center_kernel<true><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim, skip_if);
+	else compute_center_kernel<false><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim, skip_if);
 	return cudaGetLastError();
 }
 
-cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream)
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream,
+	const uint32_t* skip_if)
 {
 	const uint64_t groups = tp.n_pad / 32;
 	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, (uint64_t)current_sm_count() * 16);
-	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl);
-	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl);
+	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl, skip_if);
+	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl, skip_if);
 	return cudaGetLastError();
 }
 
@@ -222,21 +226,17 @@ static_assert(sizeof(TcBars) <= 256, "barrier block too large");
 static_assert(SM_ALLOC <= 227 * 1024, "shared memory budget exceeded");
 static_assert(KL_AUG_OFF + 2 * AUG_BYTES <= SM_AAUG_OFF, "K-loop stages overlap the constant tile");
 
-// The end of a point's arg-min: decode the winning key (key - key_base = M * mantissa + column),
-// write the assignment, and queue the point for the exact kernel when best and second are closer
-// than `margin`.
-__device__ __forceinline__ void finish_point(uint32_t best, uint32_t second, uint32_t bchunk, uint32_t key_base, uint32_t key_mult, uint32_t key_magic,
-	float ulp, float margin, uint64_t p, uint64_t n, uint32_t* __restrict__ asg, Control* __restrict__ ctl, uint32_t* __restrict__ flag_list)
+// The end of a point's arg-min: decode the winning key (key - key_base = M * mantissa + column) and
+// write the assignment.  Returns whether best and second are closer than `margin`, i.e. whether
+// the point has to be queued for the exact kernel (the caller appends, a warp at a time).
+__device__ __forceinline__ bool finish_point(uint32_t best, uint32_t second, uint32_t bchunk, uint32_t key_base, uint32_t key_mult, uint32_t key_magic,
+	float ulp, float margin, uint64_t p, uint32_t* __restrict__ asg)
 {
 	const uint32_t bm = div_key(best - key_base, key_magic);
 	asg[p] = bchunk * 32u + ((best - key_base) - bm * key_mult);
 	// keys are (mantissa * M + column): the difference of the quotients counts value spacings
 	const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)(div_key(second - key_base, key_magic) - bm) * ulp;
-	if (gap <= margin) {
-		const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-		if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
-		else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
-	}
+	return gap <= margin;
 }
 
 // Combines the partial arg-min results of the CTAs that shared the mean tiles of a point block.
@@ -247,20 +247,27 @@ __global__ void __launch_bounds__(256) merge_partials_kernel(const uint32_t* __r
 	const float c2max = ctl->cmax2[slot];
 	const KeyConsts kc = make_key_consts(ctl->xmax2, c2max);
 	const float ulp = kc.pow2 * 1.1920929e-07f;
-	for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (uint64_t)gridDim.x * blockDim.x) {
-		uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
-		for (uint32_t part = 0; part < parts; ++part) {
-			const uint32_t* src = partial + (size_t)part * 3 * partial_stride + p;
-			const uint32_t ob = src[0], os = src[partial_stride], oc = src[2 * partial_stride];
-			second = umin3(second, os, max(best, ob));
-			bchunk = ob < best ? oc : bchunk;
-			best = min(best, ob);
+	const uint64_t n32 = (n + 31) & ~(uint64_t)31;      // whole warps walk the loop together (the append is a warp operation)
+	for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n32; p += (uint64_t)gridDim.x * blockDim.x) {
+		bool flag = false;
+		if (p < n) {
+			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
+			for (uint32_t part = 0; part < parts; ++part) {
+				const uint32_t* src = partial + (size_t)part * 3 * partial_stride + p;
+				const uint32_t ob = src[0], os = src[partial_stride], oc = src[2 * partial_stride];
+				second = umin3(second, os, max(best, ob));
+				bchunk = ob < best ? oc : bchunk;
+				best = min(best, ob);
+			}
+			flag = finish_point(best, second, bchunk, kc.key_base, kc.key_mult, kc.key_magic, ulp, margin_coef * (xnorm[p] + c2max) + 4.0f * ulp, p, asg);
 		}
-		finish_point(best, second, bchunk, kc.key_base, kc.key_mult, kc.key_magic, ulp, margin_coef * (xnorm[p] + c2max) + 4.0f * ulp,
-			p, n, asg, ctl, flag_list);
+		append_flagged(flag, (uint32_t)p, ctl, flag_list, n);
 	}
 }
 
+// FULL: k is a whole number of mean tiles, so no accumulator column is padding and the epilogue runs
+// without its masked path.
+template<bool FULL>
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
 	const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -348,7 +355,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						{
 							const uint32_t as = aug_count & 1u, au = aug_count >> 1;
-							ok = wait_or_abort(&bars->aug_empty[as], (au & 1u) ^ 1u, abort_flag);
+							ok = wait_or_abort<400>(&bars->aug_empty[as], (au & 1u) ^ 1u, abort_flag);
 							if (!ok) break;
 							ptx::mbar_arrive_expect_tx(&bars->aug_full[as], nt_cols * 8 * 4);
 							ptx::bulk_g2s(smem + KL_AUG_OFF + as * AUG_BYTES, b_aug + (size_t)j * nt_cols * 8, nt_cols * 8 * 4, &bars->aug_full[as]);
@@ -356,7 +363,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						}
 						for (uint32_t kc = 0; kc < kchunks; ++kc) {
 							const uint32_t s = b_count % KL_STAGES, u = b_count / KL_STAGES;
-							ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
+							ok = wait_or_abort<400>(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
 							if (!ok) break;
 							uint8_t* dst = smem + s * KL_STAGE_BYTES;
 							const int32_t row = (int32_t)(blk * TC_MA * TC_MTILE), x = (int32_t)(kc * KL_KW);
@@ -380,7 +387,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 					for (uint32_t i = 0; i < tiles && ok; ++i, ++g) {
 						const uint32_t buf = g % n_abuf, u = g / n_abuf;
-						ok = wait_or_abort(&bars->a_empty[buf], (u & 1u) ^ 1u, abort_flag);
+						ok = wait_or_abort<400>(&bars->a_empty[buf], (u & 1u) ^ 1u, abort_flag);
 						if (!ok) break;
 						uint8_t* dst = smem + SM_A_OFF + buf * a_tile;
 						const int32_t row = (int32_t)((blk * TC_MA + i) * TC_MTILE);
@@ -392,7 +399,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						if (b_resident && b_loaded) break;
 						const uint32_t s = b_count % TC_NB, u = b_count / TC_NB;
-						ok = wait_or_abort(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
+						ok = wait_or_abort<400>(&bars->b_empty[s], (u & 1u) ^ 1u, abort_flag);
 						if (!ok) break;
 						uint8_t* dst = smem + sm_b_off + s * b_stage;
 						const uint32_t aug_bytes = nt_cols * 8 * 4;
@@ -436,19 +443,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					const uint32_t tiles = min(TC_MA, n_tiles - blk * TC_MA);
 					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						for (uint32_t i = 0; i < tiles && ok; ++i) {
-							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
+							ok = wait_or_abort<200>(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
 							++acc_use[i];
 						}
 						if (!ok) break;
 						ptx::tc_fence_after();
 						for (uint32_t kc = 0; kc < kchunks; ++kc) {
 							const uint32_t s = b_count % KL_STAGES, u = b_count / KL_STAGES;
-							ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
+							ok = wait_or_abort<100>(&bars->b_full[s], u & 1u, abort_flag);
 							if (!ok) break;
 							const bool last = kc == kchunks - 1;
 							const uint32_t as = aug_count & 1u;
 							if (last) {
-								ok = wait_or_abort(&bars->aug_full[as], (aug_count >> 1) & 1u, abort_flag);
+								ok = wait_or_abort<100>(&bars->aug_full[as], (aug_count >> 1) & 1u, abort_flag);
 								if (!ok) break;
 							}
 							ptx::tc_fence_after();
@@ -490,7 +497,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					for (uint32_t j = j_begin; j < j_end && ok; ++j) {
 						const uint32_t s = b_resident ? 0u : b_count % TC_NB, u = b_count / TC_NB;
 						if (!(b_resident && b_ready)) {
-							ok = wait_or_abort(&bars->b_full[s], u & 1u, abort_flag);
+							ok = wait_or_abort<100>(&bars->b_full[s], u & 1u, abort_flag);
 							if (!ok) break;
 							b_ready = true;
 						}
@@ -500,10 +507,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						for (uint32_t i = 0; i < tiles; ++i) {
 							const uint32_t buf = (g + i) % n_abuf, ua = (g + i) / n_abuf;
 							if (j == j_begin) {
-								ok = wait_or_abort(&bars->a_full[buf], ua & 1u, abort_flag);
+								ok = wait_or_abort<100>(&bars->a_full[buf], ua & 1u, abort_flag);
 								if (!ok) break;
 							}
-							ok = wait_or_abort(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
+							ok = wait_or_abort<200>(&bars->acc_empty[i], (acc_use[i] & 1u) ^ 1u, abort_flag);
 							if (!ok) break;
 							ptx::tc_fence_after();
 							const uint32_t a_addr = ptx::smem_u32(smem + SM_A_OFF + buf * a_tile);
@@ -554,6 +561,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 		const uint32_t first_chunk = half * per_half;
 		const uint32_t nchunks = first_chunk >= chunks_total ? 0u : min(per_half, chunks_total - first_chunk);
 		const uint32_t bar_id = 1u + i * 4u + q;   // named barrier of the two warps that share these rows
+		uint32_t* flag_buf = reinterpret_cast<uint32_t*>(smem + SM_FLAG_OFF) + (warp - 2) * FLAG_BUFFER;
+		uint32_t flag_cnt = 0;
 		uint32_t acc_use = 0, blk_count = 0;
 		bool ok = true;
 		for (uint32_t blk = bid; blk < nblocks; blk += nbid, ++blk_count) {
@@ -567,7 +576,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				if (ok) {
 					// one lane polls the barrier, the warp follows
 					bool w = true;
-					if (lane == 0) w = wait_or_abort(&bars->acc_full[i], acc_use & 1u, abort_flag);
+					if (lane == 0) w = wait_or_abort<100>(&bars->acc_full[i], acc_use & 1u, abort_flag);
 					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
 				}
 				++acc_use;
@@ -594,8 +603,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						}
 						// columns at or behind k are padding
 						const uint32_t col0 = chunk0 * 32u;
-						const uint32_t left = k > col0 ? k - col0 : 0u;
-						if (left >= 64 || (!two && left >= 32)) {
+						const uint32_t left = FULL ? 64u : (k > col0 ? k - col0 : 0u);
+						if (FULL || left >= 64 || (!two && left >= 32)) {
 							chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
 							if (two) chunk_update<false>(v1, key_mult, chunk0 + 1, 32, best, second, bchunk);
 						} else {
@@ -616,6 +625,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 				mg[row] = best; mg[TC_MTILE + row] = second; mg[2 * TC_MTILE + row] = bchunk;
 			}
 			asm volatile("bar.sync %0, 64;" :: "r"(bar_id) : "memory");
+			bool flag = false;
 			if (half == 0 && p < n && ok) {
 				const uint32_t ob = mg[row], os = mg[TC_MTILE + row], oc = mg[2 * TC_MTILE + row];
 				second = umin3(second, os, max(best, ob));
@@ -626,11 +636,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 					uint32_t* dst = partial + (size_t)jpart * 3 * partial_stride + p;
 					dst[0] = best; dst[partial_stride] = second; dst[2 * partial_stride] = bchunk;
 				} else {
-					finish_point(best, second, bchunk, key_base, key_mult, key_magic, ulp, margin_coef * (xn + c2max) + 4.0f * ulp,
-						p, n, asg, ctl, flag_list);
+					flag = finish_point(best, second, bchunk, key_base, key_mult, key_magic, ulp, margin_coef * (xn + c2max) + 4.0f * ulp, p, asg);
 				}
 			}
+			if (half == 0 && partial == nullptr) buffered_append(flag, (uint32_t)p, flag_buf, flag_cnt, ctl, flag_list, n);
 		}
+		flush_flag_buffer(flag_buf, flag_cnt, ctl, flag_list, n);
 	}
 
 	ptx::tc_fence_before();
@@ -737,7 +748,8 @@ TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, in
 		delete p;
 		return nullptr;
 	}
-	if (cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM_ALLOC) != cudaSuccess) {
+	if (cudaFuncSetAttribute(assign_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM_ALLOC) != cudaSuccess ||
+		cudaFuncSetAttribute(assign_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM_ALLOC) != cudaSuccess) {
 		cudaGetLastError();
 		if (err) *err = e_attr;
 		delete p;
@@ -807,7 +819,8 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim);
 	const uint32_t jsplit = plan_jsplit(p);
 	const uint32_t grid_j = jsplit * std::min<uint32_t>(nblocks, (uint32_t)p->sm_count / jsplit);
-	assign_tc_kernel<<<jsplit > 1 ? grid_j : grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
+	auto kern = p->s.k == p->tm.k_pad ? assign_tc_kernel<true> : assign_tc_kernel<false>;
+	kern<<<jsplit > 1 ? grid_j : grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
 		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,
 		ctl, slot, flag_list, margin_coef, jsplit, jsplit > 1 ? p->tp.partial : nullptr, p->tp.n_pad);
 	if (jsplit > 1) {

@@ -359,6 +359,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				asm volatile("bar.arrive %0, 128;" :: "r"(merge_bar) : "memory");
 			} else {
 				asm volatile("bar.sync %0, 128;" :: "r"(merge_bar) : "memory");
+				bool flag = false;
 				if (p < n && ok) {
 					#pragma unroll
 					for (uint32_t o = 0; o < 3; ++o) {
@@ -374,12 +375,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 					asg[p] = mine;
 					const float gap = second == 0xFFFFFFFFu ? INFINITY : (float)(div_key(second - key_base, key_magic) - bm) * ulp;
 					const float margin = margin_coef * (xn + c2max) + 4.0f * ulp;
-					if (gap <= margin) {
-						const uint32_t pos = atomicAdd(&ctl->flag_count, 1u);
-						if ((uint64_t)pos < n) flag_list[pos] = (uint32_t)p;
-						else atomicOr(&ctl->status, (uint32_t)STATUS_LIST_OVERFLOW);
-					}
+					flag = gap <= margin;
 				}
+				append_flagged(flag, (uint32_t)p, ctl, flag_list, n);
 			}
 			if (fuse_acc != nullptr) {
 				// Update sums: the final clusters go to shared memory; the reductions themselves are

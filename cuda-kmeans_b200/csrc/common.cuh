@@ -26,6 +26,17 @@ struct Control {
 	uint32_t pad[2];
 };
 
+// What a stateless workspace remembers about the point set its one-off operands (centre vector,
+// largest norm, tf32 planes) were derived from; it lives at byte 64 of the workspace.  `valid` is
+// rewritten by every call: 1 when the points of this call are the remembered ones.
+struct PointsKey {
+	unsigned long long fp_new;   // fingerprint of the points of the current call (accumulated, then compared)
+	unsigned long long fp_old;   // fingerprint the operands in the workspace belong to
+	unsigned long long ptr, n;
+	uint32_t dim, layout, variant, valid;
+};
+constexpr size_t POINTS_KEY_OFFSET = 64;
+
 // Element offset of (item, dim) in a buffer of `items` vectors of `dims` floats.
 // AoS: item*dims + dim, SoA: dim*items + item (the reference's layout policies, ALIGN = 1).
 template<bool SOA>
@@ -43,12 +54,12 @@ __host__ __device__ __forceinline__ uint32_t round_up(uint32_t x, uint32_t m) { 
 __host__ __device__ __forceinline__ uint64_t round_up64(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
 // Row stride (floats) of the prepared means used by the CUDA-core assignment:
-// [ t, c_0 ... c_{d-1}, 0-padding ] rounded to a multiple of 4 floats, where the additive term t
-// is 0 for a real mean and +inf for a padding row.
+// [ |c - centre|^2, -2(c_0 - centre_0) ... -2(c_{d-1} - centre_{d-1}), 0-padding ] rounded to a
+// multiple of 4 floats; a padding row holds +inf in its first slot (and zeros).
 __host__ __device__ __forceinline__ uint32_t simt_row_stride(uint32_t dim) { return round_up(dim + 1, 4); }
 
-// Rows of the prepared means: k rounded to a multiple of 4.
-__host__ __device__ __forceinline__ uint32_t simt_rows(uint32_t k) { return round_up(k, 4); }
+// Rows of the prepared means: k rounded to the 32-mean chunk the kernel walks.
+__host__ __device__ __forceinline__ uint32_t simt_rows(uint32_t k) { return round_up(k, 32); }
 
 // Geometry of the tensor-core operands: K (dimension) padded to 32 floats (one 128-byte
 // swizzle row), point rows padded to 128, mean rows padded to 16.

@@ -26,6 +26,12 @@ struct TcMeans {
 	uint32_t d_pad;  // dim rounded up to TC_KCHUNK
 };
 
+// Operand of the CUDA-core fast pass derived from the means (rewritten every iteration).
+struct SimtMeans {
+	float* rows;          // [simt_rows(k)][simt_row_stride(dim)]: |c - centre|^2, -2(c - centre), zero padding; +inf marks a padding row
+	const float* center;  // [dim] the vector subtracted from points and means alike (as for the tensor-core operands)
+};
+
 // Operands derived from the points (written once per initialize).
 struct TcPoints {
 	float* a_hi;     // [n_pad][d_pad]
@@ -43,15 +49,15 @@ int current_sm_count();
 // ---- means preparation + divide (update.cu) ----
 
 // means (given layout) -> CUDA-core rows and/or tensor-core operands; cmax2 -> ctl slot.
-// `cprep` / `tc` may be null.  Also clears flag_count.
+// `sm` / `tc` may be null.  Also clears flag_count.
 // `slot` is the cmax2 slot to fill (it must be zero on entry).
-void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,
+void launch_prepare_means(const float* means, const Shape& s, const SimtMeans* sm, const TcMeans* tc,
 	Control* ctl, int slot, cudaStream_t stream);
 
 // acc/counts -> means_out (given layout), sizes_out, then the same preparation as above from
 // the fresh means; clears acc, counts and flag_count for the next iteration.
 void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* means_out, uint32_t* sizes_out, const Shape& s,
-	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
+	const SimtMeans* sm, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
 
 // ---- exchange between ranks (update.cu) ----
 // Every rank owns a receive buffer of exchange_buffer_bytes(k, dim) that all ranks can write: two
@@ -68,13 +74,21 @@ size_t exchange_buffer_bytes(uint32_t k, uint32_t dim);
 // every rank, starting at 1.
 cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, void* const* peer_bases, uint32_t world,
 	uint32_t rank, uint32_t epoch, uint64_t wait_limit_ns, float* means_out, uint32_t* sizes_out, const Shape& s,
-	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
+	const SimtMeans* sm, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream);
 
 // acc/counts -> sums_out in the means layout of `s`, NOT divided (the bucketing study's result); clears acc and counts.
 void launch_finalize_sums(float* acc, uint32_t* counts, uint32_t replicas, float* sums_out, const Shape& s, Control* ctl, cudaStream_t stream);
 // Write-only atomic-add probe: n*dim additions of 0.1 into result[(i / dim) % k][i % dim] (result layout `soa`).
 cudaError_t launch_probe_atomics(float* result, uint64_t n, uint32_t k, uint32_t dim, int soa, bool shared_cache, uint32_t items_per_thread,
 	cudaStream_t stream);
+
+// ---- recognising the point set of a stateless call (update.cu) ----
+// Adds a fingerprint of the points (every 16th 128-byte line and the last one; order-independent
+// sum of mixed (value, position) words) to key->fp_new, which must be zero on entry.
+cudaError_t launch_points_fingerprint(const float* pts, uint64_t words, PointsKey* key, int sm_count, cudaStream_t stream);
+// Sets key->valid (same address, shape, variant and fingerprint as remembered) and remembers the
+// current call's; when the points are new it also clears ctl->xmax2, which their preprocessing refills.
+cudaError_t launch_points_key_decide(PointsKey* key, const float* pts, const Shape& s, int variant, Control* ctl, cudaStream_t stream);
 
 // ---- update (update.cu) ----
 // variant: BKM_UPDATE_SHARED or BKM_UPDATE_GLOBAL (already resolved).  acc/counts must be zero.
@@ -107,17 +121,22 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 
 // Small-d fast pass (dim <= 8): approximate distances, near-ties appended to flag_list.
 bool assign_simt_supported(const Shape& s);
-cudaError_t launch_assign_simt(const float* pts, const float* cprep, uint32_t* asg, const Shape& s,
+// max |x - center|^2 over the points -> ctl->xmax2 (zero on entry); once per data set.
+// `skip_if` (optional, device): the kernels of the one-off preprocessing return at once when *skip_if != 0.
+cudaError_t launch_points_norm_max(const float* pts, const Shape& s, const float* center, Control* ctl, int sm_count, cudaStream_t stream,
+	const uint32_t* skip_if = nullptr);
+cudaError_t launch_assign_simt(const float* pts, const SimtMeans& sm, uint32_t* asg, const Shape& s,
 	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream);
 
 // ---- assignment on tensor cores (assign_tc.cu) ----
 bool assign_tc_supported(const Shape& s);
 uint32_t tc_kpad(uint32_t k);
 // One-off split of the points into tf32 hi/lo K-major planes + |x|^2.
-cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream);
+cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream,
+	const uint32_t* skip_if = nullptr);
 // center[j] = mean of dimension j over a strided sample of the points (any vector would do; the
 // sample mean keeps the shifted norms small).
-cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream);
+cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream, const uint32_t* skip_if = nullptr);
 // Opaque per-handle state (tensor maps).  Created once the operand buffers exist.
 struct TcPlan;
 TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err);

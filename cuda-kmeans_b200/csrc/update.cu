@@ -81,7 +81,7 @@ __device__ __forceinline__ void finish_row(const RowSinks& o, uint32_t c, uint32
 		const float shifted = o.center ? mean - o.center[j] : mean;
 		s2 = fmaf(shifted, shifted, s2);
 		const float b = -2.0f * shifted;
-		if (o.cprep) o.cprep[(size_t)c * o.rs + 1 + j] = mean;
+		if (o.cprep) o.cprep[(size_t)c * o.rs + 1 + j] = b;
 		if (o.b_hi) {
 			const float hi = tf32_rna(b);
 			const float lo = tf32_rna(b - hi);
@@ -93,7 +93,7 @@ __device__ __forceinline__ void finish_row(const RowSinks& o, uint32_t c, uint32
 	for (int off = 16; off > 0; off >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, off);
 	__syncwarp();
 	if (lane == 0) {
-		if (o.cprep) o.cprep[(size_t)c * o.rs] = 0.0f;
+		if (o.cprep) o.cprep[(size_t)c * o.rs] = s2;
 		if (o.cnorm) o.cnorm[c] = s2;
 		if (o.b_aug) {
 			const float hi = tf32_rna(s2);
@@ -254,8 +254,11 @@ __global__ void __launch_bounds__(256) exchange_finalize_kernel(float* __restric
 	const size_t words = exchange_slot_words(o.k, o.d);
 	const size_t slot_off = (size_t)(epoch & 1u) * EXCHANGE_MAX_RANKS * words;
 	const uint64_t tag = (uint64_t)epoch << 32;
-	if (threadIdx.x == 0) s_timeout = 0;
+	// once a wait has run out (status word still set: the host has not looked yet), later iterations
+	// of the same run do not wait again
+	if (threadIdx.x == 0) s_timeout = (o.ctl->status & (uint32_t)STATUS_WAIT_TIMEOUT) ? 1u : 0u;
 	__syncthreads();
+	if (s_timeout) wait_limit_ns = 0;
 
 	// 1. send this rank's totals of the block's rows to every rank
 	for (uint32_t c = gwarp; c < o.k; c += gwarps) {
@@ -299,25 +302,25 @@ __global__ void __launch_bounds__(256) exchange_finalize_kernel(float* __restric
 	if (blockIdx.x == 0 && threadIdx.x == 0) finish_control(o.ctl, o.slot);
 }
 
-static RowSinks make_sinks(float* means_out, uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot)
+static RowSinks make_sinks(float* means_out, uint32_t* sizes_out, const Shape& s, const SimtMeans* sm, const TcMeans* tc, Control* ctl, int slot)
 {
 	RowSinks o;
 	o.means_out = means_out; o.sizes_out = sizes_out;
 	o.k = s.k; o.d = s.dim; o.soa_means = s.soa_means;
-	o.cprep = cprep; o.rs = simt_row_stride(s.dim); o.srows = simt_rows(s.k);
+	o.cprep = sm ? sm->rows : nullptr; o.rs = simt_row_stride(s.dim); o.srows = simt_rows(s.k);
 	o.b_hi = tc ? tc->b_hi : nullptr; o.b_lo = tc ? tc->b_lo : nullptr;
 	o.cnorm = tc ? tc->cnorm : nullptr; o.b_aug = tc ? tc->b_aug : nullptr;
-	o.center = tc ? tc->center : nullptr;
+	o.center = tc ? tc->center : (sm ? sm->center : nullptr);
 	o.k_pad = tc ? tc->k_pad : 0; o.d_pad = tc ? tc->d_pad : 0;
 	o.ctl = ctl; o.slot = slot;
 	o.divide = 1;
 	return o;
 }
 
-static uint32_t sink_rows(const Shape& s, float* cprep, const TcMeans* tc)
+static uint32_t sink_rows(const Shape& s, const SimtMeans* sm, const TcMeans* tc)
 {
 	uint32_t rows_total = s.k;
-	if (cprep) rows_total = std::max(rows_total, simt_rows(s.k));
+	if (sm) rows_total = std::max(rows_total, simt_rows(s.k));
 	if (tc) rows_total = std::max(rows_total, tc->k_pad);
 	return rows_total;
 }
@@ -329,29 +332,29 @@ size_t exchange_buffer_bytes(uint32_t k, uint32_t dim)
 
 cudaError_t launch_exchange_finalize(float* acc, uint32_t* counts, uint32_t replicas, void* const* peer_bases, uint32_t world,
 	uint32_t rank, uint32_t epoch, uint64_t wait_limit_ns, float* means_out, uint32_t* sizes_out, const Shape& s,
-	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
+	const SimtMeans* sm, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
 	if (world < 1 || world > EXCHANGE_MAX_RANKS || rank >= world) return cudaErrorInvalidValue;
 	ExchangePeers peers;
 	for (uint32_t r = 0; r < EXCHANGE_MAX_RANKS; ++r) peers.base[r] = r < world ? static_cast<uint64_t*>(peer_bases[r]) : nullptr;
-	const uint32_t rows_total = sink_rows(s, cprep, tc);
+	const uint32_t rows_total = sink_rows(s, sm, tc);
 	// never more blocks than SMs: all of them are resident together (see the kernel)
 	const uint32_t wpb = 8;
 	const uint32_t grid = std::min<uint32_t>(std::max<uint32_t>((rows_total + wpb - 1) / wpb, 1), (uint32_t)current_sm_count());
 	exchange_finalize_kernel<<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, acc_replica_stride(s.k, s.dim), peers, world, rank, epoch,
-		wait_limit_ns, make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot));
+		wait_limit_ns, make_sinks(means_out, sizes_out, s, sm, tc, ctl, slot));
 	return cudaGetLastError();
 }
 
 static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t replicas, const float* means_in, float* means_out,
-	uint32_t* sizes_out, const Shape& s, float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream, bool divide = true)
+	uint32_t* sizes_out, const Shape& s, const SimtMeans* sm, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream, bool divide = true)
 {
 	const size_t rep_stride = acc_replica_stride(s.k, s.dim);
-	const uint32_t rows_total = sink_rows(s, cprep, tc);
+	const uint32_t rows_total = sink_rows(s, sm, tc);
 	const uint32_t wpb = 8;
 	uint32_t grid = (rows_total + wpb - 1) / wpb;
 	grid = std::min<uint32_t>(std::max<uint32_t>(grid, 1), (uint32_t)current_sm_count() * 8);
-	RowSinks o = make_sinks(means_out, sizes_out, s, cprep, tc, ctl, slot);
+	RowSinks o = make_sinks(means_out, sizes_out, s, sm, tc, ctl, slot);
 	o.divide = divide ? 1 : 0;
 	if (finalize)
 		finalize_prepare_kernel<true><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, o);
@@ -359,16 +362,16 @@ static void launch_fp(bool finalize, float* acc, uint32_t* counts, uint32_t repl
 		finalize_prepare_kernel<false><<<grid, wpb * 32, 0, stream>>>(acc, counts, replicas, rep_stride, means_in, o);
 }
 
-void launch_prepare_means(const float* means, const Shape& s, float* cprep, const TcMeans* tc,
+void launch_prepare_means(const float* means, const Shape& s, const SimtMeans* sm, const TcMeans* tc,
 	Control* ctl, int slot, cudaStream_t stream)
 {
-	launch_fp(false, nullptr, nullptr, 1, means, nullptr, nullptr, s, cprep, tc, ctl, slot, stream);
+	launch_fp(false, nullptr, nullptr, 1, means, nullptr, nullptr, s, sm, tc, ctl, slot, stream);
 }
 
 void launch_finalize(float* acc, uint32_t* counts, uint32_t replicas, float* means_out, uint32_t* sizes_out, const Shape& s,
-	float* cprep, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
+	const SimtMeans* sm, const TcMeans* tc, Control* ctl, int slot, cudaStream_t stream)
 {
-	launch_fp(true, acc, counts, replicas, nullptr, means_out, sizes_out, s, cprep, tc, ctl, slot, stream);
+	launch_fp(true, acc, counts, replicas, nullptr, means_out, sizes_out, s, sm, tc, ctl, slot, stream);
 }
 
 void launch_finalize_sums(float* acc, uint32_t* counts, uint32_t replicas, float* sums_out, const Shape& s, Control* ctl, cudaStream_t stream)
@@ -422,6 +425,57 @@ cudaError_t launch_probe_atomics(float* result, uint64_t n, uint32_t k, uint32_t
 		if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(probe_atomics_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
 		probe_atomics_kernel<false><<<(uint32_t)blocks, 256, smem, stream>>>(result, total, k, dim, cached);
 	}
+	return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// recognising the point set of a stateless call
+// ------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) points_fingerprint_kernel(const uint32_t* __restrict__ bits, uint64_t words, PointsKey* __restrict__ key)
+{
+	const uint32_t lane = threadIdx.x & 31u;
+	const uint64_t lines = (words + 31) / 32;
+	const uint64_t samples = (lines + 15) / 16 + 1;             // every 16th line, and the last one
+	const uint64_t gwarp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, gwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+	unsigned long long acc = 0;
+	for (uint64_t sidx = gwarp; sidx < samples; sidx += gwarps) {
+		const uint64_t line = sidx + 1 == samples ? lines - 1 : sidx * 16;
+		const uint64_t i = line * 32 + lane;
+		if (i < words && (sidx + 1 == samples || line < lines)) {
+			unsigned long long x = ((unsigned long long)bits[i] << 32) ^ (i * 0x9E3779B97F4A7C15ull);
+			x ^= x >> 29; x *= 0xBF58476D1CE4E5B9ull; x ^= x >> 32;
+			acc += x;
+		}
+	}
+	#pragma unroll
+	for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+	if (lane == 0 && acc) atomicAdd(&key->fp_new, acc);
+}
+
+__global__ void points_key_decide_kernel(PointsKey* key, unsigned long long ptr, unsigned long long n, uint32_t dim, uint32_t layout,
+	uint32_t variant, Control* ctl)
+{
+	const bool same = key->fp_old == key->fp_new && key->ptr == ptr && key->n == n && key->dim == dim && key->layout == layout &&
+		key->variant == variant;
+	key->valid = same ? 1u : 0u;
+	key->fp_old = key->fp_new;
+	key->ptr = ptr; key->n = n; key->dim = dim; key->layout = layout; key->variant = variant;
+	if (!same) ctl->xmax2 = 0.0f;
+}
+
+cudaError_t launch_points_fingerprint(const float* pts, uint64_t words, PointsKey* key, int sm_count, cudaStream_t stream)
+{
+	const uint64_t samples = ((words + 31) / 32 + 15) / 16 + 1;
+	const uint32_t grid = (uint32_t)std::min<uint64_t>((samples + 7) / 8, (uint64_t)sm_count * 8);
+	points_fingerprint_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(pts), words, key);
+	return cudaGetLastError();
+}
+
+cudaError_t launch_points_key_decide(PointsKey* key, const float* pts, const Shape& s, int variant, Control* ctl, cudaStream_t stream)
+{
+	points_key_decide_kernel<<<1, 1, 0, stream>>>(key, (unsigned long long)reinterpret_cast<uintptr_t>(pts), s.n, s.dim, (uint32_t)s.soa,
+		(uint32_t)variant, ctl);
 	return cudaGetLastError();
 }
 

@@ -206,7 +206,7 @@ int bkm_set_stream(bkm_handle_t h, void* stream);
  * pairs with all means resident in shared memory where the shape allows, i.e. 257..1024 means
  * of 17..32 dimensions), "fuse_update" (0/1, default 1: let that kernel add every point to the sum
  * of the cluster it picks, which replaces the row-wise update pass of bkm_run; needs dim % 4 == 0),
- * "exchange_wait_ms" (1..600000, default 10000: how long the peer-memory exchange waits for a peer).
+ * "exchange_wait_ms" (1..600000, default 2000: how long the peer-memory exchange waits for a peer).
  * Unknown names fail with BKM_ERR_INVALID. */
 int bkm_set_option(bkm_handle_t h, const char* name, double value);
 
@@ -302,8 +302,9 @@ int bkm_shard_range(uint64_t n_total, int world_size, int rank, uint64_t* begin,
  * sure that ALL ranks succeeded (otherwise stay with NCCL), then every rank calls
  * bkm_peer_enable(h, 1).  One process driving several GPUs: bkm_peer_buffer of every handle,
  * bkm_peer_attach with the raw pointers (peer access enabled by the caller), bkm_peer_enable.
- * A wait that runs out ("exchange_wait_ms" option, default 10000) sets the status word: the run
- * returns BKM_ERR_DEVICE instead of hanging when a rank has died or made a different call. */
+ * A wait that runs out ("exchange_wait_ms" option, default 2000) sets the status word, and the
+ * remaining iterations of that run do not wait again: the run returns BKM_ERR_DEVICE within about
+ * the limit, instead of hanging, when a rank has died or made a different call. */
 #define BKM_PEER_BLOB_BYTES 128
 int bkm_peer_export(bkm_handle_t h, void* blob, size_t blob_bytes);
 int bkm_peer_open(bkm_handle_t h, const void* blobs, size_t blob_bytes_each, int world_size, int rank);
