@@ -54,7 +54,7 @@ class Config(ctypes.Structure):
     _fields_ = [
         ("n", ctypes.c_uint64), ("k", ctypes.c_uint32), ("dim", ctypes.c_uint32),
         ("layout", ctypes.c_int32), ("layout_means", ctypes.c_int32), ("device", ctypes.c_int32),
-        ("variant_assign", ctypes.c_int32), ("variant_update", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("variant_assign", ctypes.c_int32), ("variant_update", ctypes.c_int32), ("num_gpus", ctypes.c_int32),
     ]
 
 
@@ -269,12 +269,13 @@ class KMeans:
     """
 
     def __init__(self, layout=LAYOUT_AOS, layout_means=None, device=0, variant_assign=ASSIGN_AUTO,
-                 variant_update=UPDATE_AUTO):
+                 variant_update=UPDATE_AUTO, num_gpus=1):
         self.layout = layout
         self.layout_means = layout if layout_means is None else layout_means
         self.device = device
         self.variant_assign = variant_assign
         self.variant_update = variant_update
+        self.num_gpus = num_gpus      # > 1: this one process drives GPUs device .. device+num_gpus-1
         self._h = None
         self.dim = self.k = self.n = 0
         self.iters = 1
@@ -442,7 +443,7 @@ class KMeans:
         self.dim, self.k, self.n, self.iters = int(dim), int(k), int(n), int(iters)
         cfg = Config(n=self.n, k=self.k, dim=self.dim, layout=self.layout, layout_means=self.layout_means,
                      device=self.device, variant_assign=self.variant_assign,
-                     variant_update=self.variant_update, reserved=0)
+                     variant_update=self.variant_update, num_gpus=self.num_gpus)
         h = ctypes.c_void_p()
         check(lib().bkm_create(ctypes.byref(cfg), ctypes.byref(h)))
         self._h = h

@@ -14,6 +14,7 @@
  * The inputs are the reference executable's own for the same --N --k --dim --seed --layout
  * (reference_data.hpp restates its generator call for call); without --seed the reference draws a
  * random seed, this harness uses 42.  --dumpInputs <file> writes them out (with --dryRun: and stops).
+ * --gpus G (not in the reference, which drives device 0 only) shards the points over G GPUs.
  */
 #include "bkm.h"
 #include "reference_data.hpp"
@@ -38,7 +39,7 @@ namespace {
 
 struct Options {
 	uint64_t n = 10240;
-	uint32_t k = 128, dim = 20, iterations = 1, seed = 42;
+	uint32_t k = 128, dim = 20, iterations = 1, seed = 42, gpus = 1;
 	bool assignment_only = false, verify = false, dry_run = false;
 	std::string algorithm = "b200", layout = "aos", layout_means, dump_inputs;
 };
@@ -48,7 +49,7 @@ struct Options {
 	std::cout << "Invalid arguments: " << what << std::endl << std::endl
 		<< "Usage: bkm-kmeans [--N n] [--k k] [--dim d] [--iterations i | --assignmentOnly] [--seed s]\n"
 		<< "                  [--algorithm b200|b200_exact|b200_simt|b200_tc|serial] [--layout aos|soa]\n"
-		<< "                  [--layoutMeans aos|soa] [--verify] [--dryRun] [--dumpInputs file]\n"
+		<< "                  [--layoutMeans aos|soa] [--verify] [--dryRun] [--dumpInputs file] [--gpus g]\n"
 		<< "Integers take the suffixes k, M, G (powers of 1024)." << std::endl;
 	std::exit(1);
 }
@@ -95,6 +96,7 @@ Options parse(int argc, char** argv)
 		else if (a == "layout") o.layout = value();
 		else if (a == "layoutMeans") o.layout_means = value();
 		else if (a == "dumpInputs") o.dump_inputs = value();
+		else if (a == "gpus") o.gpus = (uint32_t)parse_int(a, value());
 		else if (a == "cudaBlockSize" || a == "cudaBlockCount" || a == "cudaSharedMemorySize" || a == "privatizedCopies" ||
 			a == "itemsPerThread" || a == "regsCache") (void)value();
 		else if (a == "double") usage_error("--double: the B200 kernels are fp32 only");
@@ -104,6 +106,8 @@ Options parse(int argc, char** argv)
 	if (o.layout_means.empty()) o.layout_means = o.layout;
 	if (o.assignment_only && iterations_given) usage_error("--assignmentOnly conflicts with --iterations");
 	if (o.dim < 1 || o.k < 1 || o.n < 1 || o.iterations < 1) usage_error("N, k, dim and iterations must be positive");
+	if (o.gpus < 1 || o.gpus > 8) usage_error("--gpus must be 1..8");
+	if (o.gpus > 1 && o.assignment_only) usage_error("--assignmentOnly runs on one GPU");
 	for (const std::string* l : {&o.layout, &o.layout_means})
 		if (*l != "aos" && *l != "soa") usage_error("layout must be aos or soa");
 	return o;
@@ -248,6 +252,7 @@ int run(const Options& o)
 		cfg.layout = soa ? BKM_LAYOUT_SOA : BKM_LAYOUT_AOS;
 		cfg.layout_means = soa_means ? BKM_LAYOUT_SOA : BKM_LAYOUT_AOS;
 		cfg.variant_assign = variant;
+		cfg.num_gpus = (int32_t)o.gpus;          // > 1: the points are sharded over GPUs 0 .. gpus-1 of this process
 		bkm_handle_t h = nullptr;
 		std::cerr << "Initializing ... ";
 		double t0 = now_ms();

@@ -16,6 +16,7 @@
 #include <mutex>
 #include <new>
 #include <string>
+#include <vector>
 
 namespace {
 
@@ -312,6 +313,11 @@ struct bkm_handle_s {
 	int graph_cur = 0, graph_slot = 0;
 	cudaStream_t graph_stream = nullptr;
 	cudaEvent_t ev_run[2] = {};
+	// One process driving several GPUs (config.num_gpus > 1): this handle then owns no device state
+	// itself but one handle per GPU, each with a contiguous shard of the points, joined by the
+	// peer-memory exchange.
+	std::vector<bkm_handle_s*> shards;
+	std::vector<uint64_t> shard_begin;
 };
 
 extern "C" {
@@ -558,15 +564,69 @@ int bkm_selftest_wait_timeout(void* workspace, uint32_t limit_ms, void* stream)
 
 // ---- driver -------------------------------------------------------------------------------------
 
+// One process, several GPUs: one shard handle per device, joined by the peer-memory exchange over
+// directly attached buffers (peer access between all pairs of the devices is required).
+static int create_group(const bkm_config_t* cfg, int ndev, bkm_handle_t* out)
+{
+	const int g_count = cfg->num_gpus;
+	if (cfg->device < 0 || cfg->device + g_count > ndev)
+		return fail(BKM_ERR_INVALID, "devices %d..%d requested, %d present", cfg->device, cfg->device + g_count - 1, ndev);
+	if (cfg->n < (uint64_t)g_count) return fail(BKM_ERR_INVALID, "fewer points than GPUs");
+	if ((uint64_t)cfg->k * cfg->dim + cfg->k > bkm::EXCHANGE_MAX_WORDS)
+		return fail(BKM_ERR_UNSUPPORTED, "k*dim + k = %llu is beyond the peer-memory exchange (%llu words): run one process per GPU with bkm_comm_init",
+			(unsigned long long)cfg->k * cfg->dim + cfg->k, (unsigned long long)bkm::EXCHANGE_MAX_WORDS);
+	for (int a = 0; a < g_count; ++a)
+		for (int b = 0; b < g_count; ++b) {
+			if (a == b) continue;
+			int can = 0;
+			CUDA_TRY(cudaDeviceCanAccessPeer(&can, cfg->device + a, cfg->device + b));
+			if (!can) return fail(BKM_ERR_UNSUPPORTED, "device %d cannot access the memory of device %d", cfg->device + a, cfg->device + b);
+			CUDA_TRY(cudaSetDevice(cfg->device + a));
+			const cudaError_t e = cudaDeviceEnablePeerAccess(cfg->device + b, 0);
+			if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return fail(BKM_ERR_CUDA, "cudaDeviceEnablePeerAccess: %s", cudaGetErrorString(e));
+			cudaGetLastError();
+		}
+	bkm_handle_s* h = new (std::nothrow) bkm_handle_s();
+	if (!h) return fail(BKM_ERR_INVALID, "out of host memory");
+	h->cfg = *cfg;
+	h->shape.n = cfg->n; h->shape.k = cfg->k; h->shape.dim = cfg->dim;
+	h->shape.soa = cfg->layout == BKM_LAYOUT_SOA; h->shape.soa_means = cfg->layout_means == BKM_LAYOUT_SOA;
+	auto bail = [&](int code) { std::string keep = g_error; bkm_destroy(h); g_error = keep; return code; };
+	void* bases[bkm::EXCHANGE_MAX_RANKS] = {};
+	for (int g = 0; g < g_count; ++g) {
+		uint64_t begin = 0, count = 0;
+		bkm_shard_range(cfg->n, g_count, g, &begin, &count);
+		bkm_config_t c = *cfg;
+		c.n = count; c.device = cfg->device + g; c.num_gpus = 0;
+		bkm_handle_t child = nullptr;
+		int rc = bkm_create(&c, &child);
+		if (rc) return bail(rc);
+		h->shards.push_back(child);
+		h->shard_begin.push_back(begin);
+		if ((rc = bkm_peer_buffer(child, &bases[g], nullptr))) return bail(rc);
+	}
+	for (int g = 0; g < g_count; ++g) {
+		int rc = bkm_peer_attach(h->shards[g], bases, g_count, g);
+		if (rc == BKM_OK) rc = bkm_peer_enable(h->shards[g], 1);
+		if (rc) return bail(rc);
+	}
+	*out = h;
+	return BKM_OK;
+}
+
+#define NOT_FOR_GROUPS(h, what) do { if (!(h)->shards.empty()) \
+	return fail(BKM_ERR_UNSUPPORTED, "%s is not available on a handle that drives several GPUs", what); } while (0)
+
 int bkm_create(const bkm_config_t* cfg, bkm_handle_t* out)
 {
 	if (!cfg || !out) return fail(BKM_ERR_INVALID, "null argument");
 	*out = nullptr;
-	if (cfg->reserved != 0) return fail(BKM_ERR_INVALID, "reserved must be 0");
+	if (cfg->num_gpus < 0 || cfg->num_gpus > (int)bkm::EXCHANGE_MAX_RANKS) return fail(BKM_ERR_INVALID, "num_gpus must be 0..%d", (int)bkm::EXCHANGE_MAX_RANKS);
 	int rc = check_shape(cfg->n, cfg->k, cfg->dim, cfg->layout, cfg->layout_means);
 	if (rc) return rc;
 	int ndev = bkm_device_count();
 	if (ndev == 0) return fail(BKM_ERR_CUDA, "no CUDA device");
+	if (cfg->num_gpus > 1) return create_group(cfg, ndev, out);
 	if (cfg->device < 0 || cfg->device >= ndev) return fail(BKM_ERR_INVALID, "device %d out of range (0..%d)", cfg->device, ndev - 1);
 	CUDA_TRY(cudaSetDevice(cfg->device));
 
@@ -613,6 +673,11 @@ int bkm_create(const bkm_config_t* cfg, bkm_handle_t* out)
 int bkm_destroy(bkm_handle_t h)
 {
 	if (!h) return BKM_OK;
+	if (!h->shards.empty()) {
+		for (bkm_handle_s* c : h->shards) bkm_destroy(c);
+		delete h;
+		return BKM_OK;
+	}
 	cudaSetDevice(h->cfg.device);
 	if (h->stream) cudaStreamSynchronize(h->stream);
 	drop_graph(h);
@@ -639,6 +704,7 @@ int bkm_destroy(bkm_handle_t h)
 int bkm_set_stream(bkm_handle_t h, void* stream)
 {
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	NOT_FOR_GROUPS(h, "bkm_set_stream");
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
 	h->stream = static_cast<cudaStream_t>(stream);   // NULL is the legacy default stream
@@ -648,6 +714,10 @@ int bkm_set_stream(bkm_handle_t h, void* stream)
 int bkm_set_option(bkm_handle_t h, const char* name, double value)
 {
 	if (!h || !name) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) {
+		for (bkm_handle_s* c : h->shards) { const int rc = bkm_set_option(c, name, value); if (rc) return rc; }
+		return BKM_OK;
+	}
 	if (!strcmp(name, "margin_scale")) {
 		if (!(value > 0.0)) return fail(BKM_ERR_INVALID, "margin_scale must be positive");
 		h->margin_scale = (float)value;
@@ -715,6 +785,30 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_means)
 {
 	if (!h || !host_points || !host_means) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) {
+		// every GPU gets its contiguous range of points: rows of the row-major array, or the same
+		// column range of every dimension of the dimension-major one
+		const uint64_t n_total = h->shape.n;
+		const uint32_t dim = h->shape.dim;
+		for (size_t g = 0; g < h->shards.size(); ++g) {
+			bkm_handle_s* c = h->shards[g];
+			const uint64_t begin = h->shard_begin[g], count = c->shape.n;
+			if (!h->shape.soa) {
+				const int rc = bkm_initialize(c, host_points + (size_t)begin * dim, host_means);
+				if (rc) return rc;
+				continue;
+			}
+			CUDA_TRY(cudaSetDevice(c->cfg.device));
+			if (!c->d_points_owned) CUDA_TRY(cudaMalloc(&c->d_points_owned, (size_t)count * dim * sizeof(float)));
+			c->d_points = c->d_points_owned;
+			CUDA_TRY(cudaMemcpy2DAsync(c->d_points_owned, (size_t)count * sizeof(float), host_points + begin, (size_t)n_total * sizeof(float),
+				(size_t)count * sizeof(float), dim, cudaMemcpyHostToDevice, c->stream));
+			const int rc = initialize_common(c, host_means, cudaMemcpyHostToDevice);
+			if (rc) return rc;
+		}
+		h->initialized = true;
+		return BKM_OK;
+	}
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	const size_t bytes = (size_t)h->shape.n * h->shape.dim * sizeof(float);
 	if (!h->d_points_owned) CUDA_TRY(cudaMalloc(&h->d_points_owned, bytes));
@@ -726,6 +820,7 @@ int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_m
 int bkm_initialize_device(bkm_handle_t h, const float* dev_points, const float* dev_means)
 {
 	if (!h || !dev_points || !dev_means) return fail(BKM_ERR_INVALID, "null argument");
+	NOT_FOR_GROUPS(h, "bkm_initialize_device (the points of a shard must lie on its own GPU)");
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	h->d_points = dev_points;
 	return initialize_common(h, dev_means, cudaMemcpyDeviceToDevice);
@@ -735,6 +830,10 @@ int bkm_set_means(bkm_handle_t h, const float* host_means)
 {
 	if (!h || !host_means) return fail(BKM_ERR_INVALID, "null argument");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "set_means before initialize");
+	if (!h->shards.empty()) {
+		for (bkm_handle_s* c : h->shards) { const int rc = bkm_set_means(c, host_means); if (rc) return rc; }
+		return BKM_OK;
+	}
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	const bkm::Shape& s = h->shape;
 	cudaStream_t st = h->stream;
@@ -830,6 +929,20 @@ int bkm_run_async(bkm_handle_t h, uint32_t iters)
 {
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "run before initialize");
+	if (!h->shards.empty()) {
+		// iteration by iteration over all GPUs, so that no device runs far ahead of the one whose
+		// kernels this thread has not enqueued yet (their exchange kernels wait for each other)
+		for (bkm_handle_s* c : h->shards) c->ev_count = 0;
+		for (uint32_t it = 0; it < iters; ++it)
+			for (bkm_handle_s* c : h->shards) {
+				CUDA_TRY(cudaSetDevice(c->cfg.device));
+				const bool timed = c->phase_timing && (iters - it) <= (uint32_t)bkm_handle_s::EV_RING;
+				const int rc = enqueue_iteration(c, timed ? c->ev[c->ev_count] : nullptr);
+				if (rc) return rc;
+				if (timed) ++c->ev_count;
+			}
+		return BKM_OK;
+	}
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	cudaStream_t st = h->stream;
 	h->ev_count = 0;
@@ -873,6 +986,16 @@ int bkm_run_async(bkm_handle_t h, uint32_t iters)
 int bkm_synchronize(bkm_handle_t h)
 {
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	if (!h->shards.empty()) {
+		int first = BKM_OK;
+		std::string msg;
+		for (bkm_handle_s* c : h->shards) {
+			const int rc = bkm_synchronize(c);
+			if (rc && !first) { first = rc; msg = g_error; }
+		}
+		if (first) g_error = msg;
+		return first;
+	}
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
 	bkm::Control c;
@@ -895,6 +1018,7 @@ int bkm_get_means(bkm_handle_t h, float* host_means)
 {
 	if (!h || !host_means) return fail(BKM_ERR_INVALID, "null argument");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "no results before initialize");
+	if (!h->shards.empty()) return bkm_get_means(h->shards[0], host_means);      // identical on every GPU
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaMemcpyAsync(host_means, h->d_means[h->cur], (size_t)h->shape.k * h->shape.dim * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
@@ -905,6 +1029,13 @@ int bkm_get_assignment(bkm_handle_t h, uint32_t* host_assignment)
 {
 	if (!h || !host_assignment) return fail(BKM_ERR_INVALID, "null argument");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "no results before initialize");
+	if (!h->shards.empty()) {
+		for (size_t g = 0; g < h->shards.size(); ++g) {
+			const int rc = bkm_get_assignment(h->shards[g], host_assignment + h->shard_begin[g]);
+			if (rc) return rc;
+		}
+		return BKM_OK;
+	}
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaMemcpyAsync(host_assignment, h->d_asg, h->shape.n * sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
@@ -915,6 +1046,7 @@ int bkm_get_sizes(bkm_handle_t h, uint32_t* host_sizes)
 {
 	if (!h || !host_sizes) return fail(BKM_ERR_INVALID, "null argument");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "no results before initialize");
+	if (!h->shards.empty()) return bkm_get_sizes(h->shards[0], host_sizes);
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaMemcpyAsync(host_sizes, h->d_sizes, (size_t)h->shape.k * sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
@@ -924,6 +1056,7 @@ int bkm_get_sizes(bkm_handle_t h, uint32_t* host_sizes)
 int bkm_device_means(bkm_handle_t h, const float** dev_means)
 {
 	if (!h || !dev_means) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) return bkm_device_means(h->shards[0], dev_means);
 	*dev_means = h->d_means[h->cur];
 	return BKM_OK;
 }
@@ -931,6 +1064,7 @@ int bkm_device_means(bkm_handle_t h, const float** dev_means)
 int bkm_device_assignment(bkm_handle_t h, const uint32_t** dev_assignment)
 {
 	if (!h || !dev_assignment) return fail(BKM_ERR_INVALID, "null argument");
+	NOT_FOR_GROUPS(h, "bkm_device_assignment (the assignment is spread over the GPUs)");
 	*dev_assignment = h->d_asg;
 	return BKM_OK;
 }
@@ -938,6 +1072,7 @@ int bkm_device_assignment(bkm_handle_t h, const uint32_t** dev_assignment)
 int bkm_iterations_done(bkm_handle_t h, uint64_t* out)
 {
 	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) return bkm_iterations_done(h->shards[0], out);
 	*out = h->iters_done;
 	return BKM_OK;
 }
@@ -945,6 +1080,7 @@ int bkm_iterations_done(bkm_handle_t h, uint64_t* out)
 int bkm_phase_ms(bkm_handle_t h, float out[6])
 {
 	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) return bkm_phase_ms(h->shards[0], out);
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
 	for (int p = 0; p < 6; ++p) out[p] = 0.0f;
@@ -965,6 +1101,14 @@ int bkm_phase_ms(bkm_handle_t h, float out[6])
 int bkm_counters(bkm_handle_t h, uint64_t out[4])
 {
 	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) {
+		// kernels and variants of the first GPU; the re-checked points of all
+		uint64_t total = 0;
+		for (bkm_handle_s* c : h->shards) { const int rc = bkm_counters(c, out); if (rc) return rc; total += out[0]; }
+		const int rc = bkm_counters(h->shards[0], out);
+		out[0] = total;
+		return rc;
+	}
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
 	bkm::Control c;
@@ -979,6 +1123,7 @@ int bkm_counters(bkm_handle_t h, uint64_t out[4])
 int bkm_assign_plan(bkm_handle_t h, uint32_t out[4])
 {
 	if (!h || !out) return fail(BKM_ERR_INVALID, "null argument");
+	if (!h->shards.empty()) return bkm_assign_plan(h->shards[0], out);
 	out[0] = out[1] = out[2] = out[3] = 0;
 	if (h->assign_variant == BKM_ASSIGN_EXACT) out[0] = BKM_PLAN_EXACT;
 	else if (h->assign_variant == BKM_ASSIGN_SIMT) out[0] = BKM_PLAN_SIMT;
@@ -1007,6 +1152,7 @@ int bkm_comm_init(bkm_handle_t h, const void* id, size_t id_bytes, int world_siz
 {
 	if (!h || !id || id_bytes < sizeof(nccl_unique_id)) return fail(BKM_ERR_INVALID, "bad argument");
 	if (world_size < 1 || rank < 0 || rank >= world_size) return fail(BKM_ERR_INVALID, "bad world_size/rank");
+	NOT_FOR_GROUPS(h, "bkm_comm_init");
 	if (h->comm) return fail(BKM_ERR_STATE, "communicator already initialised");
 	Nccl* nc = nccl();
 	if (!nc->ok) return fail(BKM_ERR_NCCL, "libnccl.so.2 not found");
@@ -1035,6 +1181,7 @@ constexpr uint32_t PEER_MAGIC = 0x626b6d78u;
 
 int own_exchange_buffer(bkm_handle_t h)
 {
+	NOT_FOR_GROUPS(h, "the peer exchange of a single shard");
 	if (h->d_xbuf) return BKM_OK;
 	if ((uint64_t)h->shape.k * h->shape.dim + h->shape.k > bkm::EXCHANGE_MAX_WORDS)
 		return fail(BKM_ERR_UNSUPPORTED, "k*dim + k = %llu exceeds the %llu words the peer exchange is meant for (use the NCCL all-reduce)",
@@ -1142,6 +1289,7 @@ int bkm_peer_attach(bkm_handle_t h, void* const* bases, int world_size, int rank
 int bkm_peer_enable(bkm_handle_t h, int enable)
 {
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
+	NOT_FOR_GROUPS(h, "bkm_peer_enable");
 	if (enable && !h->peer_world) return fail(BKM_ERR_STATE, "no peer buffers attached (bkm_peer_open / bkm_peer_attach first)");
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	CUDA_TRY(cudaStreamSynchronize(h->stream));
@@ -1154,6 +1302,10 @@ int bkm_run_ready(bkm_handle_t h)
 {
 	if (!h) return fail(BKM_ERR_INVALID, "null handle");
 	if (!h->initialized) return fail(BKM_ERR_STATE, "not initialized");
+	if (!h->shards.empty()) {
+		for (bkm_handle_s* c : h->shards) { const int rc = bkm_run_ready(c); if (rc) return rc; }
+		return BKM_OK;
+	}
 	if (h->assign_variant == BKM_ASSIGN_TC && !h->plan) return fail(BKM_ERR_STATE, "the tensor-core plan is missing");
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	bkm::Control c;

@@ -169,9 +169,9 @@ int bkm_selftest_wait_timeout(void* workspace, uint32_t limit_ms, void* stream);
 /* ------------------------------------------------------------------------------------------
  * Fixed-iteration driver.  Replaces CudaKMeansAlgorithm (headers/cuda.hpp:19-112) behind the
  * IKMeansAlgorithm call sequence initialize / run / getMeans / getAssignment / cleanup
- * (headers/interface.hpp:8-49).  One handle drives one GPU; with world_size > 1 every rank
- * holds a contiguous shard of the points and the per-iteration sums and sizes are
- * all-reduced with NCCL before the divide.
+ * (headers/interface.hpp:8-49).  One handle drives one GPU, or (config.num_gpus) several from one
+ * process; with one process per GPU (bkm_comm_init) every rank holds a contiguous shard of the
+ * points and the per-iteration sums and sizes are exchanged between the ranks before the divide.
  * ------------------------------------------------------------------------------------------ */
 
 typedef struct bkm_handle_s* bkm_handle_t;
@@ -185,7 +185,14 @@ typedef struct bkm_config_s {
 	int32_t device;        /* CUDA device ordinal */
 	int32_t variant_assign;/* BKM_ASSIGN_* */
 	int32_t variant_update;/* BKM_UPDATE_* */
-	int32_t reserved;      /* must be 0 */
+	int32_t num_gpus;      /* 0 or 1: this handle drives GPU `device`.  G = 2..8: ONE process drives the GPUs
+	                          device .. device+G-1 through this handle: n is then the TOTAL number of points,
+	                          split into contiguous shards (bkm_shard_range), and every iteration's sums and
+	                          sizes cross between the GPUs through the peer-memory exchange (all pairs of the
+	                          devices must have peer access, k*dim + k <= 2^19).  bkm_initialize takes the
+	                          whole host array; results come back whole.  Not available on such a handle:
+	                          bkm_initialize_device, bkm_set_stream, bkm_device_assignment, bkm_comm_init.
+	                          The reference drives device 0 only (headers/cuda.hpp:53). */
 } bkm_config_t;
 
 /* Allocates the device state for the configuration (no data yet). */

@@ -165,7 +165,8 @@ private:
 	}
 
 public:
-	explicit B200KMeansAlgorithm(int device = 0) : mDevice(device) {}
+	/* gpus > 1: the points are sharded over GPUs device .. device+gpus-1 of this process (bkm_config_t::num_gpus) */
+	explicit B200KMeansAlgorithm(int device = 0, int gpus = 1) : mDevice(device), mGpus(gpus) {}
 	~B200KMeansAlgorithm() override { if (mHandle) bkm_destroy(mHandle); }
 
 	void initialize(std::size_t dim, std::size_t k, std::size_t n, std::size_t iters,
@@ -180,6 +181,7 @@ public:
 		cfg.layout = bkm_adaptor::layout_code<LAYOUT>::value;
 		cfg.layout_means = bkm_adaptor::layout_code<LAYOUT_MEANS>::value;
 		cfg.device = mDevice;
+		cfg.num_gpus = mGpus;
 		bkm_adaptor::check(bkm_create(&cfg, &mHandle));
 		bkm_adaptor::check(bkm_initialize(mHandle, data.data(), means.data()));
 	}
@@ -201,6 +203,7 @@ public:
 
 private:
 	int mDevice;
+	int mGpus;
 };
 
 #endif /* BKM_REFERENCE_ADAPTORS_HPP */

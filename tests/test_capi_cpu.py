@@ -65,10 +65,10 @@ def test_argument_validation_needs_no_gpu(pkg):
     rc = L.bkm_assign_f32(None, None, None, 10, 2, 2, 0, 0, 0, None, 0, None)
     assert rc == pkg.ERR_INVALID
     assert b"null" in L.bkm_last_error()
-    cfg = pkg.Config(n=0, k=2, dim=2, layout=0, layout_means=0, device=0, variant_assign=0, variant_update=0, reserved=0)
+    cfg = pkg.Config(n=0, k=2, dim=2, layout=0, layout_means=0, device=0, variant_assign=0, variant_update=0, num_gpus=0)
     h = ctypes.c_void_p()
     assert L.bkm_create(ctypes.byref(cfg), ctypes.byref(h)) == pkg.ERR_INVALID
-    cfg = pkg.Config(n=8, k=2, dim=2, layout=5, layout_means=0, device=0, variant_assign=0, variant_update=0, reserved=0)
+    cfg = pkg.Config(n=8, k=2, dim=2, layout=5, layout_means=0, device=0, variant_assign=0, variant_update=0, num_gpus=0)
     assert L.bkm_create(ctypes.byref(cfg), ctypes.byref(h)) == pkg.ERR_INVALID
 
 

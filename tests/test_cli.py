@@ -52,6 +52,16 @@ def test_serial_algorithm_output_format(cli):
     assert "Running (3 iterations)" in err and "ms/iter" in err and "ns/input float" in err
 
 
+@pytest.mark.gpu
+def test_verify_on_two_gpus(cli):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    rc, out, err = _run(cli, "--N", "64k", "--k", "256", "--dim", "16", "--iterations", "4", "--gpus", "2", "--verify")
+    assert rc == 0, (out, err)
+    assert "Verifying results ... OK" in err
+
+
 def test_unknown_algorithm_exit_code_2(cli):
     rc, out, _ = _run(cli, "--algorithm", "nope", "--N", "256")
     assert rc == 2 and out.startswith("Error: Unkown algorithm 'nope'.")

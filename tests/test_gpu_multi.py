@@ -93,3 +93,37 @@ def test_two_ranks_match_single_gpu_and_oracle(tmp_path, pkg, torch_cuda, worklo
     assert ok, err
     assert (asg != want_asg).mean() <= 1e-3
     assert int(np.load(tmp_path / "sizes_0.npy").astype(np.int64).sum()) == n_total
+
+
+@pytest.mark.parametrize("name,n_total,iters,gpus", [("c1", 50001, 4, 2), ("c2", 40000, 3, 2), ("c5", 30011, 3, 2)])
+def test_one_process_driving_several_gpus(pkg, torch_cuda, workloads, oracle_mod, name, n_total, iters, gpus):
+    """bkm_config_t::num_gpus: one handle, the points sharded over the GPUs of this process, sums and
+    sizes exchanged through peer memory - against the single-GPU run and, step by step, the oracle."""
+    if torch_cuda.cuda.device_count() < gpus:
+        pytest.skip("needs %d GPUs" % gpus)
+    from helpers import means_close
+    spec = dict(workloads.CONFIGS[name])
+    k, d, lay = spec["k"], spec["dim"], spec["layout"]
+    rows = workloads.generate_rows(spec["kind"], n_total, d, k, 5, spec.get("sigma", 0.05), spec.get("zipf"), chunk=4096)
+    data, means0 = workloads.to_layout(rows, lay), workloads.to_layout(rows[:k], lay)
+    km = pkg.KMeans(layout=lay, num_gpus=gpus)
+    km.initialize(d, k, n_total, iters, data, means0)
+    prev = means0.copy()
+    for it in range(iters):
+        km.run(1)
+        asg, cur, sizes = km.getAssignment(), km.getMeans(), km.getSizes()
+        want = oracle_mod.assign(data, prev, n_total, k, d, lay, lay, threads=8)
+        assert np.array_equal(asg, want), (it, int((asg != want).sum()))
+        want_means, want_sizes = oracle_mod.update(data, asg, n_total, k, d, lay, lay)
+        assert np.array_equal(sizes, want_sizes), it
+        ok, err = means_close(cur, want_means)
+        assert ok, (it, err)
+        prev = cur
+    assert km.iterations_done() == iters
+    km.cleanup()
+    single = pkg.KMeans(layout=lay)
+    single.initialize(d, k, n_total, iters, data, means0)
+    single.run(iters)
+    ok, err = means_close(prev, single.getMeans())
+    assert ok, err
+    single.cleanup()
