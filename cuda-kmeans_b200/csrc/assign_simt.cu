@@ -326,15 +326,17 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 }
 
 // The same arithmetic with one THREAD per queued point and all means in shared memory, for mean sets
-// of a few hundred floats (the regime of the small-d fast pass): there a block per four points
-// leaves most of its threads without a mean, while a thread walks the whole set in microseconds.
-constexpr uint32_t LIST_SMALL_MAX_FLOATS = 2048;
+// of a few thousand floats and at most 16 dimensions: there a block per four points spends its time
+// in barriers and reductions, while a thread walks the whole set in microseconds and a long list
+// fills the machine by itself.
+constexpr uint32_t LIST_SMALL_MAX_FLOATS = 4096;
+constexpr uint32_t LIST_SMALL_MAX_DIM = 16;
 
 template<int D, bool SOA, bool SOAM>
 __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const float* __restrict__ pts, const float* __restrict__ means,
 	uint32_t* __restrict__ asg, uint64_t n, uint32_t k, const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
 {
-	__shared__ float sm[LIST_SMALL_MAX_FLOATS];          // [mean][dimension]
+	__shared__ __align__(16) float sm[LIST_SMALL_MAX_FLOATS];          // [mean][dimension]
 	for (uint32_t e = threadIdx.x; e < k * D; e += blockDim.x) {
 		const uint32_t m = e / D, j = e - m * D;
 		sm[e] = means[at<SOAM>(m, j, k, D)];
@@ -350,10 +352,22 @@ __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const floa
 		float best = 0.0f;
 		uint32_t bidx = 0;
 		for (uint32_t m = 0; m < k; ++m) {
+			float c[D];
+			if (D % 4 == 0) {
+				// whole rows as 128-bit loads (the same address for all threads: broadcast)
+				#pragma unroll
+				for (int q = 0; q < D / 4; ++q) {
+					const float4 v = reinterpret_cast<const float4*>(sm + m * D)[q];
+					c[4 * q] = v.x; c[4 * q + 1] = v.y; c[4 * q + 2] = v.z; c[4 * q + 3] = v.w;
+				}
+			} else {
+				#pragma unroll
+				for (int j = 0; j < D; ++j) c[j] = sm[m * D + j];
+			}
 			float sum = 0.0f;
 			#pragma unroll
 			for (int j = 0; j < D; ++j) {
-				const float diff = __fsub_rn(x[j], sm[m * D + j]);
+				const float diff = __fsub_rn(x[j], c[j]);
 				sum = __fadd_rn(sum, __fmul_rn(diff, diff));
 			}
 			const float dist = __fsqrt_rn(sum);
@@ -386,7 +400,7 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 	unsigned long long* split_keys = reinterpret_cast<unsigned long long*>(split_scratch);
 	uint32_t* split_arrive = split_scratch ? reinterpret_cast<uint32_t*>(split_keys + (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB) : nullptr;
 	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
-	if (list != nullptr && fix == nullptr && s.dim <= 8 && (uint64_t)s.k * s.dim <= LIST_SMALL_MAX_FLOATS) {
+	if (list != nullptr && fix == nullptr && s.dim <= LIST_SMALL_MAX_DIM && (uint64_t)s.k * s.dim <= LIST_SMALL_MAX_FLOATS) {
 		switch (s.dim) {
 		case 1: return launch_list_small<1>(pts, means, asg, s, list, list_count, sm_count, stream);
 		case 2: return launch_list_small<2>(pts, means, asg, s, list, list_count, sm_count, stream);
@@ -395,7 +409,15 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 		case 5: return launch_list_small<5>(pts, means, asg, s, list, list_count, sm_count, stream);
 		case 6: return launch_list_small<6>(pts, means, asg, s, list, list_count, sm_count, stream);
 		case 7: return launch_list_small<7>(pts, means, asg, s, list, list_count, sm_count, stream);
-		default: return launch_list_small<8>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 8: return launch_list_small<8>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 9: return launch_list_small<9>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 10: return launch_list_small<10>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 11: return launch_list_small<11>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 12: return launch_list_small<12>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 13: return launch_list_small<13>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 14: return launch_list_small<14>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 15: return launch_list_small<15>(pts, means, asg, s, list, list_count, sm_count, stream);
+		default: return launch_list_small<16>(pts, means, asg, s, list, list_count, sm_count, stream);
 		}
 	}
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {

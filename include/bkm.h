@@ -66,10 +66,19 @@ int bkm_device_count(void);
 
 /* ------------------------------------------------------------------------------------------
  * Kernel-runner entry points: device pointers in, device pointers out, stream-ordered, no
- * allocation.  `workspace` is device scratch of at least bkm_workspace_bytes(n,k,dim) bytes,
- * 256-byte aligned, owned by the caller; its contents are undefined between calls.
+ * device allocation.  `workspace` is device scratch of at least bkm_workspace_bytes(n,k,dim)
+ * bytes, 256-byte aligned, owned by the caller; it may hold anything on the first call.
  * `stream` is a cudaStream_t (NULL = legacy default stream, which is what the reference's
  * runners launch on, kernels/kernels.cu:201-207).
+ *
+ * The reference's drivers call their runners once per iteration on the same, immutable points
+ * (headers/cuda.hpp:70-88).  bkm_assign_f32 and bkm_iterate_f32 therefore leave what they derive
+ * from the points alone (a centre vector, the largest norm, tf32 operand planes) in the
+ * workspace, and a later call on the same workspace skips that work when it finds the same
+ * points: same address, shape and variant, and the same fingerprint of a sample of the values
+ * (every 16th 128-byte line and the last).  New data at the same address is therefore noticed;
+ * a caller that rewrites single coordinates in place, or scribbles over the workspace while
+ * keeping its first 256 bytes, must clear those 256 bytes before the next call.
  * ------------------------------------------------------------------------------------------ */
 
 /* Scratch size for the three calls below (0 on overflow or bad arguments). */
