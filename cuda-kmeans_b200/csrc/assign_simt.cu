@@ -82,30 +82,32 @@ __device__ __forceinline__ void add_four_dims(float (&sum)[PB], const float* sx,
 	}
 }
 
-// The same arithmetic for a list of queued points: one block per LIST_PB points, one mean per
+// The same arithmetic for a list of queued points: one block per PB points, one mean per
 // thread at a time, so that a short list still fills the machine and every mean that is
-// fetched serves LIST_PB points.  Each distance is still summed in dimension order by a single
+// fetched serves PB points (4, or 16 for long rows and many means, where the re-reads of the means
+// for every group of points are what the kernel spends its time on).  Each distance is still summed in dimension order by a single
 // thread.  AoS means are staged through a shared tile (32 dimensions of 256 means at a time,
 // loaded along the dimensions) so that the global loads stay coalesced; SoA means are read
 // directly (consecutive threads = consecutive means).
 constexpr int LIST_THREADS = 256;
-constexpr int LIST_PB = 4;
+constexpr int LIST_PB = 4;          // points per block (the default)
+constexpr int LIST_PB_WIDE = 16;    // ... when every fetched mean should serve more points (long rows, many means)
 constexpr uint32_t LIST_SPLIT_MAX_BLOCKS = 2048;   // grid size up to which a short list is shared between blocks
 
-template<bool SOA, bool SOAM>
-__global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const float* __restrict__ pts,
+template<bool SOA, bool SOAM, int PB>
+__global__ void __launch_bounds__(LIST_THREADS, 2) assign_exact_list_kernel(const float* __restrict__ pts,
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
 	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count,
 	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts, uint32_t resident_ok,
 	unsigned long long* __restrict__ split_keys, uint32_t* __restrict__ split_arrive)
 {
-	extern __shared__ __align__(16) float sx[];         // LIST_PB points (dpad floats each), then the means tile
-	__shared__ uint32_t smoved[LIST_PB][2];             // (old, new) cluster of a point that changed, else old == new
+	extern __shared__ __align__(16) float sx[];         // PB points (dpad floats each), then the means tile
+	__shared__ uint32_t smoved[PB][2];             // (old, new) cluster of a point that changed, else old == new
 	__shared__ uint32_t s_last;                         // this block is the last of its group's blocks to finish
 	const uint32_t dpad = (d + 3) & ~3u;
-	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + (size_t)LIST_PB * dpad);
-	__shared__ float sbest[LIST_PB][LIST_THREADS / 32];
-	__shared__ uint32_t sidx[LIST_PB][LIST_THREADS / 32];
+	float (*tile)[33] = reinterpret_cast<float (*)[33]>(sx + (size_t)PB * dpad);
+	__shared__ float sbest[PB][LIST_THREADS / 32];
+	__shared__ uint32_t sidx[PB][LIST_THREADS / 32];
 	const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
 	uint64_t total = *list_count;
 	if (total > n) total = n;
@@ -113,8 +115,8 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	// odd number of floats, one mean per thread -> conflict-free) instead of fetching them again
 	// for every group of points.
 	const uint32_t ds = d | 1u;
-	float* mres = sx + (size_t)LIST_PB * dpad;
-	const bool resident = resident_ok != 0 && total >= (uint64_t)gridDim.x * LIST_PB * 4;
+	float* mres = sx + (size_t)PB * dpad;
+	const bool resident = resident_ok != 0 && total >= (uint64_t)gridDim.x * PB * 4;
 	if (resident) {
 		for (uint32_t e = tid; e < k * d; e += LIST_THREADS) {
 			// e walks the means array in memory order (coalesced)
@@ -123,11 +125,11 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 		}
 	}
 	// Staging of a group's points: two dependent global reads (the list entry, then the coordinate)
-	// for each of the LIST_PB * d floats, all of them in flight together.  With few dimensions
+	// for each of the PB * d floats, all of them in flight together.  With few dimensions
 	// (at most two floats per thread) a thread fetches the NEXT group's floats into registers
 	// while the block works on the current group, which takes both reads off the block's
 	// critical path.  Unused slots of the last group repeat its first point.
-	const uint32_t pe = LIST_PB * d;
+	const uint32_t pe = PB * d;
 	const bool prefetch = pe <= 2 * LIST_THREADS;
 	uint32_t pf_p[2], pf_j[2];
 	float pf[2] = {0.0f, 0.0f};
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	// blocks walk all k means one after another.  The blocks then share the groups: `splits`
 	// blocks take one group, each a contiguous range of the means, and combine their results in
 	// global memory (see below); every block has at most one piece of work.
-	const uint64_t groups = (total + LIST_PB - 1) / LIST_PB;
+	const uint64_t groups = (total + PB - 1) / PB;
 	const uint32_t mchunks = (k + LIST_THREADS - 1) / LIST_THREADS;
 	uint32_t splits = 1;
 	if (split_keys != nullptr && groups > 0 && groups < gridDim.x && gridDim.x <= LIST_SPLIT_MAX_BLOCKS && mchunks > 1) {
@@ -162,11 +164,11 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 	const uint32_t m_end = splits > 1 ? min(k, ((split_part + 1) * mchunks / splits) * LIST_THREADS) : k;
 	const uint32_t n_chunks = (m_end - m_begin + LIST_THREADS - 1) / LIST_THREADS;
 	const uint32_t chunk_rot = (splits > 1 ? split_group : blockIdx.x) % n_chunks;
-	const uint64_t stride = (uint64_t)gridDim.x * LIST_PB;        // with splits > 1 one step leaves the list
-	const uint64_t w_first = (uint64_t)(splits > 1 ? split_group : blockIdx.x) * LIST_PB;
+	const uint64_t stride = (uint64_t)gridDim.x * PB;        // with splits > 1 one step leaves the list
+	const uint64_t w_first = (uint64_t)(splits > 1 ? split_group : blockIdx.x) * PB;
 	if (prefetch && w_first < total) fetch(w_first);
 	for (uint64_t w0 = w_first; w0 < total; w0 += stride) {
-		const uint32_t np = total - w0 < LIST_PB ? (uint32_t)(total - w0) : LIST_PB;
+		const uint32_t np = total - w0 < PB ? (uint32_t)(total - w0) : PB;
 		__syncthreads();
 		if (prefetch) {
 			#pragma unroll
@@ -181,27 +183,27 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 		}
 		__syncthreads();
 		if (prefetch && w0 + stride < total) fetch(w0 + stride);
-		float best[LIST_PB];
-		uint32_t bidx[LIST_PB];
+		float best[PB];
+		uint32_t bidx[PB];
 		#pragma unroll
-		for (int p = 0; p < LIST_PB; ++p) { best[p] = INFINITY; bidx[p] = 0xffffffffu; }
+		for (int p = 0; p < PB; ++p) { best[p] = INFINITY; bidx[p] = 0xffffffffu; }
 		// The blocks walk their chunks of 256 means starting at different chunks, so that blocks
 		// working at the same time do not all ask the L2 for the same rows at once.
 		for (uint32_t c = 0; c < n_chunks; ++c) {
 			const uint32_t m0 = m_begin + (c + chunk_rot < n_chunks ? c + chunk_rot : c + chunk_rot - n_chunks) * LIST_THREADS;
 			const uint32_t m = m0 + tid;
-			float sum[LIST_PB];
+			float sum[PB];
 			#pragma unroll
-			for (int p = 0; p < LIST_PB; ++p) sum[p] = 0.0f;
+			for (int p = 0; p < PB; ++p) sum[p] = 0.0f;
 			if (resident) {
 				if (m < k) {
 					const float* cm = mres + m * ds;
 					uint32_t j = 0;
-					for (; j + 4 <= d; j += 4) add_four_dims<LIST_PB>(sum, sx, dpad, j, cm[j], cm[j + 1], cm[j + 2], cm[j + 3]);
+					for (; j + 4 <= d; j += 4) add_four_dims<PB>(sum, sx, dpad, j, cm[j], cm[j + 1], cm[j + 2], cm[j + 3]);
 					for (; j < d; ++j) {
 						const float c = cm[j];
 						#pragma unroll
-						for (int p = 0; p < LIST_PB; ++p) {
+						for (int p = 0; p < PB; ++p) {
 							const float diff = __fsub_rn(sx[p * dpad + j], c);
 							sum[p] = __fadd_rn(sum[p], __fmul_rn(diff, diff));
 						}
@@ -212,37 +214,43 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 					const float* cm = means + m;
 					uint32_t j = 0;
 					for (; j + 4 <= d; j += 4)
-						add_four_dims<LIST_PB>(sum, sx, dpad, j, cm[(size_t)j * k], cm[(size_t)(j + 1) * k], cm[(size_t)(j + 2) * k], cm[(size_t)(j + 3) * k]);
+						add_four_dims<PB>(sum, sx, dpad, j, cm[(size_t)j * k], cm[(size_t)(j + 1) * k], cm[(size_t)(j + 2) * k], cm[(size_t)(j + 3) * k]);
 					for (; j < d; ++j) {
 						const float c = cm[(size_t)j * k];
 						#pragma unroll
-						for (int p = 0; p < LIST_PB; ++p) {
+						for (int p = 0; p < PB; ++p) {
 							const float diff = __fsub_rn(sx[p * dpad + j], c);
 							sum[p] = __fadd_rn(sum[p], __fmul_rn(diff, diff));
 						}
 					}
 				}
 			} else {
-				for (uint32_t j0 = 0; j0 < d; j0 += 32) {
-					__syncthreads();
-					// all 32 row segments of the warp in flight at once
-					float seg[32];
+				// 32 dimensions of the chunk's 256 means at a time go through the shared tile (read along
+				// the rows, used along the means).  The next slab's row segments are fetched into registers
+				// while the current slab is evaluated, so their latency does not sit between two barriers.
+				float seg[32];
+				auto fetch_slab = [&](uint32_t j0) {
 					#pragma unroll
 					for (uint32_t r = 0; r < 32; ++r) {
 						const uint32_t row = warp * 32 + r;
 						seg[r] = (m0 + row < k && j0 + lane < d) ? means[(size_t)(m0 + row) * d + j0 + lane] : 0.0f;
 					}
+				};
+				fetch_slab(0);
+				for (uint32_t j0 = 0; j0 < d; j0 += 32) {
+					__syncthreads();                    // the previous slab has been read by everyone
 					#pragma unroll
 					for (uint32_t r = 0; r < 32; ++r) tile[warp * 32 + r][lane] = seg[r];
 					__syncthreads();
+					if (j0 + 32 < d) fetch_slab(j0 + 32);
 					const uint32_t jn = d - j0 < 32 ? d - j0 : 32;
 					uint32_t jj = 0;
 					for (; jj + 4 <= jn; jj += 4)
-						add_four_dims<LIST_PB>(sum, sx, dpad, j0 + jj, tile[tid][jj], tile[tid][jj + 1], tile[tid][jj + 2], tile[tid][jj + 3]);
+						add_four_dims<PB>(sum, sx, dpad, j0 + jj, tile[tid][jj], tile[tid][jj + 1], tile[tid][jj + 2], tile[tid][jj + 3]);
 					for (; jj < jn; ++jj) {
 						const float c = tile[tid][jj];
 						#pragma unroll
-						for (int p = 0; p < LIST_PB; ++p) {
+						for (int p = 0; p < PB; ++p) {
 							const float diff = __fsub_rn(sx[p * dpad + j0 + jj], c);
 							sum[p] = __fadd_rn(sum[p], __fmul_rn(diff, diff));
 						}
@@ -251,7 +259,7 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 			}
 			if (m < k) {
 				#pragma unroll
-				for (int p = 0; p < LIST_PB; ++p) {
+				for (int p = 0; p < PB; ++p) {
 					const float dist = __fsqrt_rn(sum[p]);
 					// (the chunks come in rotated order: the lower index wins a tie explicitly)
 					if (bidx[p] == 0xffffffffu || dist < best[p] || (dist == best[p] && m < bidx[p])) { best[p] = dist; bidx[p] = m; }
@@ -259,7 +267,7 @@ __global__ void __launch_bounds__(LIST_THREADS) assign_exact_list_kernel(const f
 			}
 		}
 		#pragma unroll
-		for (int p = 0; p < LIST_PB; ++p) {
+		for (int p = 0; p < PB; ++p) {
 			// Distances are >= +0, so their bit patterns order like the values: the warp's smallest
 			// distance, then the lowest index among the means that have it (a thread without a mean
 			// holds infinity and the index 0xffffffff).
@@ -391,14 +399,14 @@ static cudaError_t launch_list_small(const float* pts, const float* means, uint3
 
 size_t list_split_scratch_bytes()
 {
-	return (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB * sizeof(unsigned long long) + (size_t)LIST_SPLIT_MAX_BLOCKS * sizeof(uint32_t);
+	return (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB_WIDE * sizeof(unsigned long long) + (size_t)LIST_SPLIT_MAX_BLOCKS * sizeof(uint32_t);
 }
 
 cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* asg, const Shape& s,
 	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix, void* split_scratch)
 {
 	unsigned long long* split_keys = reinterpret_cast<unsigned long long*>(split_scratch);
-	uint32_t* split_arrive = split_scratch ? reinterpret_cast<uint32_t*>(split_keys + (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB) : nullptr;
+	uint32_t* split_arrive = split_scratch ? reinterpret_cast<uint32_t*>(split_keys + (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB_WIDE) : nullptr;
 	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
 	if (list != nullptr && fix == nullptr && s.dim <= LIST_SMALL_MAX_DIM && (uint64_t)s.k * s.dim <= LIST_SMALL_MAX_FLOATS) {
 		switch (s.dim) {
@@ -421,7 +429,12 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 		}
 	}
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
-		const size_t points_bytes = (size_t)LIST_PB * ((s.dim + 3) & ~3u) * sizeof(float);
+		// Every group of points walks all means: with long rows and many means (megabytes of them) the
+		// re-reads through L2 dominate, and sixteen points per group cut them fourfold.
+		const bool wide = fix == nullptr && (size_t)s.k * s.dim * sizeof(float) >= (1u << 20) &&
+			(size_t)LIST_PB_WIDE * ((s.dim + 3) & ~3u) * sizeof(float) <= 64 * 1024;
+		const int pb = wide ? LIST_PB_WIDE : LIST_PB;
+		const size_t points_bytes = (size_t)pb * ((s.dim + 3) & ~3u) * sizeof(float);
 		size_t lsmem = points_bytes + (s.soa_means ? 0 : (size_t)LIST_THREADS * 33 * sizeof(float));
 		// room for all means (the kernel uses it when the list is long): at most 64 KiB, so that
 		// several blocks still share an SM
@@ -429,16 +442,18 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 		const uint32_t resident_ok = resident_bytes <= 64 * 1024 ? 1u : 0u;
 		if (resident_ok && resident_bytes > lsmem) lsmem = resident_bytes;
 		const uint32_t lgrid = (uint32_t)sm_count * 8;
-#define BKM_LAUNCH_LIST(SOA, SOAM) do { \
-		auto kern = assign_exact_list_kernel<SOA, SOAM>; \
+#define BKM_LAUNCH_LIST_PB(SOA, SOAM, PBV) do { \
+		auto kern = assign_exact_list_kernel<SOA, SOAM, PBV>; \
 		if (lsmem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lsmem); if (e != cudaSuccess) return e; } \
 		kern<<<lgrid, LIST_THREADS, lsmem, stream>>>(pts, means, asg, s.n, s.k, s.dim, list, list_count, \
 			fix ? fix->acc : nullptr, fix ? fix->counts : nullptr, resident_ok, split_keys, split_arrive); \
 	} while (0)
+#define BKM_LAUNCH_LIST(SOA, SOAM) do { if (wide) BKM_LAUNCH_LIST_PB(SOA, SOAM, LIST_PB_WIDE); else BKM_LAUNCH_LIST_PB(SOA, SOAM, LIST_PB); } while (0)
 		if (s.soa && s.soa_means) BKM_LAUNCH_LIST(true, true);
 		else if (s.soa && !s.soa_means) BKM_LAUNCH_LIST(true, false);
 		else if (!s.soa && s.soa_means) BKM_LAUNCH_LIST(false, true);
 		else BKM_LAUNCH_LIST(false, false);
+#undef BKM_LAUNCH_LIST_PB
 #undef BKM_LAUNCH_LIST
 		return cudaGetLastError();
 	}
