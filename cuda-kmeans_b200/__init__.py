@@ -39,6 +39,7 @@ SYMBOLS = [
     "bkm_kmeans_host_f32", "bkm_update_noalloc_f32", "bkm_selftest_wait_timeout", "bkm_assign_plan",
     "bkm_noalloc_check", "bkm_peer_export", "bkm_peer_open", "bkm_peer_buffer", "bkm_peer_attach", "bkm_peer_enable",
     "bkm_peer_layout", "bkm_run_ready", "bkm_bucket_sums_f32", "bkm_probe_atomics_f32",
+    "bkm_kmeans_host_f64",
 ]
 
 
@@ -116,6 +117,7 @@ def lib():
     L.bkm_run_ready.argtypes = [vp]
     L.bkm_bucket_sums_f32.argtypes = [vp, vp, vp, u64, u32, u32, ci, ci, vp, sz, vp]
     L.bkm_probe_atomics_f32.argtypes = [vp, u64, u32, u32, ci, ci, u32, vp]
+    L.bkm_kmeans_host_f64.argtypes = [vp, vp, vp, u64, u32, u32, u32, ci, ci, ci]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("bkm_last_error", "bkm_workspace_bytes"):
@@ -255,6 +257,19 @@ def kmeans_host(points, means, n, k, dim, iters, layout=LAYOUT_AOS, layout_means
         raise ValueError("array sizes do not match n, k, dim")
     asg = np.empty(n, dtype=np.uint32)
     check(lib().bkm_kmeans_host_f32(pts.ctypes.data, out_means.ctypes.data, asg.ctypes.data,
+                                    n, k, dim, iters, layout, layout_means, device))
+    return out_means, asg
+
+
+def kmeans_host_f64(points, means, n, k, dim, iters, layout=LAYOUT_AOS, layout_means=None, device=0):
+    """Whole job in fp64 on HOST arrays (bkm_kmeans_host_f64): returns (final means, assignment)."""
+    layout_means = layout if layout_means is None else layout_means
+    pts = np.ascontiguousarray(points, dtype=np.float64).reshape(-1)
+    out_means = np.ascontiguousarray(means, dtype=np.float64).reshape(-1).copy()
+    if pts.size != n * dim or out_means.size != k * dim:
+        raise ValueError("array sizes do not match n, k, dim")
+    asg = np.empty(n, dtype=np.uint32)
+    check(lib().bkm_kmeans_host_f64(pts.ctypes.data, out_means.ctypes.data, asg.ctypes.data,
                                     n, k, dim, iters, layout, layout_means, device))
     return out_means, asg
 

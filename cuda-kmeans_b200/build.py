@@ -13,8 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbkm.so")
-SOURCES = ["api.cu", "assign_simt.cu", "assign_tc.cu", "assign_tc_pair.cu", "update.cu", "no_alloc.cu"]
-HEADERS = ["common.cuh", "kernels.cuh", "ptx.cuh", "tc_common.cuh", os.path.join("..", "..", "include", "bkm.h")]
+SOURCES = ["api.cu", "assign_simt.cu", "assign_tc.cu", "assign_tc_pair.cu", "update.cu", "no_alloc.cu", "f64.cu"]
+HEADERS = ["common.cuh", "kernels.cuh", "ptx.cuh", "tc_common.cuh", "keys.cuh", os.path.join("..", "..", "include", "bkm.h")]
 CLI_SRC = os.path.join(HERE, "cli", "bkm_kmeans.cpp")
 CLI = os.path.join(HERE, "bkm-kmeans")
 CLI2_SRC = os.path.join(HERE, "cli", "bkm_bucketing.cpp")

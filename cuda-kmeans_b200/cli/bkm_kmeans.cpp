@@ -10,7 +10,8 @@
  * Algorithms: b200 (automatic variants), b200_exact, b200_simt, b200_tc, serial (the built-in
  * single-thread check, small sizes only).  Flags that tune the reference's own kernels
  * (--cudaBlockSize, --cudaBlockCount, --cudaSharedMemorySize, --privatizedCopies,
- * --itemsPerThread, --regsCache) are accepted and ignored; --double and --Rscript are refused.
+ * --itemsPerThread, --regsCache) are accepted and ignored; --Rscript is refused; --double runs the
+ * library's fp64 path (reference arithmetic in double; one GPU).
  * The inputs are the reference executable's own for the same --N --k --dim --seed --layout
  * (reference_data.hpp restates its generator call for call); without --seed the reference draws a
  * random seed, this harness uses 42.  --dumpInputs <file> writes them out (with --dryRun: and stops).
@@ -40,7 +41,7 @@ namespace {
 struct Options {
 	uint64_t n = 10240;
 	uint32_t k = 128, dim = 20, iterations = 1, seed = 42, gpus = 1;
-	bool assignment_only = false, verify = false, dry_run = false;
+	bool assignment_only = false, verify = false, dry_run = false, use_double = false;
 	std::string algorithm = "b200", layout = "aos", layout_means, dump_inputs;
 };
 
@@ -49,7 +50,7 @@ struct Options {
 	std::cout << "Invalid arguments: " << what << std::endl << std::endl
 		<< "Usage: bkm-kmeans [--N n] [--k k] [--dim d] [--iterations i | --assignmentOnly] [--seed s]\n"
 		<< "                  [--algorithm b200|b200_exact|b200_simt|b200_tc|serial] [--layout aos|soa]\n"
-		<< "                  [--layoutMeans aos|soa] [--verify] [--dryRun] [--dumpInputs file] [--gpus g]\n"
+		<< "                  [--layoutMeans aos|soa] [--verify] [--dryRun] [--dumpInputs file] [--gpus g] [--double]\n"
 		<< "Integers take the suffixes k, M, G (powers of 1024)." << std::endl;
 	std::exit(1);
 }
@@ -99,7 +100,7 @@ Options parse(int argc, char** argv)
 		else if (a == "gpus") o.gpus = (uint32_t)parse_int(a, value());
 		else if (a == "cudaBlockSize" || a == "cudaBlockCount" || a == "cudaSharedMemorySize" || a == "privatizedCopies" ||
 			a == "itemsPerThread" || a == "regsCache") (void)value();
-		else if (a == "double") usage_error("--double: the B200 kernels are fp32 only");
+		else if (a == "double") o.use_double = true;
 		else if (a == "Rscript") usage_error("--Rscript is not supported");
 		else usage_error("unknown argument '--" + a + "'");
 	}
@@ -108,6 +109,7 @@ Options parse(int argc, char** argv)
 	if (o.dim < 1 || o.k < 1 || o.n < 1 || o.iterations < 1) usage_error("N, k, dim and iterations must be positive");
 	if (o.gpus < 1 || o.gpus > 8) usage_error("--gpus must be 1..8");
 	if (o.gpus > 1 && o.assignment_only) usage_error("--assignmentOnly runs on one GPU");
+	if (o.use_double && o.gpus > 1) usage_error("--double runs on one GPU");
 	for (const std::string* l : {&o.layout, &o.layout_means})
 		if (*l != "aos" && *l != "soa") usage_error("layout must be aos or soa");
 	return o;
@@ -116,7 +118,8 @@ Options parse(int argc, char** argv)
 inline size_t at(bool soa, uint64_t i, uint32_t j, uint64_t rows, uint32_t dim) { return soa ? (size_t)j * rows + i : (size_t)i * dim + j; }
 
 // The reference executable's inputs for these arguments (k-means.cpp:205-210): see reference_data.hpp.
-void generate(const Options& o, bool soa, bool soa_means, std::vector<float>& data, std::vector<float>& means)
+template<typename F>
+void generate(const Options& o, bool soa, bool soa_means, std::vector<F>& data, std::vector<F>& means)
 {
 	refdata::clustered_points(data, o.n, o.k, o.dim, o.seed, soa);
 	refdata::shuffled_means(data, means, o.n, o.k, o.dim, o.seed, soa, soa_means);
@@ -124,13 +127,14 @@ void generate(const Options& o, bool soa, bool soa_means, std::vector<float>& da
 
 // Raw dump of the generated inputs (for comparing them with the reference's): three 64-bit
 // integers n, k, dim, then the data and the initial means as 32-bit floats in their layouts.
-void dump_inputs(const std::string& path, const Options& o, const std::vector<float>& data, const std::vector<float>& means)
+template<typename F>
+void dump_inputs(const std::string& path, const Options& o, const std::vector<F>& data, const std::vector<F>& means)
 {
 	FILE* f = std::fopen(path.c_str(), "wb");
 	if (!f) throw std::runtime_error("cannot open '" + path + "' for writing");
 	const uint64_t head[3] = {o.n, o.k, o.dim};
-	bool ok = std::fwrite(head, sizeof(head), 1, f) == 1 && std::fwrite(data.data(), sizeof(float), data.size(), f) == data.size() &&
-		std::fwrite(means.data(), sizeof(float), means.size(), f) == means.size();
+	bool ok = std::fwrite(head, sizeof(head), 1, f) == 1 && std::fwrite(data.data(), sizeof(F), data.size(), f) == data.size() &&
+		std::fwrite(means.data(), sizeof(F), means.size(), f) == means.size();
 	ok = std::fclose(f) == 0 && ok;
 	if (!ok) throw std::runtime_error("writing '" + path + "' failed");
 }
@@ -138,27 +142,28 @@ void dump_inputs(const std::string& path, const Options& o, const std::vector<fl
 // Single-thread Lloyd iterations with the semantics of the reference's serial algorithm
 // (serial.hpp:21-96): Euclidean distance summed in dimension order, lowest index wins ties, an
 // empty cluster gets the zero vector.  Used by --verify and --algorithm serial.
-void serial_kmeans(const Options& o, bool soa, bool soa_means, const std::vector<float>& data, std::vector<float> means,
-	uint32_t iters, std::vector<float>& means_out, std::vector<uint32_t>& asg)
+template<typename F>
+void serial_kmeans(const Options& o, bool soa, bool soa_means, const std::vector<F>& data, std::vector<F> means,
+	uint32_t iters, std::vector<F>& means_out, std::vector<uint32_t>& asg)
 {
 	asg.assign(o.n, 0);
 	std::vector<uint32_t> counts(o.k);
 	for (uint32_t it = 0; it < iters; ++it) {
 		for (uint64_t i = 0; i < o.n; ++i) {
 			uint32_t best = 0;
-			float best_d = 0.0f;
+			F best_d = (F)0;
 			for (uint32_t m = 0; m < o.k; ++m) {
-				float sum = 0.0f;
+				F sum = (F)0;
 				for (uint32_t j = 0; j < o.dim; ++j) {
-					const float diff = data[at(soa, i, j, o.n, o.dim)] - means[at(soa_means, m, j, o.k, o.dim)];
+					const F diff = data[at(soa, i, j, o.n, o.dim)] - means[at(soa_means, m, j, o.k, o.dim)];
 					sum += diff * diff;
 				}
-				const float dist = std::sqrt(sum);
+				const F dist = std::sqrt(sum);
 				if (m == 0 || best_d > dist) { best_d = dist; best = m; }
 			}
 			asg[i] = best;
 		}
-		std::fill(means.begin(), means.end(), 0.0f);
+		std::fill(means.begin(), means.end(), (F)0);
 		std::fill(counts.begin(), counts.end(), 0u);
 		for (uint64_t i = 0; i < o.n; ++i) {
 			++counts[asg[i]];
@@ -166,7 +171,7 @@ void serial_kmeans(const Options& o, bool soa, bool soa_means, const std::vector
 		}
 		for (uint32_t m = 0; m < o.k; ++m)
 			if (counts[m])
-				for (uint32_t j = 0; j < o.dim; ++j) means[at(soa_means, m, j, o.k, o.dim)] /= (float)counts[m];
+				for (uint32_t j = 0; j < o.dim; ++j) means[at(soa_means, m, j, o.k, o.dim)] /= (F)counts[m];
 	}
 	means_out = means;
 }
@@ -179,6 +184,68 @@ void check(int rc)
 double now_ms()
 {
 	return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// --double: the whole job in fp64 (k-means.cpp:340-345 runs every algorithm with F = double then).  The
+// library has one fp64 path (reference arithmetic in double, bkm_kmeans_host_f64); the variant names
+// that select fp32 kernels all map to it.  The timed region includes the copies to and from the GPU.
+int run_double(const Options& o, bool soa, bool soa_means)
+{
+	std::vector<double> data, means, got_means;
+	std::vector<uint32_t> got_asg;
+	std::cerr << "Generating input data (" << o.n << " x " << o.dim << ") ..." << std::endl;
+	std::cerr << "Seed is set to " << o.seed << std::endl;
+	generate(o, soa, soa_means, data, means);
+	if (!o.dump_inputs.empty()) {
+		dump_inputs(o.dump_inputs, o, data, means);
+		if (o.dry_run) return 0;
+	}
+	const uint32_t iters = o.assignment_only ? 1u : o.iterations;
+	std::cerr << "Initializing ... 0 ms" << std::endl;
+	std::cerr << "Running (" << iters << " iterations) ... ";
+	double run_ms = 0.0;
+	if (o.algorithm == "serial") {
+		const double t0 = now_ms();
+		serial_kmeans(o, soa, soa_means, data, means, iters, got_means, got_asg);
+		run_ms = now_ms() - t0;
+	} else {
+		got_means = means;
+		got_asg.resize(o.n);
+		const double t0 = now_ms();
+		check(bkm_kmeans_host_f64(data.data(), got_means.data(), got_asg.data(), o.n, o.k, o.dim, iters,
+			soa ? BKM_LAYOUT_SOA : BKM_LAYOUT_AOS, soa_means ? BKM_LAYOUT_SOA : BKM_LAYOUT_AOS, 0));
+		run_ms = now_ms() - t0;
+	}
+	std::cout << run_ms / (double)iters;
+	std::cerr << " ms/iter (which is";
+	std::cout << " " << (run_ms * 1000000.0 / ((double)iters * o.dim * (double)o.n));
+	std::cerr << " ns/input float)";
+	std::cout << std::endl;
+	if (o.verify && o.algorithm != "serial") {
+		std::cerr << "Verifying results ... ";
+		std::vector<double> want_means;
+		std::vector<uint32_t> want_asg;
+		serial_kmeans(o, soa, soa_means, data, means, iters, want_means, want_asg);
+		uint64_t errors = 0;
+		for (uint64_t i = 0; i < o.n; ++i) errors += got_asg[i] != want_asg[i];
+		if (!o.assignment_only) {
+			double total = 0.0;
+			for (uint32_t m = 0; m < o.k; ++m) {
+				double d2 = 0.0;
+				for (uint32_t j = 0; j < o.dim; ++j) {
+					const double d = got_means[at(soa_means, m, j, o.k, o.dim)] - want_means[at(soa_means, m, j, o.k, o.dim)];
+					d2 += d * d;
+				}
+				const double dist = std::sqrt(d2);
+				total += dist;
+				if (dist > 0.1) ++errors;
+			}
+			if (total / o.k > 0.01) ++errors;
+		}
+		std::cerr << (errors == 0 ? "OK" : "FAILED") << std::endl;
+		if (errors) return 3;
+	}
+	return 0;
 }
 
 int run(const Options& o)
@@ -198,6 +265,7 @@ int run(const Options& o)
 		return 0;
 	}
 
+	if (o.use_double) return run_double(o, soa, soa_means);
 	std::vector<float> data, means, got_means;
 	std::vector<uint32_t> got_asg;
 	std::cerr << "Generating input data (" << o.n << " x " << o.dim << ") ..." << std::endl;

@@ -36,26 +36,30 @@ inline std::size_t at(bool soa, std::size_t item, std::size_t d, std::size_t ite
 	return soa ? d * items + item : item * dim + d;
 }
 
-inline void clustered_points(std::vector<float>& data, std::size_t n, std::size_t k, std::size_t dim, std::size_t seed, bool soa)
+// F = float, or double for the reference's --double mode (the double-typed distributions consume
+// the generator differently, so the two streams are unrelated).
+template<typename F>
+inline void clustered_points(std::vector<F>& data, std::size_t n, std::size_t k, std::size_t dim, std::size_t seed, bool soa)
 {
 	if (n < k) throw std::runtime_error("N must not be smaller than k (the first k points are the cluster centres)");
 	std::mt19937 gen((unsigned int)seed);
-	std::uniform_real_distribution<float> centre(0.0f, 1.0f);
+	std::uniform_real_distribution<F> centre((F)0, (F)1);
 	std::uniform_int_distribution<std::size_t> which(0, k - 1);
-	std::normal_distribution<float> noise(0.0f, 0.025f);
+	std::normal_distribution<F> noise((F)0, (F)0.025);
 	data.resize(n * dim);
 	for (std::size_t i = 0; i < k; ++i)
 		for (std::size_t d = 0; d < dim; ++d) data[at(soa, i, d, n, dim)] = centre(gen);
 	for (std::size_t i = k; i < n; ++i) {
 		const std::size_t c = which(gen);
 		for (std::size_t d = 0; d < dim; ++d) {
-			const float offset = noise(gen);
+			const F offset = noise(gen);
 			data[at(soa, i, d, n, dim)] = offset + data[at(soa, c, d, n, dim)];
 		}
 	}
 }
 
-inline void shuffled_means(const std::vector<float>& data, std::vector<float>& means, std::size_t n, std::size_t k, std::size_t dim,
+template<typename F>
+inline void shuffled_means(const std::vector<F>& data, std::vector<F>& means, std::size_t n, std::size_t k, std::size_t dim,
 	std::size_t seed, bool soa, bool soa_means)
 {
 	std::vector<std::uint32_t> order(n);

@@ -350,6 +350,15 @@ int bkm_kmeans_host_f32(const float* host_points, float* means, uint32_t* assign
                         uint64_t n, uint32_t k, uint32_t dim, uint32_t iters,
                         int layout, int layout_means, int device);
 
+/* The same whole job in fp64, for the reference executable's --double mode (k-means.cpp:313-315,
+ * 340-345: every algorithm there is instantiated for double as well).  Not the tuned path: one plain
+ * kernel per step with the reference's arithmetic in double, so the assignment equals the serial
+ * algorithm's (headers/serial.hpp:21-35 with F = double) bit for bit for the same means; sums are
+ * accumulated with double atomics (means agree with the serial loop to rounding). */
+int bkm_kmeans_host_f64(const double* host_points, double* means, uint32_t* assignment,
+                        uint64_t n, uint32_t k, uint32_t dim, uint32_t iters,
+                        int layout, int layout_means, int device);
+
 #ifdef __cplusplus
 }
 #endif

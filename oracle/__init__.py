@@ -42,6 +42,12 @@ def _load_port():
     lib.okm_update_f64.restype = None
     lib.okm_kmeans_f32.argtypes = [_f32p, _f32p, _f32p, _u32p, _u32p, ctypes.c_void_p, _u64, _u32, _u32, _u32, _int, _int]
     lib.okm_kmeans_f32.restype = None
+    lib.okm_assign_range_d.argtypes = [_f64p, _f64p, _u32p, _u64, _u32, _u32, _int, _int, _u64, _u64]
+    lib.okm_assign_range_d.restype = None
+    lib.okm_update_d.argtypes = [_f64p, _u32p, _f64p, _u32p, _u64, _u32, _u32, _int, _int]
+    lib.okm_update_d.restype = None
+    lib.okm_kmeans_d.argtypes = [_f64p, _f64p, _f64p, _u32p, _u32p, _u64, _u32, _u32, _u32, _int, _int]
+    lib.okm_kmeans_d.restype = None
     return lib
 
 
@@ -159,6 +165,8 @@ class _Ref:
         lib.ref_kmeans_f32.restype = _int
         lib.ref_assign_f32.argtypes = [_int, _int, _u64, _u64, _u64, _f32p, _f32p, _u32p]
         lib.ref_assign_f32.restype = _int
+        lib.ref_kmeans_f64.argtypes = [_int, _int, _u64, _u64, _u64, _u64, _f64p, _f64p, _f64p, _u32p]
+        lib.ref_kmeans_f64.restype = _int
         self._lib = lib
         self.path = path
 
@@ -172,6 +180,15 @@ class _Ref:
             raise RuntimeError("ref_kmeans_f32 failed")
         return out_means, out_asg
 
+    def kmeans_f64(self, data, means, n, k, d, iters, layout=AOS, layout_means=None):
+        layout_means = layout if layout_means is None else layout_means
+        data, means = _f64(data), _f64(means)
+        out_means = np.empty(k * d, dtype=np.float64)
+        out_asg = np.empty(n, dtype=np.uint32)
+        if self._lib.ref_kmeans_f64(layout, layout_means, d, k, n, iters, data, means, out_means, out_asg) != 0:
+            raise RuntimeError("ref_kmeans_f64 failed")
+        return out_means, out_asg
+
     def assign(self, data, means, n, k, d, layout=AOS, layout_means=None):
         layout_means = layout if layout_means is None else layout_means
         data, means = _f32(data), _f32(means)
@@ -180,6 +197,42 @@ class _Ref:
         if rc != 0:
             raise RuntimeError("ref_assign_f32 failed")
         return out_asg
+
+
+def _f64(a):
+    return np.ascontiguousarray(a, dtype=np.float64).reshape(-1)
+
+
+def kmeans_f64(data, means, n, k, d, iters, layout=AOS, layout_means=None):
+    """Full fixed-iteration run in double (serial.hpp:89-96 with F = double): (means, assignment)."""
+    layout_means = layout if layout_means is None else layout_means
+    data = _f64(data)
+    cur = _f64(means).copy()
+    prev = np.empty_like(cur)
+    asg = np.zeros(n, dtype=np.uint32)
+    sizes = np.zeros(k, dtype=np.uint32)
+    _port().okm_kmeans_d(data, cur, prev, asg, sizes, n, k, d, iters, layout, layout_means)
+    return cur, asg
+
+
+def assign_f64(data, means, n, k, d, layout=AOS, layout_means=None, threads=1):
+    """Nearest-mean index of every point in double (serial.hpp:21-42 with F = double)."""
+    layout_means = layout if layout_means is None else layout_means
+    data, means = _f64(data), _f64(means)
+    out = np.empty(n, dtype=np.uint32)
+    lib = _port()
+    _parallel(lambda b, e: lib.okm_assign_range_d(data, means, out, n, k, d, layout, layout_means, b, e), n, threads)
+    return out
+
+
+def update_d(data, assignment, n, k, d, layout=AOS, layout_means=None):
+    """(means, sizes) of the update step in double (serial.hpp:44-73 with F = double)."""
+    layout_means = layout if layout_means is None else layout_means
+    data, assignment = _f64(data), _u32a(assignment)
+    means = np.empty(k * d, dtype=np.float64)
+    sizes = np.empty(k, dtype=np.uint32)
+    _port().okm_update_d(data, assignment, means, sizes, n, k, d, layout, layout_means)
+    return means, sizes
 
 
 class _RefData:
@@ -191,6 +244,8 @@ class _RefData:
         lib.ref_make_inputs_f32.restype = _int
         lib.ref_make_bucketing_inputs_f32.argtypes = [_u64, _u64, _u32, _u64, _f32p, _u32p]
         lib.ref_make_bucketing_inputs_f32.restype = _int
+        lib.ref_make_inputs_f64.argtypes = [_int, _int, _u64, _u64, _u64, _u64, _f64p, _f64p]
+        lib.ref_make_inputs_f64.restype = _int
         self._lib = lib
         self.path = path
 
@@ -201,6 +256,15 @@ class _RefData:
         means = np.empty(k * d, dtype=np.float32)
         if self._lib.ref_make_inputs_f32(layout, layout_means, n, k, d, seed, data, means) != 0:
             raise RuntimeError("ref_make_inputs_f32 failed")
+        return data, means
+
+    def kmeans_inputs_f64(self, n, k, d, seed, layout=AOS, layout_means=None):
+        """The same for the reference executable's --double mode."""
+        layout_means = layout if layout_means is None else layout_means
+        data = np.empty(n * d, dtype=np.float64)
+        means = np.empty(k * d, dtype=np.float64)
+        if self._lib.ref_make_inputs_f64(layout, layout_means, n, k, d, seed, data, means) != 0:
+            raise RuntimeError("ref_make_inputs_f64 failed")
         return data, means
 
     def bucketing_inputs(self, count, count_idx, k, seed):

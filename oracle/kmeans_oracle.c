@@ -165,3 +165,69 @@ void okm_kmeans_f32(const float *data, float *means, float *prev, uint32_t *assi
 		if (trace) memcpy(trace + (size_t)it * kd, means, kd * sizeof(float));
 	}
 }
+
+/* ---- the same algorithm with F = double (the reference executable's --double mode) ----------
+ * headers/serial.hpp is a template on F; with F = double every sum, difference and square root
+ * below is done in double (headers/metric_policies.hpp:50-64 for the metric). */
+
+static inline double okm_dist_d(const double *data, size_t i, int layout, size_t n,
+	const double *means, size_t m, int layout_means, size_t k, size_t d)
+{
+	double sum = 0.0;
+	for (size_t j = 0; j < d; ++j) {
+		double diff = data[okm_at(layout, i, j, n, d)] - means[okm_at(layout_means, m, j, k, d)];
+		sum += diff * diff;
+	}
+	return sqrt(sum);
+}
+
+/* headers/serial.hpp:21-42 with F = double. */
+void okm_assign_range_d(const double *data, const double *means, uint32_t *assignment,
+	uint64_t n, uint32_t k, uint32_t d, int layout, int layout_means, uint64_t begin, uint64_t end)
+{
+	for (uint64_t i = begin; i < end; ++i) {
+		uint32_t nearest = 0;
+		double min_dist = okm_dist_d(data, i, layout, n, means, 0, layout_means, k, d);
+		for (uint32_t m = 1; m < k; ++m) {
+			double dist = okm_dist_d(data, i, layout, n, means, m, layout_means, k, d);
+			if (min_dist > dist) {
+				min_dist = dist;
+				nearest = m;
+			}
+		}
+		assignment[i] = nearest;
+	}
+}
+
+/* headers/serial.hpp:44-73 with F = double. */
+void okm_update_d(const double *data, const uint32_t *assignment, double *means, uint32_t *sizes,
+	uint64_t n, uint32_t k, uint32_t d, int layout, int layout_means)
+{
+	for (uint32_t m = 0; m < k; ++m) {
+		sizes[m] = 0;
+		for (uint32_t j = 0; j < d; ++j) means[okm_at(layout_means, m, j, k, d)] = 0.0;
+	}
+	for (uint64_t i = 0; i < n; ++i) {
+		uint32_t target = assignment[i];
+		++sizes[target];
+		for (uint32_t j = 0; j < d; ++j)
+			means[okm_at(layout_means, target, j, k, d)] += data[okm_at(layout, i, j, n, d)];
+	}
+	for (uint32_t m = 0; m < k; ++m) {
+		if (sizes[m] == 0) continue;
+		double divisor = (double)sizes[m];
+		for (uint32_t j = 0; j < d; ++j) means[okm_at(layout_means, m, j, k, d)] /= divisor;
+	}
+}
+
+/* headers/serial.hpp:89-96 with F = double. */
+void okm_kmeans_d(const double *data, double *means, double *prev, uint32_t *assignment,
+	uint32_t *sizes, uint64_t n, uint32_t k, uint32_t d, uint32_t iters, int layout, int layout_means)
+{
+	size_t kd = (size_t)k * d;
+	for (uint32_t it = 0; it < iters; ++it) {
+		memcpy(prev, means, kd * sizeof(double));
+		okm_assign_range_d(data, prev, assignment, n, k, d, layout, layout_means, 0, n);
+		okm_update_d(data, assignment, means, sizes, n, k, d, layout, layout_means);
+	}
+}

@@ -47,6 +47,33 @@ extern "C" int ref_make_inputs_f32(int layout, int layoutMeans, std::uint64_t n,
 	return 1;
 }
 
+/* The same with --double: generate_clustered_data<double> and prepare_means<double> draw from
+ * double-typed distributions, which consume the generator differently. */
+template<class LAYOUT, class LAYOUT_MEANS>
+static int make_double(std::size_t n, std::size_t k, std::size_t dim, std::size_t seed, double* dataOut, double* meansOut)
+{
+	std::vector<double> data, means;
+	generate_clustered_data<double, LAYOUT>(data, n, k, dim, seed);
+	prepare_means<double, std::uint32_t, LAYOUT, LAYOUT_MEANS>(data, means, n, k, dim, true, seed);
+	std::memcpy(dataOut, data.data(), sizeof(double) * LAYOUT::size(n, dim));
+	std::memcpy(meansOut, means.data(), sizeof(double) * LAYOUT_MEANS::size(k, dim));
+	return 0;
+}
+
+extern "C" int ref_make_inputs_f64(int layout, int layoutMeans, std::uint64_t n, std::uint64_t k, std::uint64_t dim,
+	std::uint64_t seed, double* dataOut, double* meansOut)
+{
+	try {
+		if (layout == 0 && layoutMeans == 0) return make_double<AoSLayoutPolicy<1>, AoSLayoutPolicy<1>>(n, k, dim, seed, dataOut, meansOut);
+		if (layout == 0 && layoutMeans == 1) return make_double<AoSLayoutPolicy<1>, SoALayoutPolicy<1>>(n, k, dim, seed, dataOut, meansOut);
+		if (layout == 1 && layoutMeans == 0) return make_double<SoALayoutPolicy<1>, AoSLayoutPolicy<1>>(n, k, dim, seed, dataOut, meansOut);
+		if (layout == 1 && layoutMeans == 1) return make_double<SoALayoutPolicy<1>, SoALayoutPolicy<1>>(n, k, dim, seed, dataOut, meansOut);
+	} catch (...) {
+		return 2;
+	}
+	return 1;
+}
+
 /* The inputs of the reference's bucketing executable (bucketing-cuda.cpp:172-173): `count` uniform
  * floats in [0,1) and `count_idx` uniform indices in [0,k), each from its own generator seeded alike. */
 extern "C" int ref_make_bucketing_inputs_f32(std::uint64_t count, std::uint64_t countIdx, std::uint32_t k, std::uint64_t seed,

@@ -48,9 +48,37 @@ int assign(std::size_t dim, std::size_t k, std::size_t n, const float* data, con
 	return 0;
 }
 
+template<class LAYOUT, class LAYOUT_MEANS>
+int kmeans_double(std::size_t dim, std::size_t k, std::size_t n, std::size_t iters, const double* data,
+	const double* means, double* meansOut, std::uint32_t* assignmentOut)
+{
+	std::vector<double> vData(data, data + LAYOUT::size(n, dim));
+	std::vector<double> vMeans(means, means + LAYOUT_MEANS::size(k, dim));
+	SerialKMeansAlgorithm<double, std::uint32_t, LAYOUT, LAYOUT_MEANS> algorithm;
+	algorithm.initialize(dim, k, n, iters, vData, vMeans);
+	algorithm.run();
+	std::memcpy(meansOut, algorithm.getMeans().data(), sizeof(double) * LAYOUT_MEANS::size(k, dim));
+	std::memcpy(assignmentOut, algorithm.getAssignment().data(), sizeof(std::uint32_t) * n);
+	algorithm.cleanup();
+	return 0;
+}
+
 } // namespace
 
 extern "C" {
+
+/* SerialKMeansAlgorithm<double, ...>: what the reference executable runs with --double. */
+int ref_kmeans_f64(int layout, int layoutMeans, std::uint64_t dim, std::uint64_t k, std::uint64_t n,
+	std::uint64_t iters, const double* data, const double* means, double* meansOut, std::uint32_t* assignmentOut)
+{
+	using A = AoSLayoutPolicy<1>;
+	using S = SoALayoutPolicy<1>;
+	if (layout == 0 && layoutMeans == 0) return kmeans_double<A, A>(dim, k, n, iters, data, means, meansOut, assignmentOut);
+	if (layout == 1 && layoutMeans == 1) return kmeans_double<S, S>(dim, k, n, iters, data, means, meansOut, assignmentOut);
+	if (layout == 0 && layoutMeans == 1) return kmeans_double<A, S>(dim, k, n, iters, data, means, meansOut, assignmentOut);
+	if (layout == 1 && layoutMeans == 0) return kmeans_double<S, A>(dim, k, n, iters, data, means, meansOut, assignmentOut);
+	return 1;
+}
 
 int ref_kmeans_f32(int layout, int layoutMeans, std::uint64_t dim, std::uint64_t k, std::uint64_t n,
 	std::uint64_t iters, const float* data, const float* means, float* meansOut, std::uint32_t* assignmentOut)

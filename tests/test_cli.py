@@ -32,7 +32,8 @@ def test_suffixes_and_defaults(cli):
 
 
 def test_invalid_arguments_exit_code_1(cli):
-    for bad in (["--N", "3x"], ["--bogus"], ["--assignmentOnly", "--iterations", "3"], ["--double"], ["--layout", "aos32"]):
+    for bad in (["--N", "3x"], ["--bogus"], ["--assignmentOnly", "--iterations", "3"], ["--double", "--gpus", "2"], ["--layout", "aos32"],
+                ["--Rscript"]):
         rc, out, _ = _run(cli, *bad)
         assert rc == 1, bad
         assert out.startswith("Invalid arguments:"), bad

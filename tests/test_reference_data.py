@@ -126,3 +126,71 @@ def test_bucketing_verify_on_gpu(cli_dir, args):
     assert "Verifying results ... OK" in p.stderr
     ms, ns = p.stdout.split()
     assert float(ms) > 0 and float(ns) > 0
+
+
+# ---- the fp64 path (the reference executable's --double mode) ------------------------------------
+
+def _dump_f64(cli_dir, tmp_path, n, k, d, seed, lay, laym):
+    path = str(tmp_path / "inputs64.bin")
+    p = subprocess.run([os.path.join(cli_dir, "bkm-kmeans"), "--N", str(n), "--k", str(k), "--dim", str(d), "--seed", str(seed),
+                        "--layout", LAYOUTS[lay], "--layoutMeans", LAYOUTS[laym], "--double", "--dumpInputs", path, "--dryRun"],
+                       capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, (p.stdout, p.stderr)
+    raw = np.fromfile(path, dtype=np.uint8)
+    assert list(raw[:24].view(np.uint64)) == [n, k, d]
+    body = raw[24:].view(np.float64)
+    return body[:n * d], body[n * d:]
+
+
+def test_double_inputs_equal_the_reference_generator_golden(cli_dir, tmp_path, refdata_golden):
+    for i, (n, k, d, seed, lay, laym, iters) in enumerate(refdata_golden["kmeans_f64_cases"].tolist()):
+        data, means = _dump_f64(cli_dir, tmp_path, n, k, d, seed, lay, laym)
+        assert np.array_equal(data, refdata_golden["kmeans_f64_%d_data" % i])
+        assert np.array_equal(means, refdata_golden["kmeans_f64_%d_means" % i])
+
+
+def test_double_oracle_equals_the_reference_serial_golden(oracle_mod, refdata_golden):
+    """oracle.kmeans_f64 (serial.hpp restated with F = double) bit for bit against the reference's own
+    SerialKMeansAlgorithm<double> on the reference's own --double inputs."""
+    for i, (n, k, d, seed, lay, laym, iters) in enumerate(refdata_golden["kmeans_f64_cases"].tolist()):
+        means, asg = oracle_mod.kmeans_f64(refdata_golden["kmeans_f64_%d_data" % i], refdata_golden["kmeans_f64_%d_means" % i],
+                                           n, k, d, iters, lay, laym)
+        assert np.array_equal(means, refdata_golden["kmeans_f64_%d_out_means" % i])
+        assert np.array_equal(asg, refdata_golden["kmeans_f64_%d_out_assignment" % i])
+
+
+@pytest.mark.gpu
+def test_double_path_matches_the_oracle_on_gpu(pkg, torch_cuda, oracle_mod, refdata_golden):
+    """bkm_kmeans_host_f64: assignments bit for bit for one iteration (same means in), final means of
+    the whole run within 1e-9 relative (the sums are accumulated in another order), and the golden
+    trajectories of the reference."""
+    rng = np.random.default_rng(4)
+    for (n, k, d, lay, laym) in [(5000, 37, 7, 0, 1), (3000, 300, 33, 1, 1), (4096, 16, 2, 0, 0)]:
+        rows = rng.random((n, d))
+        data = rows.reshape(-1) if lay == 0 else np.ascontiguousarray(rows.T).reshape(-1)
+        m0 = rows[:k].reshape(-1) if laym == 0 else np.ascontiguousarray(rows[:k].T).reshape(-1)
+        got_means, got_asg = pkg.kmeans_host_f64(data, m0, n, k, d, 1, lay, laym)
+        assert np.array_equal(got_asg, oracle_mod.assign_f64(data, m0, n, k, d, lay, laym, threads=8))
+        want_means, _ = oracle_mod.update_d(data, got_asg, n, k, d, lay, laym)
+        assert np.allclose(got_means, want_means, rtol=1e-12, atol=1e-15)
+        got_means, got_asg = pkg.kmeans_host_f64(data, m0, n, k, d, 5, lay, laym)
+        want_means, want_asg = oracle_mod.kmeans_f64(data, m0, n, k, d, 5, lay, laym)
+        assert np.allclose(got_means, want_means, rtol=1e-9, atol=1e-12)
+        assert (got_asg != want_asg).mean() <= 1e-3
+    for i, (n, k, d, seed, lay, laym, iters) in enumerate(refdata_golden["kmeans_f64_cases"].tolist()):
+        got_means, got_asg = pkg.kmeans_host_f64(refdata_golden["kmeans_f64_%d_data" % i], refdata_golden["kmeans_f64_%d_means" % i],
+                                                 n, k, d, iters, lay, laym)
+        assert np.allclose(got_means, refdata_golden["kmeans_f64_%d_out_means" % i], rtol=1e-9, atol=1e-12)
+        assert (got_asg != refdata_golden["kmeans_f64_%d_out_assignment" % i]).mean() <= 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("args", [
+    ["--N", "16k", "--k", "64", "--dim", "8", "--iterations", "4"],
+    ["--N", "8k", "--k", "100", "--dim", "20", "--iterations", "2", "--layout", "soa", "--layoutMeans", "aos"],
+    ["--N", "8k", "--k", "32", "--dim", "4", "--assignmentOnly"],
+])
+def test_double_verify_on_gpu(cli_dir, args):
+    p = subprocess.run([os.path.join(cli_dir, "bkm-kmeans")] + args + ["--double", "--verify"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout, p.stderr)
+    assert "Verifying results ... OK" in p.stderr
