@@ -95,7 +95,7 @@ constexpr int LIST_PB_WIDE = 16;    // ... when every fetched mean should serve 
 constexpr uint32_t LIST_SPLIT_MAX_BLOCKS = 2048;   // grid size up to which a short list is shared between blocks
 
 template<bool SOA, bool SOAM, int PB>
-__global__ void __launch_bounds__(LIST_THREADS, 2) assign_exact_list_kernel(const float* __restrict__ pts,
+__global__ void __launch_bounds__(LIST_THREADS, PB > LIST_PB ? 2 : 3) assign_exact_list_kernel(const float* __restrict__ pts,
 	const float* __restrict__ means, uint32_t* __restrict__ asg, uint64_t n, uint32_t k, uint32_t d,
 	const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count,
 	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts, uint32_t resident_ok,

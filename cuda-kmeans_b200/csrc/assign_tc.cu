@@ -573,12 +573,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 			float xn = 0.0f;                       // |x|^2 of this thread's point, needed at the end of the block
 			#pragma unroll 1
 			for (uint32_t j = j_begin; j < j_end; ++j) {
-				if (ok) {
-					// one lane polls the barrier, the warp follows
-					bool w = true;
-					if (lane == 0) w = wait_or_abort<100>(&bars->acc_full[i], acc_use & 1u, abort_flag);
-					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
-				}
+				// the whole warp polls (one warp instruction either way, and no divergent region around it)
+				if (ok) ok = __all_sync(0xffffffffu, wait_or_abort<100>(&bars->acc_full[i], acc_use & 1u, abort_flag)) != 0;
 				++acc_use;
 				if (ok && nchunks > 0) {
 					ptx::tc_fence_after();

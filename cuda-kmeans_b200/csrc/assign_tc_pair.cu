@@ -317,11 +317,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 				const uint32_t c = c_step + u;
 				const uint32_t acc = c % P2_ACCS;
 				const uint32_t acc_release = acc_empty_base + acc * 8u;
-				if (ok) {
-					bool w = true;
-					if (lane == 0) w = pair_wait(&bars->acc_full[acc], (c / P2_ACCS) & 1u, abort_flag, peer_abort_addr);
-					ok = __shfl_sync(0xffffffffu, (int)w, 0) != 0;
-				}
+				// the whole warp polls (one warp instruction either way, and no divergent region around it)
+				if (ok) ok = __all_sync(0xffffffffu, pair_wait(&bars->acc_full[acc], (c / P2_ACCS) & 1u, abort_flag, peer_abort_addr)) != 0;
 				if (ok) {
 					ptx::tc_fence_after();
 					const uint32_t j = u >> 1, h = u & 1u;

@@ -51,9 +51,10 @@ __device__ __forceinline__ void chunk_update(const uint32_t (&v)[32], uint32_t k
 	// 16 + 32 + 8 integer instructions per chunk where a tournament takes 77 + 5.
 	const uint32_t b = min_of_32(p);
 	const uint32_t nb1 = ~b;                       // -(b + 1)
-	uint32_t r0 = 0xFFFFFFFFu, r1 = 0xFFFFFFFFu, r2 = 0xFFFFFFFFu, r3 = 0xFFFFFFFFu;
+	// (the chains start from their first keys: an add each instead of a constant and an add-and-minimum)
+	uint32_t r0 = p[0] + nb1, r1 = p[1] + nb1, r2 = p[2] + nb1, r3 = p[3] + nb1;
 	#pragma unroll
-	for (uint32_t t = 0; t < 32; t += 4) {
+	for (uint32_t t = 4; t < 32; t += 4) {
 		r0 = __viaddmin_u32(p[t], nb1, r0);
 		r1 = __viaddmin_u32(p[t + 1], nb1, r1);
 		r2 = __viaddmin_u32(p[t + 2], nb1, r2);
