@@ -265,8 +265,9 @@ __global__ void __launch_bounds__(256) merge_partials_kernel(const uint32_t* __r
 	}
 }
 
-// FULL: k is a whole number of mean tiles, so no accumulator column is padding and the epilogue runs
-// without its masked path.
+// FULL: k is a whole number of mean tiles of 128 or 256 columns, so no accumulator column is padding
+// and every warp takes its columns in pairs of 32-column chunks: the epilogue runs without its masked
+// path and without the odd-chunk branches.
 template<bool FULL>
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 	const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
@@ -583,7 +584,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						const uint32_t colbase = (first_chunk + c) * 32u;
 						const uint32_t taddr = tmem_base + ((q * 32u) << 16) + i * TC_NT_MAX + colbase;
 						const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
-						const bool two = c + 1 < nchunks;
+						const bool two = FULL ? true : c + 1 < nchunks;
 						uint32_t v0[32], v1[32];
 						ptx::tmem_ld32(taddr, v0);
 						if (two) ptx::tmem_ld32(taddr + 32, v1);
@@ -815,7 +816,7 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim);
 	const uint32_t jsplit = plan_jsplit(p);
 	const uint32_t grid_j = jsplit * std::min<uint32_t>(nblocks, (uint32_t)p->sm_count / jsplit);
-	auto kern = p->s.k == p->tm.k_pad ? assign_tc_kernel<true> : assign_tc_kernel<false>;
+	auto kern = (p->s.k == p->tm.k_pad && p->nt_cols % 128 == 0) ? assign_tc_kernel<true> : assign_tc_kernel<false>;
 	kern<<<jsplit > 1 ? grid_j : grid, TC_THREADS, SM_ALLOC, stream>>>(p->a_hi, p->a_lo, p->b_hi, p->b_lo,
 		p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles, p->s.k, p->tm.k_pad, p->nt_cols, kw, kchunks, ksteps_last, idesc,
 		ctl, slot, flag_list, margin_coef, jsplit, jsplit > 1 ? p->tp.partial : nullptr, p->tp.n_pad);
