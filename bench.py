@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--update", default="auto", choices=["auto", "shared", "global", "rows", "sorted"])
     ap.add_argument("--no-fuse", action="store_true",
                     help="keep the update a launch of its own where the assignment kernel could accumulate the sums")
+    ap.add_argument("--fuse-all", action="store_true",
+                    help="let the assignment kernel accumulate the sums wherever it can, also where the library's default keeps two passes")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
                     help="how the ranks exchange sums and sizes: NCCL all-reduce, or the library's peer-load kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -273,6 +275,8 @@ class Job:
             km.initialize(spec["dim"], spec["k"], self.count, 1, self.host_points.numpy(), self.host_means.numpy())
         if not fuse:
             km.set_option("fuse_update", 0)
+        elif args.fuse_all:
+            km.set_option("fuse_update", 2)
         if ctx["world"] > 1:
             ctx["join"](km)
         return km

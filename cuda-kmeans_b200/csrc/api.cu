@@ -242,8 +242,8 @@ int check_shape(uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_mea
 }
 
 // Enqueues one assignment pass (fast pass + exact re-check, or the exact kernel alone).
-// With `fused` set the tensor-core pass also accumulates the update sums and the re-check moves
-// the points it reassigns, so no update pass must follow.
+// With `fused` set the fast pass also accumulates the update sums and the re-check moves the
+// points it reassigns, so no update pass must follow.
 int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* asg, const bkm::Shape& s,
 	const Workspace& w, int slot, bkm::TcPlan* plan, float margin_scale, int sm_count, cudaStream_t stream,
 	cudaEvent_t mid, const bkm::FusedAcc* fused = nullptr)
@@ -254,7 +254,7 @@ int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* 
 		return BKM_OK;
 	}
 	if (variant == BKM_ASSIGN_SIMT) {
-		CUDA_TRY(bkm::launch_assign_simt(pts, w.sm, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream));
+		CUDA_TRY(bkm::launch_assign_simt(pts, w.sm, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream, fused));
 	} else {
 		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream, fused));
 	}
@@ -307,7 +307,7 @@ struct bkm_handle_s {
 	// CUDA graph of two iterations (launch-bound problem sizes)
 	int use_graph = 2;                 // 0 = never, 1 = always (single GPU), 2 = by problem size
 	bool tc_pair = true;               // let the tensor-core assignment use its CTA-pair kernel where it applies
-	bool fuse_update = true;           // let that kernel accumulate the update sums (no separate update pass)
+	int fuse_update = 1;               // fast pass accumulates the update sums: 0 never, 1 where it pays, 2 wherever it can
 	bool last_fused = false;
 	cudaGraphExec_t graph_exec = nullptr;
 	int graph_cur = 0, graph_slot = 0;
@@ -404,9 +404,25 @@ static bkm::TcPlan* cached_plan(const bkm::Shape& s, const Workspace& w, int dev
 // One assignment pass on a caller's workspace.  The operands derived from the (immutable) points -
 // centre vector, largest norm, tf32 planes - stay in the workspace; a call that finds the same
 // point set there (address, shape and a fingerprint of a sample of the values) skips them.
+// Whether the fast assignment pass should accumulate the update sums itself.  On CTA pairs the
+// epilogue warps send the reductions, which pays where the update would otherwise be the row-wise
+// kernel (the sorted update of row-major points costs less than that).  In the CUDA-core pass every
+// warp sorts the points it has just assigned by cluster and sends pre-added rows.
+static bool fuse_pays(int assign_variant, int update_variant, const bkm::TcPlan* plan, const bkm::FusedAcc& fa, const bkm::Shape& s, bool force = false)
+{
+	if (assign_variant == BKM_ASSIGN_SIMT) {
+		// measured: the warp-private sort adds 0.11 ms to a 0.32 ms pass over 2^24 two-dimensional points
+		// where the separate sorted update takes 0.10 ms, so it pays only where a launch less does
+		return bkm::assign_simt_can_fuse(s, fa) && (force || (double)s.n * s.k * s.dim <= 1.0e8);
+	}
+	if (assign_variant != BKM_ASSIGN_TC) return false;
+	return update_variant == BKM_UPDATE_ROWS && bkm::tc_plan_can_fuse(plan, fa) && (size_t)s.dim * sizeof(float) * 4 <= 120 * 1024;
+}
+
 // With `fa` given and the shape allowing it, the pass also accumulates the update sums (*fused).
 static int stateless_assign(const float* points, const float* means, uint32_t* assignment, const bkm::Shape& s,
-	const Workspace& w, int variant, int device, int sm_count, cudaStream_t st, const bkm::FusedAcc* fa = nullptr, bool* fused_out = nullptr)
+	const Workspace& w, int variant, int device, int sm_count, cudaStream_t st, const bkm::FusedAcc* fa = nullptr, int variant_update = 0,
+	bool* fused_out = nullptr)
 {
 	int v = 0;
 	int rc = resolve_assign(variant, s, &v);
@@ -427,6 +443,7 @@ static int stateless_assign(const float* points, const float* means, uint32_t* a
 			CUDA_TRY(cudaMemsetAsync(w.sm.rows, 0, w.cprep_bytes, st));
 			CUDA_TRY(bkm::launch_points_norm_max(points, s, w.tm.center, w.ctl, sm_count, st, skip));
 			bkm::launch_prepare_means(means, s, &w.sm, nullptr, w.ctl, 0, st);
+			fused = fa != nullptr && fuse_pays(v, variant_update, nullptr, *fa, s, true);     // the caller asked for the one-pass form
 		} else {
 			CUDA_TRY(cudaMemsetAsync(w.tm.b_hi, 0, w.tm_bytes, st));
 			bkm::launch_prepare_means(means, s, nullptr, &w.tm, w.ctl, 0, st);
@@ -435,9 +452,9 @@ static int stateless_assign(const float* points, const float* means, uint32_t* a
 			plan = cached_plan(s, w, device, &err);
 			if (!plan) return fail(BKM_ERR_CUDA, "tensor-core plan: %s", err ? err : "unknown");
 			bkm::tc_plan_allow_pair(plan, true);
-			fused = fa != nullptr && bkm::tc_plan_can_fuse(plan, *fa) && (size_t)s.dim * sizeof(float) * 4 <= 120 * 1024;
-			if (fused) CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
+			fused = fa != nullptr && fuse_pays(v, variant_update, plan, *fa, s);
 		}
+		if (fused) CUDA_TRY(cudaMemsetAsync(w.acc, 0, w.acc_bytes, st));
 	}
 	CUDA_TRY(cudaGetLastError());
 	if (fused_out) *fused_out = fused;
@@ -519,13 +536,14 @@ int bkm_iterate_f32(const float* points, const float* means_in, float* means_out
 	if (rc) return rc;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	uint32_t* asg = assignment ? assignment : w.asg_scratch;
-	// Where the assignment pass can accumulate the sums itself (the shapes of the CTA-pair kernel with
-	// an update that would otherwise be the row-wise kernel) the points are read once.
+	// Where the assignment pass can accumulate the sums itself (the CUDA-core pass for up to 8
+	// dimensions and 1024 means; the shapes of the CTA-pair kernel with an update that would
+	// otherwise be the row-wise kernel) the points are read once.
 	int vu = 0;
 	if ((rc = resolve_update(variant_update, s, device, &vu))) return rc;
 	bkm::FusedAcc fa{w.acc, w.counts, w.replicas, bkm::acc_replica_stride(k, dim), w.tm.center};
 	bool fused = false;
-	rc = stateless_assign(points, means_in, asg, s, w, variant_assign, device, sm, st, vu == BKM_UPDATE_ROWS ? &fa : nullptr, &fused);
+	rc = stateless_assign(points, means_in, asg, s, w, variant_assign, device, sm, st, &fa, vu, &fused);
 	if (rc) return rc;
 	if (fused) {
 		bkm::launch_finalize(w.acc, w.counts, w.replicas, means_out, sizes, s, nullptr, nullptr, w.ctl, 1, st);
@@ -731,7 +749,7 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value)
 		return BKM_OK;
 	}
 	if (!strcmp(name, "fuse_update")) {
-		h->fuse_update = value != 0.0;
+		h->fuse_update = value >= 2.0 ? 2 : (value != 0.0 ? 1 : 0);
 		drop_graph(h);
 		return BKM_OK;
 	}
@@ -856,14 +874,10 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 	const size_t kd = (size_t)s.k * s.dim;
 	const int next = h->cur ^ 1;
 	if (ev) CUDA_TRY(cudaEventRecord(ev[0], st));
-	// The CTA-pair tensor-core pass can add every point to its cluster's sum on the way (the
-	// accumulators are zero between iterations: the finalize pass clears what it has read).
+	// The CTA-pair tensor-core pass and the CUDA-core pass can add every point to its cluster's sum on
+	// the way (the accumulators are zero between iterations: the finalize pass clears what it has read).
 	bkm::FusedAcc fa{h->ws.acc, h->ws.counts, h->ws.replicas, bkm::acc_replica_stride(s.k, s.dim), h->ws.tm.center};
-	// (worth it where the update would otherwise be the row-wise kernel; the sorted update of
-	// row-major points costs less than the reductions cost inside the assignment kernel)
-	const bool fused = h->fuse_update && h->assign_variant == BKM_ASSIGN_TC && h->update_variant == BKM_UPDATE_ROWS &&
-		bkm::tc_plan_can_fuse(h->plan, fa) &&
-		(size_t)s.dim * sizeof(float) * 4 <= 120 * 1024;
+	const bool fused = h->fuse_update && fuse_pays(h->assign_variant, h->update_variant, h->plan, fa, s, h->fuse_update >= 2);
 	h->last_fused = fused;
 	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + (fused ? 0u : 1u) + 1u;
 	int rc = enqueue_assign(h->assign_variant, h->d_points, h->d_means[h->cur], h->d_asg, s, h->ws, h->slot,

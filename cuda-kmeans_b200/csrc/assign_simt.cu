@@ -342,7 +342,8 @@ constexpr uint32_t LIST_SMALL_MAX_DIM = 16;
 
 template<int D, bool SOA, bool SOAM>
 __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const float* __restrict__ pts, const float* __restrict__ means,
-	uint32_t* __restrict__ asg, uint64_t n, uint32_t k, const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count)
+	uint32_t* __restrict__ asg, uint64_t n, uint32_t k, const uint32_t* __restrict__ list, const uint32_t* __restrict__ list_count,
+	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts)
 {
 	__shared__ __align__(16) float sm[LIST_SMALL_MAX_FLOATS];          // [mean][dimension]
 	for (uint32_t e = threadIdx.x; e < k * D; e += blockDim.x) {
@@ -381,19 +382,34 @@ __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const floa
 			const float dist = __fsqrt_rn(sum);
 			if (m == 0 || dist < best) { best = dist; bidx = m; }
 		}
+		if (fix_acc) {
+			// the fast pass has already added this point to the sum of the cluster it picked
+			const uint32_t from = asg[i];
+			if (from != bidx && from < k) {
+				#pragma unroll
+				for (int j = 0; j < D; ++j) {
+					atomicAdd(&fix_acc[(size_t)from * D + j], -x[j]);
+					atomicAdd(&fix_acc[(size_t)bidx * D + j], x[j]);
+				}
+				atomicSub(&fix_counts[from], 1u);
+				atomicAdd(&fix_counts[bidx], 1u);
+			}
+		}
 		asg[i] = bidx;
 	}
 }
 
 template<int D>
 static cudaError_t launch_list_small(const float* pts, const float* means, uint32_t* asg, const Shape& s,
-	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream)
+	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix)
 {
 	const uint32_t grid = (uint32_t)sm_count * 4;
-	if (s.soa && s.soa_means) assign_exact_list_small_kernel<D, true, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
-	else if (s.soa) assign_exact_list_small_kernel<D, true, false><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
-	else if (s.soa_means) assign_exact_list_small_kernel<D, false, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
-	else assign_exact_list_small_kernel<D, false, false><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count);
+	float* fa = fix ? fix->acc : nullptr;
+	uint32_t* fc = fix ? fix->counts : nullptr;
+	if (s.soa && s.soa_means) assign_exact_list_small_kernel<D, true, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count, fa, fc);
+	else if (s.soa) assign_exact_list_small_kernel<D, true, false><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count, fa, fc);
+	else if (s.soa_means) assign_exact_list_small_kernel<D, false, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count, fa, fc);
+	else assign_exact_list_small_kernel<D, false, false><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count, fa, fc);
 	return cudaGetLastError();
 }
 
@@ -408,24 +424,24 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 	unsigned long long* split_keys = reinterpret_cast<unsigned long long*>(split_scratch);
 	uint32_t* split_arrive = split_scratch ? reinterpret_cast<uint32_t*>(split_keys + (size_t)LIST_SPLIT_MAX_BLOCKS * LIST_PB_WIDE) : nullptr;
 	if (fix != nullptr && (list == nullptr || (size_t)s.dim * sizeof(float) * LIST_PB > 120 * 1024)) return cudaErrorInvalidValue;
-	if (list != nullptr && fix == nullptr && s.dim <= LIST_SMALL_MAX_DIM && (uint64_t)s.k * s.dim <= LIST_SMALL_MAX_FLOATS) {
+	if (list != nullptr && s.dim <= LIST_SMALL_MAX_DIM && (uint64_t)s.k * s.dim <= LIST_SMALL_MAX_FLOATS) {
 		switch (s.dim) {
-		case 1: return launch_list_small<1>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 2: return launch_list_small<2>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 3: return launch_list_small<3>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 4: return launch_list_small<4>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 5: return launch_list_small<5>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 6: return launch_list_small<6>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 7: return launch_list_small<7>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 8: return launch_list_small<8>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 9: return launch_list_small<9>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 10: return launch_list_small<10>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 11: return launch_list_small<11>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 12: return launch_list_small<12>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 13: return launch_list_small<13>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 14: return launch_list_small<14>(pts, means, asg, s, list, list_count, sm_count, stream);
-		case 15: return launch_list_small<15>(pts, means, asg, s, list, list_count, sm_count, stream);
-		default: return launch_list_small<16>(pts, means, asg, s, list, list_count, sm_count, stream);
+		case 1: return launch_list_small<1>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 2: return launch_list_small<2>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 3: return launch_list_small<3>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 4: return launch_list_small<4>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 5: return launch_list_small<5>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 6: return launch_list_small<6>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 7: return launch_list_small<7>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 8: return launch_list_small<8>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 9: return launch_list_small<9>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 10: return launch_list_small<10>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 11: return launch_list_small<11>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 12: return launch_list_small<12>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 13: return launch_list_small<13>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 14: return launch_list_small<14>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		case 15: return launch_list_small<15>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
+		default: return launch_list_small<16>(pts, means, asg, s, list, list_count, sm_count, stream, fix);
 		}
 	}
 	if (list != nullptr && (size_t)s.dim * sizeof(float) * LIST_PB <= 120 * 1024) {
@@ -498,14 +514,58 @@ cudaError_t launch_assign_exact(const float* pts, const float* means, uint32_t* 
 constexpr int SIMT_THREADS = 256;
 constexpr int SIMT_TILE_ROWS = 1024; // means per shared-memory tile (a multiple of the 32-mean chunk)
 
-template<int D, bool SOA, int P>
+// Fused update sums (FUSE): every WARP sorts the 32 * P points it has just assigned by cluster, in
+// shared memory of its own (counters whose atomic also yields the rank, prefix sum over the counters,
+// scatter of the centred coordinates to the sorted position).  A lane then walks P neighbouring
+// sorted positions, adds rows while the cluster stays the same and sends one row of reductions when
+// it changes (with the centre added back, once per point of the run); the sizes are counted per
+// block and sent at the end.  Nothing here waits for another warp, and no separate update pass reads
+// the points again.  (Measured alternatives on 2^24 two-dimensional points, 64 clusters, where the
+// plain pass takes 0.32 ms and a separate sorted update 0.10 ms: this form 0.43 ms; the same sort per
+// block with five block-wide barriers 0.48 ms; match.any groups added by the warp's integer
+// reduction 1.53 ms - both instructions are replayed once per distinct cluster in the warp.)
+constexpr uint32_t SIMT_FUSE_MAX_K = 1024;
+
+// sum[0..D) + len * cen[0..D) onto the row `dst` of the accumulators, as vector reductions where the row allows
+template<int D>
+__device__ __forceinline__ void send_row(float* dst, const float (&sum)[D], float len, const float (&cen)[D])
+{
+	float v[D];
+	#pragma unroll
+	for (int j = 0; j < D; ++j) v[j] = fmaf(len, cen[j], sum[j]);
+	if (D % 4 == 0) {
+		#pragma unroll
+		for (int q = 0; q < D / 4; ++q)
+			asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(dst + 4 * q), "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+	} else if (D % 2 == 0) {
+		#pragma unroll
+		for (int q = 0; q < D / 2; ++q)
+			asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" :: "l"(dst + 2 * q), "f"(v[2 * q]), "f"(v[2 * q + 1]) : "memory");
+	} else {
+		#pragma unroll
+		for (int j = 0; j < D; ++j) atomicAdd(dst + j, v[j]);
+	}
+}
+
+template<int D, bool SOA, int P, bool FUSE>
 __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* __restrict__ pts,
 	const float* __restrict__ cprep, const float* __restrict__ center, uint32_t* __restrict__ asg, uint64_t n, uint32_t rows,
-	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_ulps, int vec_ok)
+	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_ulps, int vec_ok,
+	uint32_t k, float* __restrict__ fuse_acc, uint32_t* __restrict__ fuse_counts)
 {
 	constexpr int RS = (D + 1 + 3) / 4 * 4;
 	extern __shared__ __align__(128) float tile[];
 	__shared__ __align__(8) uint64_t bar;
+	// fused update sums: see above
+	__shared__ uint32_t s_hist[FUSE ? SIMT_THREADS / 32 : 1][FUSE ? (SIMT_FUSE_MAX_K + 2) / 2 : 1];   // per warp: points per cluster, 16 bits each
+	__shared__ uint32_t s_cnt[FUSE ? SIMT_FUSE_MAX_K : 1];                  // sizes counted by this block
+	__shared__ __align__(16) float s_x[FUSE ? SIMT_THREADS * P * D : 1];    // per warp: sorted position -> centred coordinates
+	__shared__ __align__(8) uint16_t s_cl[FUSE ? SIMT_THREADS * P : 4];     // per warp: sorted position -> cluster
+	float* fuse_acc_rep = fuse_acc;
+	if (FUSE) {
+		fuse_acc_rep += (blockIdx.x % acc_replicas(k, D)) * acc_replica_stride(k, D);
+		for (uint32_t c = threadIdx.x; c < SIMT_FUSE_MAX_K; c += SIMT_THREADS) s_cnt[c] = 0;
+	}
 	__shared__ uint32_t flag_bufs[SIMT_THREADS / 32][FLAG_BUFFER];     // per warp: near-ties on their way to the list
 	uint32_t* flag_buf = flag_bufs[threadIdx.x >> 5];
 	uint32_t flag_cnt = 0;
@@ -637,17 +697,100 @@ __global__ void __launch_bounds__(SIMT_THREADS) assign_simt_kernel(const float* 
 			}
 		}
 
+		uint32_t cl[P];
 		#pragma unroll
 		for (int p = 0; p < P; ++p) {
 			bool flag = false;
+			cl[p] = k;                     // rows behind the last point sort behind every cluster
 			if (idx[p] < n) {
 				// key - key_base = M * mantissa + column
 				const uint32_t bm = div_key(best[p] - key_base, key_magic);
-				asg[idx[p]] = bchunk[p] * 32u + ((best[p] - key_base) - bm * key_mult);
+				cl[p] = bchunk[p] * 32u + ((best[p] - key_base) - bm * key_mult);
+				asg[idx[p]] = cl[p];
 				const float gap = second[p] == 0xFFFFFFFFu ? INFINITY : (float)(div_key(second[p] - key_base, key_magic) - bm);
 				flag = gap <= margin_ulps;
 			}
 			buffered_append(flag, (uint32_t)idx[p], flag_buf, flag_cnt, ctl, flag_list, n);
+		}
+
+		if (FUSE) {
+			// everything below is private to the warp: its 32 * P points, its counters, its sorted rows
+			const uint32_t lane = tid & 31u, warp = tid >> 5;
+			uint32_t* hist32 = s_hist[warp];
+			uint16_t* hist = reinterpret_cast<uint16_t*>(hist32);      // k + 1 counters, two to a word; the start positions later
+			uint16_t* w_cl = s_cl + warp * (32 * P);
+			float* w_x = s_x + warp * (32 * P * D);
+			const uint32_t nb = k + 1;
+			__syncwarp();                  // the walk over the previous block's rows is over
+			for (uint32_t w = lane; w < (nb + 1) / 2; w += 32) hist32[w] = 0;
+			__syncwarp();
+			uint32_t rank[P];
+			#pragma unroll
+			for (int p = 0; p < P; ++p) {
+				if (cl[p] > k) cl[p] = k;  // (cannot happen: padding columns never win)
+				const uint32_t sh = (cl[p] & 1u) * 16u;
+				rank[p] = (atomicAdd(&hist32[cl[p] >> 1], 1u << sh) >> sh) & 0xffffu;   // the count also hands out the place within the cluster
+			}
+			__syncwarp();
+			// exclusive prefix sum over the counters: a run of them per lane, warp scan of the run totals
+			const uint32_t per = (nb + 31) / 32, b0 = min(nb, lane * per), b1 = min(nb, b0 + per);
+			uint32_t local = 0;
+			for (uint32_t b = b0; b < b1; ++b) {
+				const uint32_t v = hist[b];
+				local += v;
+				if (v != 0 && b < k) atomicAdd(&s_cnt[b], v);          // the sizes, sent once at the end of the kernel
+			}
+			uint32_t incl = local;
+			#pragma unroll
+			for (uint32_t off = 1; off < 32; off <<= 1) { const uint32_t o = __shfl_up_sync(0xffffffffu, incl, off); if (lane >= off) incl += o; }
+			uint32_t run = incl - local;
+			for (uint32_t b = b0; b < b1; ++b) {
+				const uint32_t v = hist[b];
+				hist[b] = (uint16_t)run;
+				run += v;
+			}
+			__syncwarp();
+			#pragma unroll
+			for (int p = 0; p < P; ++p) {
+				const uint32_t pos = hist[cl[p]] + rank[p];
+				w_cl[pos] = (uint16_t)cl[p];
+				#pragma unroll
+				for (int j = 0; j < D; ++j) w_x[pos * D + j] = x[p][j];
+			}
+			__syncwarp();
+			const uint32_t total = hist[k];    // rows of real points
+			float sum[D];
+			#pragma unroll
+			for (int j = 0; j < D; ++j) sum[j] = 0.0f;
+			float len = 0.0f;
+			uint32_t cur = 0;
+			#pragma unroll
+			for (int u = 0; u < P; ++u) {
+				const uint32_t sp = lane * P + u;
+				if (sp < total) {
+					const uint32_t c = w_cl[sp];
+					if (u == 0) cur = c;
+					if (c != cur) {
+						send_row<D>(fuse_acc_rep + (size_t)cur * D, sum, len, cen);
+						#pragma unroll
+						for (int j = 0; j < D; ++j) sum[j] = 0.0f;
+						len = 0.0f;
+						cur = c;
+					}
+					#pragma unroll
+					for (int j = 0; j < D; ++j) sum[j] += w_x[sp * D + j];
+					len += 1.0f;
+				}
+			}
+			if (len > 0.0f) send_row<D>(fuse_acc_rep + (size_t)cur * D, sum, len, cen);
+		}
+	}
+	if (FUSE) {
+		__syncthreads();
+		uint32_t* cnt = fuse_counts + (blockIdx.x % acc_replicas(k, D)) * acc_replica_stride(k, D);
+		for (uint32_t c = tid; c < k; c += SIMT_THREADS) {
+			const uint32_t v = s_cnt[c];
+			if (v) atomicAdd(&cnt[c], v);
 		}
 	}
 	flush_flag_buffer(flag_buf, flag_cnt, ctl, flag_list, n);
@@ -659,9 +802,16 @@ bool assign_simt_supported(const Shape& s)
 	return s.dim >= 1 && s.dim <= 8 && s.n < (1ull << 32);
 }
 
+bool assign_simt_can_fuse(const Shape& s, const FusedAcc& f)
+{
+	// one tile of means (so that a block meets its points once), vector reductions need aligned rows
+	return assign_simt_supported(s) && s.k <= SIMT_FUSE_MAX_K && simt_rows(s.k) <= (uint32_t)SIMT_TILE_ROWS && f.acc != nullptr && f.counts != nullptr &&
+		(reinterpret_cast<uintptr_t>(f.acc) & 15u) == 0 && (f.rep_stride * sizeof(float)) % 16 == 0;
+}
+
 template<int D, int P>
 static cudaError_t launch_simt_d(const float* pts, const float* cprep, const float* center, uint32_t* asg, const Shape& s,
-	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream)
+	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream, const FusedAcc* fused)
 {
 	constexpr int RS = (D + 1 + 3) / 4 * 4;
 	const uint32_t rows = simt_rows(s.k);
@@ -676,8 +826,8 @@ static cudaError_t launch_simt_d(const float* pts, const float* cprep, const flo
 	// values, plus the reference's own sum and the collapse of its square root.
 	const float margin_ulps = margin_scale * (float)(4 * D + 16);
 	const int vec_ok = ((reinterpret_cast<uintptr_t>(pts) & 15u) == 0) ? 1 : 0;
-#define BKM_LAUNCH_SIMT(SOA) do { \
-		auto kern = assign_simt_kernel<D, SOA, P>; \
+#define BKM_LAUNCH_SIMT(SOA, FUSE) do { \
+		auto kern = assign_simt_kernel<D, SOA, P, FUSE>; \
 		cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
 		if (e != cudaSuccess) return e; \
 		e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, SIMT_THREADS, smem); \
@@ -685,25 +835,28 @@ static cudaError_t launch_simt_d(const float* pts, const float* cprep, const flo
 		if (per_sm < 1) per_sm = 1; \
 		uint32_t grid = (uint32_t)std::min<uint64_t>(nblocks, (uint64_t)sm_count * per_sm); \
 		if (grid < 1) grid = 1; \
-		kern<<<grid, SIMT_THREADS, smem, stream>>>(pts, cprep, center, asg, s.n, rows, ctl, slot, flag_list, margin_ulps, vec_ok); \
+		kern<<<grid, SIMT_THREADS, smem, stream>>>(pts, cprep, center, asg, s.n, rows, ctl, slot, flag_list, margin_ulps, vec_ok, \
+			s.k, fused ? fused->acc : nullptr, fused ? fused->counts : nullptr); \
 	} while (0)
-	if (s.soa) BKM_LAUNCH_SIMT(true); else BKM_LAUNCH_SIMT(false);
+	if (fused && !assign_simt_can_fuse(s, *fused)) return cudaErrorInvalidValue;
+	if (fused) { if (s.soa) BKM_LAUNCH_SIMT(true, true); else BKM_LAUNCH_SIMT(false, true); }
+	else { if (s.soa) BKM_LAUNCH_SIMT(true, false); else BKM_LAUNCH_SIMT(false, false); }
 #undef BKM_LAUNCH_SIMT
 	return cudaGetLastError();
 }
 
 cudaError_t launch_assign_simt(const float* pts, const SimtMeans& sm, uint32_t* asg, const Shape& s,
-	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream)
+	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream, const FusedAcc* fused)
 {
 	switch (s.dim) {
-	case 1: return launch_simt_d<1, 4>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 2: return launch_simt_d<2, 4>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 3: return launch_simt_d<3, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 4: return launch_simt_d<4, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 5: return launch_simt_d<5, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 6: return launch_simt_d<6, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 7: return launch_simt_d<7, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
-	case 8: return launch_simt_d<8, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream);
+	case 1: return launch_simt_d<1, 4>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 2: return launch_simt_d<2, 4>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 3: return launch_simt_d<3, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 4: return launch_simt_d<4, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 5: return launch_simt_d<5, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 6: return launch_simt_d<6, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 7: return launch_simt_d<7, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
+	case 8: return launch_simt_d<8, 2>(pts, sm.rows, sm.center, asg, s, ctl, slot, flag_list, margin_scale, sm_count, stream, fused);
 	default: return cudaErrorInvalidValue;
 	}
 }

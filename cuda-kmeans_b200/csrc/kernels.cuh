@@ -125,8 +125,11 @@ bool assign_simt_supported(const Shape& s);
 // `skip_if` (optional, device): the kernels of the one-off preprocessing return at once when *skip_if != 0.
 cudaError_t launch_points_norm_max(const float* pts, const Shape& s, const float* center, Control* ctl, int sm_count, cudaStream_t stream,
 	const uint32_t* skip_if = nullptr);
+// With `fused` set (allowed when assign_simt_can_fuse) the kernel also adds every point to the sum and
+// the size of the cluster it picked; points that the exact re-check moves afterwards are corrected there.
+bool assign_simt_can_fuse(const Shape& s, const FusedAcc& f);
 cudaError_t launch_assign_simt(const float* pts, const SimtMeans& sm, uint32_t* asg, const Shape& s,
-	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream);
+	Control* ctl, int slot, uint32_t* flag_list, float margin_scale, int sm_count, cudaStream_t stream, const FusedAcc* fused = nullptr);
 
 // ---- assignment on tensor cores (assign_tc.cu) ----
 bool assign_tc_supported(const Shape& s);

@@ -119,7 +119,10 @@ int bkm_probe_atomics_f32(float* result, uint64_t n, uint32_t k, uint32_t dim, i
                           int shared_cache, uint32_t items_per_thread, void* stream);
 
 /* One whole iteration: means_out/sizes from means_in.  `assignment` may be NULL when the
- * caller does not want it, as in the reference's fused runners.
+ * caller does not want it, as in the reference's fused runners.  The points are read once, as in
+ * those runners, where the assignment pass can add up the sums itself (dim <= 8 with at most 1024
+ * means; 257..1024 means of 17..32 dimensions, dim % 4 == 0, dimension-major points); elsewhere
+ * the assignment pass is followed by the update pass.
  * Replaces KERNEL::run(const FusedProblemInstance<F,IDX_T>&, CudaExecParameters&)
  * (headers/kernels.cuh:40-52, 108-116; runners kernels/kernels.cu:951-998, 1146-1190). */
 int bkm_iterate_f32(const float* points, const float* means_in, float* means_out, uint32_t* sizes,
@@ -220,8 +223,10 @@ int bkm_set_stream(bkm_handle_t h, void* stream);
  * replay a CUDA graph of two iterations when the problem is small enough to be bound by launch
  * latency; single GPU only), "tc_pair" (0/1, default 1: let the tensor-core assignment run on CTA
  * pairs with all means resident in shared memory where the shape allows, i.e. 257..1024 means
- * of 17..32 dimensions), "fuse_update" (0/1, default 1: let that kernel add every point to the sum
- * of the cluster it picks, which replaces the row-wise update pass of bkm_run; needs dim % 4 == 0),
+ * of 17..32 dimensions), "fuse_update" (0 never, 1 = default: where it pays, 2 wherever possible:
+ * let the fast assignment pass add every point to the sum of the cluster it picks, which replaces
+ * the update pass of bkm_run; possible on CTA pairs with dim % 4 == 0 and in the CUDA-core pass
+ * for dim <= 8 and at most 1024 means; by default the latter only for launch-bound sizes),
  * "exchange_wait_ms" (1..600000, default 2000: how long the peer-memory exchange waits for a peer).
  * Unknown names fail with BKM_ERR_INVALID. */
 int bkm_set_option(bkm_handle_t h, const char* name, double value);

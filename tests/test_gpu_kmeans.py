@@ -139,6 +139,35 @@ def test_tc_pair_kernel_matches_single_cta_kernel(pkg, torch_cuda, oracle_mod, w
         assert np.array_equal(got, want), (pair, int((got != want).sum()))
 
 
+@pytest.mark.parametrize("n,k,d,layout,sigma", [(50000, 64, 2, 0, 0.01), (30011, 16, 4, 0, 0.05), (9000, 1000, 3, 0, 0.05),
+                                              (20000, 40, 8, 1, 0.05), (5000, 7, 1, 1, 0.05), (300, 500, 5, 0, 0.05)])
+def test_small_dim_fused_update_matches_separate_update(pkg, torch_cuda, oracle_mod, workloads, n, k, d, layout, sigma):
+    """The CUDA-core pass (dim <= 8) sorts each block of points it has assigned by cluster and adds
+    them to the sums itself; the exact re-check moves the points it reassigns (tight clusters queue
+    thousands of them).  Assignment, sizes and means must agree with the oracle step by step, with
+    and without the fusion."""
+    rows = workloads.generate_rows("mixture", n, d, 16, seed=17, sigma=sigma)
+    data, means = workloads.to_layout(rows, layout), workloads.to_layout(np.ascontiguousarray(rows[:k] if k <= n else np.resize(rows, (k, d))), layout)
+    for fuse in (1, 0):
+        km = pkg.KMeans(layout=layout, variant_assign=pkg.ASSIGN_SIMT)
+        km.initialize(d, k, n, 3, data, means)
+        km.set_option("fuse_update", 2 * fuse)     # 2 = wherever possible (the default takes it for launch-bound sizes only)
+        km.set_option("use_graph", 0)
+        prev = np.asarray(means, dtype=np.float32).reshape(-1).copy()
+        for it in range(3):
+            km.run(1)
+            asg, cur, sizes = km.getAssignment(), km.getMeans(), km.getSizes()
+            want_asg = oracle_mod.assign(data, prev, n, k, d, layout, layout, threads=8)
+            assert np.array_equal(asg, want_asg), (fuse, it, int((asg != want_asg).sum()))
+            want, want_sizes = oracle_mod.update(data, asg, n, k, d, layout, layout)
+            assert np.array_equal(sizes, want_sizes), (fuse, it)
+            ok, err = means_close(cur, want)
+            assert ok, (fuse, it, err)
+            prev = cur
+        assert (km.counters()["update_variant"] == "fused") == (fuse == 1)
+        km.cleanup()
+
+
 @pytest.mark.parametrize("n,k,d,layout", [(20000, 1024, 32, 1), (4224, 300, 20, 0), (777, 512, 24, 1)])
 def test_fused_update_matches_separate_update(pkg, torch_cuda, oracle_mod, workloads, n, k, d, layout):
     """The CTA-pair kernel can accumulate the update sums itself; means, sizes and assignment must

@@ -49,7 +49,9 @@ def test_repeated_calls_reuse_the_workspace_and_notice_new_points(pkg, torch_cud
     (20000, 1024, 32, 1, 1, True),     # CTA-pair kernel: single pass
     (7001, 512, 24, 1, 0, False),      # same, no assignment output, other means layout
     (9000, 300, 20, 0, 0, True),       # row-major points: two passes
-    (30000, 64, 2, 0, 0, True),        # CUDA cores: two passes
+    (30000, 64, 2, 0, 0, True),        # CUDA cores: single pass (every warp sorts its points by cluster)
+    (12345, 200, 7, 1, 0, False),      # same, dimension-major points, no assignment output
+    (5000, 2000, 3, 0, 0, True),       # CUDA cores, more means than the single pass takes: two passes
 ])
 def test_iterate_matches_oracle_iteration(pkg, torch_cuda, oracle_mod, n, k, d, layout, layout_means, want_asg):
     torch = torch_cuda
