@@ -346,13 +346,14 @@ __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const floa
 	float* __restrict__ fix_acc, uint32_t* __restrict__ fix_counts)
 {
 	__shared__ __align__(16) float sm[LIST_SMALL_MAX_FLOATS];          // [mean][dimension]
+	uint64_t total = *list_count;
+	if (total > n) total = n;
+	if ((uint64_t)blockIdx.x * blockDim.x >= total) return;            // the grid is sized for long lists: most blocks of a short one have nothing to do
 	for (uint32_t e = threadIdx.x; e < k * D; e += blockDim.x) {
 		const uint32_t m = e / D, j = e - m * D;
 		sm[e] = means[at<SOAM>(m, j, k, D)];
 	}
 	__syncthreads();
-	uint64_t total = *list_count;
-	if (total > n) total = n;
 	for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (uint64_t)gridDim.x * blockDim.x) {
 		const uint64_t i = list[w];
 		float x[D];
@@ -403,7 +404,9 @@ template<int D>
 static cudaError_t launch_list_small(const float* pts, const float* means, uint32_t* asg, const Shape& s,
 	const uint32_t* list, const uint32_t* list_count, int sm_count, cudaStream_t stream, const FusedAcc* fix)
 {
-	const uint32_t grid = (uint32_t)sm_count * 4;
+	// a thread's point is a dependent gather behind its list entry: many threads in flight hide that,
+	// so a long list gets one or two points per thread rather than a loop
+	const uint32_t grid = (uint32_t)sm_count * 16;
 	float* fa = fix ? fix->acc : nullptr;
 	uint32_t* fc = fix ? fix->counts : nullptr;
 	if (s.soa && s.soa_means) assign_exact_list_small_kernel<D, true, true><<<grid, 256, 0, stream>>>(pts, means, asg, s.n, s.k, list, list_count, fa, fc);
