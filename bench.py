@@ -41,9 +41,9 @@ if ROOT not in sys.path:
 
 V100_PUBLISHED_GEVALS = 84.4  # reference's best variant, N=2M d=32 k=1024, V100 (results/README.md:20)
 # DRAM bytes (read + write, from one profiler capture) that one assignment launch on workload c2
-# moves per point: the capture ran on 2^19 points (138.88 MB read + 4.71 MB written); the traffic is
+# moves per point: the capture ran on 2^19 points (138.81 MB read + 6.79 MB written); the traffic is
 # the point operands, read once, so it grows in proportion to the points.
-C2_ASSIGN_TC_DRAM_BYTES_PER_POINT = (138.88e6 + 4.71e6) / (1 << 19)
+C2_ASSIGN_TC_DRAM_BYTES_PER_POINT = (138.81e6 + 6.79e6) / (1 << 19)
 PARITY_SAMPLE = 4096
 
 
