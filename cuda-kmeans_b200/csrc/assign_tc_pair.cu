@@ -75,7 +75,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template<uint32_t SLEEP_NS = 100>
 __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t peer_abort_addr)
 {
-	if (wait_or_abort<SLEEP_NS>(bar, parity, abort_flag)) return true;
+	if (wait_or_abort<SLEEP_NS, true>(bar, parity, abort_flag)) return true;
 	ptx::st_cluster_u32(peer_abort_addr, 1u);
 	return false;
 }

@@ -77,6 +77,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
 	}
 }
 
+// Up to `polls` rounds of (try_wait, sleep SLEEP_NS) as one six-instruction loop; true as soon as the phase is complete.
+template<uint32_t SLEEP_NS>
+__device__ __forceinline__ bool mbar_poll_round(uint64_t* bar, uint32_t parity, uint32_t polls)
+{
+	uint32_t ok;
+	asm volatile(
+		"{\n"
+		".reg .pred done, more;\n"
+		".reg .u32 left;\n"
+		"mov.u32 left, %3;\n"
+		"POLL_AGAIN:\n"
+		"mbarrier.try_wait.parity.shared::cta.b64 done, [%1], %2, %4;\n"
+		"@done bra POLL_END;\n"
+		"nanosleep.u32 %5;\n"
+		"sub.u32 left, left, 1;\n"
+		"setp.ne.u32 more, left, 0;\n"
+		"@more bra POLL_AGAIN;\n"
+		"POLL_END:\n"
+		"selp.u32 %0, 1, 0, done;\n"
+		"}\n"
+		: "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(polls), "r"(WAIT_SLICE_NS), "n"(SLEEP_NS) : "memory");
+	return ok != 0;
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar)
