@@ -299,14 +299,23 @@ def timed_run(ctx, km, steps, warmup, sample_clocks=True):
             dist.barrier()
         torch.cuda.synchronize()
 
-    km.run(warmup)
+    # The ranks leave a host-side barrier up to milliseconds apart (more so with eight processes on
+    # shared cores), and the rank that is first would count that lead as waiting time in its first
+    # exchange.  So the last warm-up step is enqueued behind the barrier, directly in front of the
+    # timed steps: its exchange lines the ranks' streams up, and the events bracket exactly `steps`
+    # iterations that all GPUs start together.
+    km.run(max(warmup - 1, 0))
     barrier()
     sampler = ClockSampler(physical_gpu_index(ctx["local_rank"])) if sample_clocks else None
     if sampler:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if warmup > 0:
+        km.run_async(1)
     e0.record(stream)
+    t_host = time.perf_counter()
     km.run_async(steps)
+    enqueue_ms = (time.perf_counter() - t_host) * 1e3
     e1.record(stream)
     barrier()
     km.synchronize()
@@ -327,7 +336,10 @@ def timed_run(ctx, km, steps, warmup, sample_clocks=True):
         dist.all_gather(allp, mine)
         allp = torch.stack(allp).cpu().numpy()
         before = allp[:, 0] + allp[:, 1] + allp[:, 2]
-        by_rank = {"compute_before_exchange_min": float(before.min()), "compute_before_exchange_max": float(before.max()),
+        t2 = torch.tensor([enqueue_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        by_rank = {"host_enqueue_ms_per_step_max": float(t2.item()) / steps,
+                   "compute_before_exchange_min": float(before.min()), "compute_before_exchange_max": float(before.max()),
                    "exchange_min": float(allp[:, 3].min()), "exchange_max": float(allp[:, 3].max()),
                    "finalize_max": float(allp[:, 4].max()), "iteration_max": float(allp[:, 5].max())}
     return ms_total / steps, clocks, phases, counters, by_rank
@@ -466,7 +478,10 @@ def main():
     config = {"workload": "%s: N=%d%s x dim %d, k=%d, fp32, %s points" % (
         args.workload, spec["n"], per_gpu, dim, k, "SoA" if lay == 1 else "AoS"),
         "distribution": spec["kind"], "init": "first k points", "l2": "inputs exceed L2 (no flush needed)"
-        if spec["n"] * dim * 4 > 126e6 else "inputs fit L2: working set is re-read from L2 between steps"}
+        if spec["n"] * dim * 4 > 126e6 else "inputs fit L2: working set is re-read from L2 between steps",
+        "timing": "CUDA events on the launching stream around exactly `steps` iterations, max over ranks; W-1 warm-up steps, "
+                  "barrier + synchronize, then the last warm-up step and the timed steps are enqueued back to back (the "
+                  "exchange of that step lines the GPUs up, so the ranks' different exits from the barrier are not timed)"}
 
     # ---------------- reference arm: the reference's CPU implementation ----------------
     if args.impl == "reference":
