@@ -273,6 +273,9 @@ struct bkm_handle_s {
 	int sm_count = 0;
 	cudaStream_t stream = nullptr;
 	cudaStream_t own_stream = nullptr;
+	static constexpr uint32_t UPLOAD_CHUNKS = 8;
+	cudaStream_t copy_stream = nullptr;            // host points travel here chunk by chunk (tensor-core path)
+	cudaEvent_t copy_ev[UPLOAD_CHUNKS] = {};       // chunk c has arrived
 	const float* d_points = nullptr;
 	float* d_points_owned = nullptr;
 	float* d_means[2] = {nullptr, nullptr};
@@ -715,6 +718,8 @@ int bkm_destroy(bkm_handle_t h)
 	cudaFree(h->d_sizes);
 	cudaFree(h->d_ws);
 	if (h->own_stream) cudaStreamDestroy(h->own_stream);
+	if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
+	for (cudaEvent_t e : h->copy_ev) if (e) cudaEventDestroy(e);
 	delete h;
 	return BKM_OK;
 }
@@ -767,7 +772,8 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value)
 	return fail(BKM_ERR_INVALID, "unknown option '%s'", name);
 }
 
-static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind kind)
+// First part of an initialisation: state reset, means, cleared workspace (all on the handle's stream).
+static int initialize_begin(bkm_handle_t h, const float* means, cudaMemcpyKind kind)
 {
 	const bkm::Shape& s = h->shape;
 	const size_t kd = (size_t)s.k * s.dim;
@@ -778,13 +784,24 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 	CUDA_TRY(cudaMemsetAsync(h->d_ws, 0, (size_t)(reinterpret_cast<char*>(h->ws.flag_list) - h->d_ws), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_asg, 0, s.n * sizeof(uint32_t), st));
 	CUDA_TRY(cudaMemsetAsync(h->d_sizes, 0, (size_t)s.k * sizeof(uint32_t), st));
+	return BKM_OK;
+}
+
+// Second part: what is derived from the points (unless the caller has done that chunk by chunk while
+// they arrived: `points_done`), the operands derived from the means, then a wait for all of it.
+static int initialize_finish(bkm_handle_t h, bool points_done)
+{
+	const bkm::Shape& s = h->shape;
+	cudaStream_t st = h->stream;
 	if (h->assign_variant == BKM_ASSIGN_SIMT) {
 		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
 		CUDA_TRY(bkm::launch_points_norm_max(h->d_points, s, h->ws.tm.center, h->ws.ctl, h->sm_count, st));
 	}
 	if (h->assign_variant == BKM_ASSIGN_TC) {
-		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
-		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, st));
+		if (!points_done) {
+			CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
+			CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, st));
+		}
 		if (h->plan) { bkm::tc_plan_destroy(h->plan); h->plan = nullptr; }
 		const char* err = nullptr;
 		h->plan = bkm::tc_plan_create(s, h->ws.tp, h->ws.tm, h->cfg.device, &err);
@@ -797,6 +814,45 @@ static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind 
 	CUDA_TRY(cudaGetLastError());
 	CUDA_TRY(cudaStreamSynchronize(st));
 	h->initialized = true;
+	return BKM_OK;
+}
+
+static int initialize_common(bkm_handle_t h, const float* means, cudaMemcpyKind kind)
+{
+	const int rc = initialize_begin(h, means, kind);
+	return rc ? rc : initialize_finish(h, false);
+}
+
+// Host points of the tensor-core path travel in chunks on a stream of their own, and every chunk is
+// split into its operand planes on the handle's stream as soon as it has arrived, while the next one is
+// on its way: the splitting (one read and two writes of the points) hides behind the upload.  The
+// centre comes from the first chunk (any vector serves).  Returns with the copies and kernels enqueued.
+static int upload_and_split(bkm_handle_t h, const float* host_points)
+{
+	const bkm::Shape& s = h->shape;
+	if (!h->copy_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+	for (cudaEvent_t& e : h->copy_ev)
+		if (!e) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+	const uint64_t chunk = bkm::round_up64((s.n + bkm_handle_s::UPLOAD_CHUNKS - 1) / bkm_handle_s::UPLOAD_CHUNKS, 4096);
+	// the copies must not overtake the clearing of the workspace and of what the previous use left in the planes' consumers
+	CUDA_TRY(cudaEventRecord(h->copy_ev[0], h->stream));
+	CUDA_TRY(cudaStreamWaitEvent(h->copy_stream, h->copy_ev[0], 0));
+	uint32_t c = 0;
+	for (uint64_t p0 = 0; p0 < s.n; p0 += chunk, ++c) {
+		const uint64_t p1 = std::min<uint64_t>(p0 + chunk, s.n), count = p1 - p0;
+		if (s.soa)
+			CUDA_TRY(cudaMemcpy2DAsync(h->d_points_owned + p0, (size_t)s.n * sizeof(float), host_points + p0, (size_t)s.n * sizeof(float),
+				(size_t)count * sizeof(float), s.dim, cudaMemcpyHostToDevice, h->copy_stream));
+		else
+			CUDA_TRY(cudaMemcpyAsync(h->d_points_owned + (size_t)p0 * s.dim, host_points + (size_t)p0 * s.dim, (size_t)count * s.dim * sizeof(float),
+				cudaMemcpyHostToDevice, h->copy_stream));
+		CUDA_TRY(cudaEventRecord(h->copy_ev[c], h->copy_stream));
+		CUDA_TRY(cudaStreamWaitEvent(h->stream, h->copy_ev[c], 0));
+		if (c == 0) CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, h->stream, nullptr, count));
+		// the last chunk also takes the padding rows behind the last point
+		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, h->stream, nullptr,
+			p0, p1 == s.n ? h->ws.tp.n_pad : p1));
+	}
 	return BKM_OK;
 }
 
@@ -831,6 +887,11 @@ int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_m
 	const size_t bytes = (size_t)h->shape.n * h->shape.dim * sizeof(float);
 	if (!h->d_points_owned) CUDA_TRY(cudaMalloc(&h->d_points_owned, bytes));
 	h->d_points = h->d_points_owned;
+	if (h->assign_variant == BKM_ASSIGN_TC && bytes >= ((size_t)32 << 20)) {
+		int rc = initialize_begin(h, host_means, cudaMemcpyHostToDevice);
+		if (!rc) rc = upload_and_split(h, host_points);
+		return rc ? rc : initialize_finish(h, true);
+	}
 	CUDA_TRY(cudaMemcpyAsync(h->d_points_owned, host_points, bytes, cudaMemcpyHostToDevice, h->stream));
 	return initialize_common(h, host_means, cudaMemcpyHostToDevice);
 }

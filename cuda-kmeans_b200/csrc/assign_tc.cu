@@ -91,14 +91,15 @@ bool assign_tc_supported(const Shape& s)
 // points for SoA, along dims for AoS) and the write (along dims) are coalesced.
 template<bool SOA>
 __global__ void __launch_bounds__(256) split_points_kernel(const float* __restrict__ pts, float* __restrict__ a_hi,
-	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t n_pad, uint32_t d, uint32_t d_pad,
+	float* __restrict__ a_lo, float* __restrict__ xnorm, uint64_t n, uint64_t p_begin, uint64_t p_end, uint32_t d, uint32_t d_pad,
 	const float* __restrict__ center, Control* __restrict__ ctl, const uint32_t* __restrict__ skip_if)
 {
 	if (skip_if && *skip_if) return;
 	float local_max = 0.0f;
 	__shared__ float tile[32][33];
 	const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
-	for (uint64_t p0 = (uint64_t)blockIdx.x * 32; p0 < n_pad; p0 += (uint64_t)gridDim.x * 32) {
+	// rows [p_begin, p_end) of the planes (both multiples of 32); rows at or behind n are padding
+	for (uint64_t p0 = p_begin + (uint64_t)blockIdx.x * 32; p0 < p_end; p0 += (uint64_t)gridDim.x * 32) {
 		float norm[4] = {0.f, 0.f, 0.f, 0.f};
 		for (uint32_t c0 = 0; c0 < d_pad; c0 += 32) {
 			__syncthreads();
@@ -146,13 +147,14 @@ __global__ void __launch_bounds__(256) split_points_kernel(const float* __restri
 // One block per dimension: mean of that coordinate over at most 65536 evenly spaced points.
 template<bool SOA>
 __global__ void __launch_bounds__(256) compute_center_kernel(const float* __restrict__ pts, float* __restrict__ center,
-	uint64_t n, uint32_t d, const uint32_t* __restrict__ skip_if)
+	uint64_t n, uint64_t n_sampled, uint32_t d, const uint32_t* __restrict__ skip_if)
 {
 	if (skip_if && *skip_if) return;
 	__shared__ float part[256];
 	const uint32_t j = blockIdx.x;
-	const uint64_t samples = n < 65536 ? n : 65536;
-	const uint64_t stride = n / samples;
+	// the sample is taken from the first n_sampled points
+	const uint64_t samples = n_sampled < 65536 ? n_sampled : 65536;
+	const uint64_t stride = n_sampled / samples;
 	float sum = 0.0f;
 	for (uint64_t t = threadIdx.x; t < samples; t += 256) {
 		const uint64_t i = t * stride;
@@ -167,20 +169,24 @@ __global__ void __launch_bounds__(256) compute_center_kernel(const float* __rest
 	if (threadIdx.x == 0) center[j] = part[0] / (float)samples;
 }
 
-cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream, const uint32_t* skip_if)
+cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream, const uint32_t* skip_if,
+	uint64_t n_sampled)
 {
-	if (s.soa) compute_center_kernel<true><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim, skip_if);
-	else compute_center_kernel<false><<<s.dim, 256, 0, stream>>>(pts, center, s.n, s.dim, skip_if);
+	if (n_sampled == 0 || n_sampled > s.n) n_sampled = s.n;
+	if (s.soa) compute_center_kernel<true><<<s.dim, 256, 0, stream>>>(pts, center, s.n, n_sampled, s.dim, skip_if);
+	else compute_center_kernel<false><<<s.dim, 256, 0, stream>>>(pts, center, s.n, n_sampled, s.dim, skip_if);
 	return cudaGetLastError();
 }
 
 cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream,
-	const uint32_t* skip_if)
+	const uint32_t* skip_if, uint64_t p_begin, uint64_t p_end)
 {
-	const uint64_t groups = tp.n_pad / 32;
+	if (p_end == 0 || p_end > tp.n_pad) p_end = tp.n_pad;
+	if ((p_begin & 31u) != 0 || (p_end & 31u) != 0 || p_begin >= p_end) return cudaErrorInvalidValue;
+	const uint64_t groups = (p_end - p_begin) / 32;
 	const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, (uint64_t)current_sm_count() * 16);
-	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl, skip_if);
-	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, tp.n_pad, s.dim, tp.d_pad, center, ctl, skip_if);
+	if (s.soa) split_points_kernel<true><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, p_begin, p_end, s.dim, tp.d_pad, center, ctl, skip_if);
+	else split_points_kernel<false><<<grid, 256, 0, stream>>>(pts, tp.a_hi, tp.a_lo, tp.xnorm, s.n, p_begin, p_end, s.dim, tp.d_pad, center, ctl, skip_if);
 	return cudaGetLastError();
 }
 

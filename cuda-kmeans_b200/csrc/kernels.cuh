@@ -135,11 +135,15 @@ cudaError_t launch_assign_simt(const float* pts, const SimtMeans& sm, uint32_t* 
 bool assign_tc_supported(const Shape& s);
 uint32_t tc_kpad(uint32_t k);
 // One-off split of the points into tf32 hi/lo K-major planes + |x|^2.
+// `p_begin`, `p_end` (multiples of 32; 0, 0 = all): only these rows of the planes, so that a host upload
+// can be split chunk by chunk while the next chunk is on its way.
 cudaError_t launch_split_points(const float* pts, const Shape& s, const TcPoints& tp, const float* center, Control* ctl, cudaStream_t stream,
-	const uint32_t* skip_if = nullptr);
+	const uint32_t* skip_if = nullptr, uint64_t p_begin = 0, uint64_t p_end = 0);
 // center[j] = mean of dimension j over a strided sample of the points (any vector would do; the
 // sample mean keeps the shifted norms small).
-cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream, const uint32_t* skip_if = nullptr);
+// `n_sampled` (0 = all): the sample is taken from the first n_sampled points only.
+cudaError_t launch_compute_center(const float* pts, const Shape& s, float* center, cudaStream_t stream, const uint32_t* skip_if = nullptr,
+	uint64_t n_sampled = 0);
 // Opaque per-handle state (tensor maps).  Created once the operand buffers exist.
 struct TcPlan;
 TcPlan* tc_plan_create(const Shape& s, const TcPoints& tp, const TcMeans& tm, int device, const char** err);

@@ -197,6 +197,18 @@ def test_fused_update_matches_separate_update(pkg, torch_cuda, oracle_mod, workl
         km.cleanup()
 
 
+@pytest.mark.parametrize("layout", [0, 1])
+def test_host_upload_in_chunks(pkg, torch_cuda, oracle_mod, workloads, layout):
+    """Host points of 32 MB and more travel in chunks, each split into the tensor-core operands while
+    the next is on its way (the centre comes from the first chunk); n is no multiple of the chunk
+    or tile sizes.  Every point against the oracle, for both layouts."""
+    n, k, d = 350003, 96, 24
+    rows = workloads.generate_rows("mixture", n, d, 32, seed=23, sigma=0.05)
+    data, means = workloads.to_layout(rows, layout), workloads.to_layout(np.ascontiguousarray(rows[:k]), layout)
+    total_exact, info = _stepwise(pkg, oracle_mod, data, means, n, k, d, 2, layout, layout)
+    assert info["assign_variant"] == "tc"
+
+
 def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
     """Headline configuration at full size: conservation laws + a sampled oracle check."""
     data, means, spec = workloads.make("c2")
