@@ -246,14 +246,16 @@ int check_shape(uint64_t n, uint32_t k, uint32_t dim, int layout, int layout_mea
 // points it reassigns, so no update pass must follow.
 int enqueue_assign(int variant, const float* pts, const float* means, uint32_t* asg, const bkm::Shape& s,
 	const Workspace& w, int slot, bkm::TcPlan* plan, float margin_scale, int sm_count, cudaStream_t stream,
-	cudaEvent_t mid, const bkm::FusedAcc* fused = nullptr)
+	cudaEvent_t mid, const bkm::FusedAcc* fused = nullptr, bool fast_pass_done = false)
 {
 	if (variant == BKM_ASSIGN_EXACT) {
 		CUDA_TRY(bkm::launch_assign_exact(pts, means, asg, s, nullptr, nullptr, sm_count, stream));
 		if (mid) CUDA_TRY(cudaEventRecord(mid, stream));
 		return BKM_OK;
 	}
-	if (variant == BKM_ASSIGN_SIMT) {
+	if (fast_pass_done) {
+		// (the pass ran behind the upload of the points: only the near-ties are left)
+	} else if (variant == BKM_ASSIGN_SIMT) {
 		CUDA_TRY(bkm::launch_assign_simt(pts, w.sm, asg, s, w.ctl, slot, w.flag_list, margin_scale, sm_count, stream, fused));
 	} else {
 		CUDA_TRY(bkm::launch_assign_tc(plan, asg, w.ctl, slot, w.flag_list, margin_scale, stream, fused));
@@ -276,6 +278,9 @@ struct bkm_handle_s {
 	static constexpr uint32_t UPLOAD_CHUNKS = 8;
 	cudaStream_t copy_stream = nullptr;            // host points travel here chunk by chunk (tensor-core path)
 	cudaEvent_t copy_ev[UPLOAD_CHUNKS] = {};       // chunk c has arrived
+	// The fast assignment pass of the first iteration has already run, chunk by chunk behind the upload
+	// (against the initial means, with or without the update sums): the first bkm_run only re-checks.
+	bool first_pass_done = false, first_pass_fused = false;
 	const float* d_points = nullptr;
 	float* d_points_owned = nullptr;
 	float* d_means[2] = {nullptr, nullptr};
@@ -734,12 +739,20 @@ int bkm_set_stream(bkm_handle_t h, void* stream)
 	return BKM_OK;
 }
 
+static int drop_first_pass(bkm_handle_t h);
+
 int bkm_set_option(bkm_handle_t h, const char* name, double value)
 {
 	if (!h || !name) return fail(BKM_ERR_INVALID, "null argument");
 	if (!h->shards.empty()) {
 		for (bkm_handle_s* c : h->shards) { const int rc = bkm_set_option(c, name, value); if (rc) return rc; }
 		return BKM_OK;
+	}
+	if (!strcmp(name, "margin_scale") || !strcmp(name, "tc_pair") || !strcmp(name, "fuse_update")) {
+		// a first pass that ran behind the upload used the old setting
+		CUDA_TRY(cudaSetDevice(h->cfg.device));
+		const int rc = drop_first_pass(h);
+		if (rc) return rc;
 	}
 	if (!strcmp(name, "margin_scale")) {
 		if (!(value > 0.0)) return fail(BKM_ERR_INVALID, "margin_scale must be positive");
@@ -779,6 +792,7 @@ static int initialize_begin(bkm_handle_t h, const float* means, cudaMemcpyKind k
 	const size_t kd = (size_t)s.k * s.dim;
 	cudaStream_t st = h->stream;
 	h->cur = 0; h->slot = 0; h->iters_done = 0; h->ev_count = 0;
+	h->first_pass_done = false;
 	drop_graph(h);
 	CUDA_TRY(cudaMemcpyAsync(h->d_means[0], means, kd * sizeof(float), kind, st));
 	CUDA_TRY(cudaMemsetAsync(h->d_ws, 0, (size_t)(reinterpret_cast<char*>(h->ws.flag_list) - h->d_ws), st));
@@ -789,19 +803,11 @@ static int initialize_begin(bkm_handle_t h, const float* means, cudaMemcpyKind k
 
 // Second part: what is derived from the points (unless the caller has done that chunk by chunk while
 // they arrived: `points_done`), the operands derived from the means, then a wait for all of it.
-static int initialize_finish(bkm_handle_t h, bool points_done)
+// The tensor-core plan and the operands derived from the initial means (the centre must be known).
+static int prepare_plan_and_means(bkm_handle_t h)
 {
 	const bkm::Shape& s = h->shape;
-	cudaStream_t st = h->stream;
-	if (h->assign_variant == BKM_ASSIGN_SIMT) {
-		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
-		CUDA_TRY(bkm::launch_points_norm_max(h->d_points, s, h->ws.tm.center, h->ws.ctl, h->sm_count, st));
-	}
 	if (h->assign_variant == BKM_ASSIGN_TC) {
-		if (!points_done) {
-			CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
-			CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, st));
-		}
 		if (h->plan) { bkm::tc_plan_destroy(h->plan); h->plan = nullptr; }
 		const char* err = nullptr;
 		h->plan = bkm::tc_plan_create(s, h->ws.tp, h->ws.tm, h->cfg.device, &err);
@@ -810,7 +816,27 @@ static int initialize_finish(bkm_handle_t h, bool points_done)
 	}
 	bkm::launch_prepare_means(h->d_means[0], s,
 		h->assign_variant == BKM_ASSIGN_SIMT ? &h->ws.sm : nullptr,
-		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot, st);
+		h->assign_variant == BKM_ASSIGN_TC ? &h->ws.tm : nullptr, h->ws.ctl, h->slot, h->stream);
+	CUDA_TRY(cudaGetLastError());
+	return BKM_OK;
+}
+
+static int initialize_finish(bkm_handle_t h, bool points_done)
+{
+	const bkm::Shape& s = h->shape;
+	cudaStream_t st = h->stream;
+	if (h->assign_variant == BKM_ASSIGN_SIMT) {
+		CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
+		CUDA_TRY(bkm::launch_points_norm_max(h->d_points, s, h->ws.tm.center, h->ws.ctl, h->sm_count, st));
+	}
+	if (!points_done) {
+		if (h->assign_variant == BKM_ASSIGN_TC) {
+			CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, st));
+			CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, st));
+		}
+		const int rc = prepare_plan_and_means(h);
+		if (rc) return rc;
+	}
 	CUDA_TRY(cudaGetLastError());
 	CUDA_TRY(cudaStreamSynchronize(st));
 	h->initialized = true;
@@ -834,6 +860,8 @@ static int upload_and_split(bkm_handle_t h, const float* host_points)
 	for (cudaEvent_t& e : h->copy_ev)
 		if (!e) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
 	const uint64_t chunk = bkm::round_up64((s.n + bkm_handle_s::UPLOAD_CHUNKS - 1) / bkm_handle_s::UPLOAD_CHUNKS, 4096);
+	bkm::FusedAcc fa{h->ws.acc, h->ws.counts, h->ws.replicas, bkm::acc_replica_stride(s.k, s.dim), h->ws.tm.center};
+	bool fused = false, early_pass = false;
 	// the copies must not overtake the clearing of the workspace and of what the previous use left in the planes' consumers
 	CUDA_TRY(cudaEventRecord(h->copy_ev[0], h->stream));
 	CUDA_TRY(cudaStreamWaitEvent(h->copy_stream, h->copy_ev[0], 0));
@@ -848,11 +876,36 @@ static int upload_and_split(bkm_handle_t h, const float* host_points)
 				cudaMemcpyHostToDevice, h->copy_stream));
 		CUDA_TRY(cudaEventRecord(h->copy_ev[c], h->copy_stream));
 		CUDA_TRY(cudaStreamWaitEvent(h->stream, h->copy_ev[c], 0));
-		if (c == 0) CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, h->stream, nullptr, count));
+		if (c == 0) {
+			CUDA_TRY(bkm::launch_compute_center(h->d_points, s, h->ws.tm.center, h->stream, nullptr, count));
+			const int rc = prepare_plan_and_means(h);
+			if (rc) return rc;
+			// On CTA pairs the fast pass of the first iteration follows the upload chunk by chunk as well
+			// (its key constants need the largest |x|^2 of the launch's own points only, and the running
+			// maximum covers those); the first bkm_run then starts at the re-check.
+			fused = h->fuse_update && fuse_pays(h->assign_variant, h->update_variant, h->plan, fa, s, h->fuse_update >= 2);
+			early_pass = bkm::tc_plan_uses_pair(h->plan);
+		}
 		// the last chunk also takes the padding rows behind the last point
 		CUDA_TRY(bkm::launch_split_points(h->d_points, s, h->ws.tp, h->ws.tm.center, h->ws.ctl, h->stream, nullptr,
 			p0, p1 == s.n ? h->ws.tp.n_pad : p1));
+		if (early_pass)
+			CUDA_TRY(bkm::launch_assign_tc(h->plan, h->d_asg, h->ws.ctl, h->slot, h->ws.flag_list, h->margin_scale, h->stream,
+				fused ? &fa : nullptr, p0, p1));
 	}
+	h->first_pass_done = early_pass;
+	h->first_pass_fused = fused;
+	return BKM_OK;
+}
+
+// Forgets a first pass that ran behind the upload (the means or a setting it depended on change):
+// its sums and its near-tie list are cleared, the next iteration runs the pass again.
+static int drop_first_pass(bkm_handle_t h)
+{
+	if (!h->first_pass_done) return BKM_OK;
+	h->first_pass_done = false;
+	CUDA_TRY(cudaMemsetAsync(h->ws.acc, 0, h->ws.acc_bytes, h->stream));
+	CUDA_TRY(cudaMemsetAsync(&h->ws.ctl->flag_count, 0, sizeof(uint32_t), h->stream));
 	return BKM_OK;
 }
 
@@ -890,6 +943,7 @@ int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_m
 	if (h->assign_variant == BKM_ASSIGN_TC && bytes >= ((size_t)32 << 20)) {
 		int rc = initialize_begin(h, host_means, cudaMemcpyHostToDevice);
 		if (!rc) rc = upload_and_split(h, host_points);
+		if (rc) h->first_pass_done = false;
 		return rc ? rc : initialize_finish(h, true);
 	}
 	CUDA_TRY(cudaMemcpyAsync(h->d_points_owned, host_points, bytes, cudaMemcpyHostToDevice, h->stream));
@@ -916,6 +970,7 @@ int bkm_set_means(bkm_handle_t h, const float* host_means)
 	CUDA_TRY(cudaSetDevice(h->cfg.device));
 	const bkm::Shape& s = h->shape;
 	cudaStream_t st = h->stream;
+	{ const int rc = drop_first_pass(h); if (rc) return rc; }
 	CUDA_TRY(cudaMemcpyAsync(h->d_means[h->cur], host_means, (size_t)s.k * s.dim * sizeof(float), cudaMemcpyHostToDevice, st));
 	// the preparation fills cmax2[slot] with atomicMax, so the slot starts from zero
 	CUDA_TRY(cudaMemsetAsync(&h->ws.ctl->cmax2[h->slot], 0, sizeof(float), st));
@@ -941,8 +996,19 @@ static int enqueue_iteration(bkm_handle_t h, cudaEvent_t* ev)
 	const bool fused = h->fuse_update && fuse_pays(h->assign_variant, h->update_variant, h->plan, fa, s, h->fuse_update >= 2);
 	h->last_fused = fused;
 	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + (fused ? 0u : 1u) + 1u;
+	bool fast_pass_done = false;
+	if (h->first_pass_done) {
+		// usable if nothing has happened since bkm_initialize and the sums went where this iteration expects them
+		if (h->iters_done == 0 && h->cur == 0 && h->slot == 0 && h->assign_variant == BKM_ASSIGN_TC && fused == h->first_pass_fused) {
+			fast_pass_done = true;
+			h->first_pass_done = false;
+		} else {
+			const int rc0 = drop_first_pass(h);
+			if (rc0) return rc0;
+		}
+	}
 	int rc = enqueue_assign(h->assign_variant, h->d_points, h->d_means[h->cur], h->d_asg, s, h->ws, h->slot,
-		h->plan, h->margin_scale, h->sm_count, st, ev ? ev[1] : nullptr, fused ? &fa : nullptr);
+		h->plan, h->margin_scale, h->sm_count, st, ev ? ev[1] : nullptr, fused ? &fa : nullptr, fast_pass_done);
 	if (rc) return rc;
 	if (ev) CUDA_TRY(cudaEventRecord(ev[2], st));
 	if (!fused)

@@ -801,10 +801,13 @@ void tc_plan_describe(const TcPlan* p, uint32_t out[4])
 }
 
 cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
-	float margin_scale, cudaStream_t stream, const FusedAcc* fused)
+	float margin_scale, cudaStream_t stream, const FusedAcc* fused, uint64_t p_begin, uint64_t p_end)
 {
 	if (!p) return cudaErrorInvalidValue;
 	if (fused && !tc_plan_can_fuse(p, *fused)) return cudaErrorInvalidValue;
+	// a range of the points: CTA pairs only, in whole steps of two point tiles
+	const bool ranged = p_begin != 0 || p_end != 0;
+	if (ranged && (!tc_plan_uses_pair(p) || p_begin % (2 * TC_MTILE) != 0 || (p_end % (2 * TC_MTILE) != 0 && p_end < p->s.n))) return cudaErrorInvalidValue;
 	const uint32_t n_tiles = (uint32_t)(p->tp.n_pad / TC_MTILE);
 	const uint32_t nblocks = (n_tiles + TC_MA - 1) / TC_MA;
 	const uint32_t grid = std::min<uint32_t>(nblocks, (uint32_t)p->sm_count);
@@ -819,7 +822,9 @@ cudaError_t launch_assign_tc(TcPlan* p, uint32_t* asg, Control* ctl, int slot, u
 	const uint32_t idesc = p->idesc;
 	if (tc_plan_uses_pair(p))
 		return launch_assign_tc_pair(p->a_hi, p->a_lo, p->bh_hi, p->bh_lo, p->tm.b_aug, p->tp.xnorm, asg, p->s.n, n_tiles,
-			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim);
+			p->s.k, p->tm.k_pad, p->tp.d_pad, ksteps_last, p->max_pairs, ctl, slot, flag_list, margin_coef, stream, fused, p->s.dim,
+			ranged ? (uint32_t)(p_begin / (2 * TC_MTILE)) : 0u,
+			ranged ? (uint32_t)((std::min<uint64_t>(p_end, p->tp.n_pad) + 2 * TC_MTILE - 1) / (2 * TC_MTILE)) : 0u);
 	const uint32_t jsplit = plan_jsplit(p);
 	const uint32_t grid_j = jsplit * std::min<uint32_t>(nblocks, (uint32_t)p->sm_count / jsplit);
 	auto kern = (p->s.k == p->tm.k_pad && p->nt_cols % 128 == 0) ? assign_tc_kernel<true> : assign_tc_kernel<false>;

@@ -89,7 +89,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	const float* __restrict__ b_aug, const float* __restrict__ xnorm, uint32_t* __restrict__ asg,
 	uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t n_ctiles, uint32_t kw, uint32_t ksteps, uint32_t idesc,
 	Control* __restrict__ ctl, int slot, uint32_t* __restrict__ flag_list, float margin_coef,
-	float* __restrict__ fuse_acc, uint32_t* __restrict__ fuse_counts, const float* __restrict__ center, uint32_t dim)
+	float* __restrict__ fuse_acc, uint32_t* __restrict__ fuse_counts, const float* __restrict__ center, uint32_t dim,
+	uint32_t step_begin, uint32_t step_end)
 {
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -100,7 +101,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 	const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 	const uint32_t rank = ptx::cluster_ctarank();
 	const uint32_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-	const uint32_t steps_total = (n_tiles + 1) / 2;                // one step = one point tile per CTA
+	// one step = one point tile per CTA; a launch takes steps [step_begin, step_end) (all of them, or the
+	// chunk of the points that has just arrived from the host)
+	const uint32_t steps_total = min(step_end, (n_tiles + 1) / 2);
 	const uint32_t n_units = 2 * n_ctiles;                         // accumulator fills per step
 	const uint32_t peer_abort_addr = ptx::map_to_cta(ptx::smem_u32(&bars->abort_flag), rank ^ 1u);
 
@@ -178,7 +181,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			}
 			uint32_t it = 0;
 			bool ok = true;
-			for (uint32_t step = pair; step < steps_total && ok; step += n_pairs, ++it) {
+			for (uint32_t step = step_begin + pair; step < steps_total && ok; step += n_pairs, ++it) {
 				const uint32_t buf = it % n_abuf, u = it / n_abuf;
 				ok = pair_wait<400>(&bars->a_empty[buf], (u & 1u) ^ 1u, abort_flag, peer_abort_addr);
 				if (!ok) break;
@@ -213,7 +216,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			const uint32_t acc_full_peer = ptx::map_to_cta(acc_full_own, peer);
 			bool ok = pair_wait(&bars->b_full, 0, abort_flag, peer_abort_addr);
 			uint32_t it = 0, c = 0;                 // c counts units: accumulator c % 4, use c / 4
-			for (uint32_t step = pair; step < steps_total && ok; step += n_pairs, ++it) {
+			for (uint32_t step = step_begin + pair; step < steps_total && ok; step += n_pairs, ++it) {
 				const uint32_t buf = it % n_abuf, ua = it / n_abuf;
 				ok = pair_wait(&bars->a_full[buf], ua & 1u, abort_flag, peer_abort_addr);
 				if (!ok) break;
@@ -303,7 +306,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 			if (lane == 0) ptx::mbar_arrive(&bars->a_empty[pend_it % n_abuf]);
 			pending = false;
 		};
-		for (uint32_t step = pair; step < steps_total; step += n_pairs, ++it) {
+		for (uint32_t step = step_begin + pair; step < steps_total; step += n_pairs, ++it) {
 			uint32_t best = 0xFFFFFFFFu, second = 0xFFFFFFFFu, bchunk = 0;
 			const uint64_t p = (uint64_t)(2 * step + rank) * TC_MTILE + row;
 			float xn = 0.0f;
@@ -432,22 +435,24 @@ cudaError_t assign_tc_pair_prepare(int sm_count, int* max_pairs)
 cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_lo, const CUtensorMap& b_hi, const CUtensorMap& b_lo,
 	const float* b_aug, const float* xnorm, uint32_t* asg, uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t d_pad,
 	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream,
-	const FusedAcc* fused, uint32_t dim)
+	const FusedAcc* fused, uint32_t dim, uint32_t step_begin, uint32_t step_end)
 {
 	const uint32_t kw = d_pad == 16 ? 16u : TC_KCHUNK;
 	const uint32_t n_ctiles = k_pad / TC_NT_MAX;
-	const uint32_t steps = (n_tiles + 1) / 2;
-	const uint32_t pairs = std::min<uint32_t>(steps, (uint32_t)max_pairs);
+	const uint32_t steps_all = (n_tiles + 1) / 2;
+	if (step_end == 0 || step_end > steps_all) step_end = steps_all;
+	if (step_begin >= step_end) return cudaErrorInvalidValue;
+	const uint32_t pairs = std::min<uint32_t>(step_end - step_begin, (uint32_t)max_pairs);
 	// c_format = f32 (bit 4), a/b format = tf32 (bits 7.., 10..), K-major both, N>>3 at bit 17, M>>4 at bit 24: M = 256 over the pair, N = 128
 	const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((P2_UNIT_COLS >> 3) << 17) | (((2 * TC_MTILE) >> 4) << 24);
 	if (ksteps == 4)
 		assign_tc_pair_kernel<4><<<2 * pairs, TC_THREADS, P2_ALLOC, stream>>>(a_hi, a_lo, b_hi, b_lo, b_aug, xnorm, asg,
 			n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef,
-			fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim);
+			fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim, step_begin, step_end);
 	else if (ksteps == 3)
 		assign_tc_pair_kernel<3><<<2 * pairs, TC_THREADS, P2_ALLOC, stream>>>(a_hi, a_lo, b_hi, b_lo, b_aug, xnorm, asg,
 			n, n_tiles, k, n_ctiles, kw, ksteps, idesc, ctl, slot, flag_list, margin_coef,
-			fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim);
+			fused ? fused->acc : nullptr, fused ? fused->counts : nullptr, fused ? fused->center : nullptr, dim, step_begin, step_end);
 	else
 		return cudaErrorInvalidValue;       // dim 17..32 only: three or four K steps
 	return cudaGetLastError();

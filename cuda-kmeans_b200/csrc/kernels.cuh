@@ -158,8 +158,10 @@ bool tc_plan_can_fuse(const TcPlan* plan, const FusedAcc& f);
 // out[0] = BKM_PLAN_* code of the kernel the plan launches, out[1] = mean tiles, out[2] = CTAs that
 // share one point block (1 = no split; > 1 implies the partial-result merge kernel).
 void tc_plan_describe(const TcPlan* plan, uint32_t out[4]);
+// `p_begin`, `p_end` (0, 0 = all; CTA-pair plans only; p_begin a multiple of 256, p_end too unless it is
+// the last point): only these points, so that the pass can follow a host upload chunk by chunk.
 cudaError_t launch_assign_tc(TcPlan* plan, uint32_t* asg, Control* ctl, int slot, uint32_t* flag_list,
-	float margin_scale, cudaStream_t stream, const FusedAcc* fused = nullptr);
+	float margin_scale, cudaStream_t stream, const FusedAcc* fused = nullptr, uint64_t p_begin = 0, uint64_t p_end = 0);
 
 // A wait that is made to run out (nothing ever arrives): sets STATUS_WAIT_TIMEOUT in `ctl` after `limit_ns`.
 cudaError_t launch_wait_timeout_selftest(Control* ctl, uint64_t limit_ns, cudaStream_t stream);

@@ -119,6 +119,6 @@ cudaError_t assign_tc_pair_prepare(int sm_count, int* max_pairs);
 cudaError_t launch_assign_tc_pair(const CUtensorMap& a_hi, const CUtensorMap& a_lo, const CUtensorMap& b_hi, const CUtensorMap& b_lo,
 	const float* b_aug, const float* xnorm, uint32_t* asg, uint64_t n, uint32_t n_tiles, uint32_t k, uint32_t k_pad, uint32_t d_pad,
 	uint32_t ksteps, int max_pairs, Control* ctl, int slot, uint32_t* flag_list, float margin_coef, cudaStream_t stream,
-	const FusedAcc* fused, uint32_t dim);
+	const FusedAcc* fused, uint32_t dim, uint32_t step_begin = 0, uint32_t step_end = 0);
 
 } // namespace bkm

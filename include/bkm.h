@@ -233,7 +233,11 @@ int bkm_set_option(bkm_handle_t h, const char* name, double value);
 
 /* initialize(): copies points and initial means from HOST memory, runs the one-off
  * preprocessing of the immutable points, resets the iteration state
- * (headers/cuda.hpp:45-68).  Synchronous. */
+ * (headers/cuda.hpp:45-68).  Synchronous.  Points of 32 MB and more on the tensor-core path
+ * travel in eight chunks (fastest from pinned memory); each chunk is preprocessed while the
+ * next is on its way, and where the assignment runs on CTA pairs the fast pass of the first
+ * iteration follows the chunks as well, so that the first bkm_run starts at its re-check
+ * (bkm_set_means or a changed option before that run discards the early pass). */
 int bkm_initialize(bkm_handle_t h, const float* host_points, const float* host_means);
 
 /* Same with DEVICE pointers.  The points are borrowed, not copied: they must stay valid and

@@ -197,16 +197,47 @@ def test_fused_update_matches_separate_update(pkg, torch_cuda, oracle_mod, workl
         km.cleanup()
 
 
-@pytest.mark.parametrize("layout", [0, 1])
-def test_host_upload_in_chunks(pkg, torch_cuda, oracle_mod, workloads, layout):
+@pytest.mark.parametrize("layout,k", [(0, 96), (1, 96), (0, 300), (1, 300)])
+def test_host_upload_in_chunks(pkg, torch_cuda, oracle_mod, workloads, layout, k):
     """Host points of 32 MB and more travel in chunks, each split into the tensor-core operands while
-    the next is on its way (the centre comes from the first chunk); n is no multiple of the chunk
-    or tile sizes.  Every point against the oracle, for both layouts."""
-    n, k, d = 350003, 96, 24
+    the next is on its way (the centre comes from the first chunk); with k = 300 the kernel runs on
+    CTA pairs and the fast pass of the first iteration follows the upload chunk by chunk too.  n is
+    no multiple of the chunk or tile sizes.  Every point against the oracle, for both layouts."""
+    n, d = 350003, 24
     rows = workloads.generate_rows("mixture", n, d, 32, seed=23, sigma=0.05)
     data, means = workloads.to_layout(rows, layout), workloads.to_layout(np.ascontiguousarray(rows[:k]), layout)
     total_exact, info = _stepwise(pkg, oracle_mod, data, means, n, k, d, 2, layout, layout)
     assert info["assign_variant"] == "tc"
+
+
+@pytest.mark.parametrize("change", ["means", "fuse_update", "margin_scale"])
+def test_first_pass_behind_the_upload_is_dropped_when_its_inputs_change(pkg, torch_cuda, oracle_mod, workloads, change):
+    """The fast pass that ran behind the upload used the initial means and the settings of that
+    moment; new means or a changed setting before the first run must make the run start over."""
+    n, k, d, layout = 350003, 300, 24, 1
+    rows = workloads.generate_rows("mixture", n, d, 32, seed=29, sigma=0.05)
+    data, means = workloads.to_layout(rows, layout), workloads.to_layout(np.ascontiguousarray(rows[:k]), layout)
+    km = pkg.KMeans(layout=layout)
+    km.initialize(d, k, n, 1, data, means)
+    start = np.asarray(means, dtype=np.float32).reshape(-1)
+    if change == "means":
+        start = workloads.to_layout(np.ascontiguousarray(rows[1000:1000 + k]), layout).reshape(-1)
+        km.set_means(start)
+    elif change == "fuse_update":
+        km.set_option("fuse_update", 0)
+    else:
+        km.set_option("margin_scale", 2.0)
+    km.run(1)
+    asg, cur, sizes = km.getAssignment(), km.getMeans(), km.getSizes()
+    info = km.counters()
+    km.cleanup()
+    want_asg = oracle_mod.assign(data, start, n, k, d, layout, layout, threads=8)
+    assert np.array_equal(asg, want_asg), int((asg != want_asg).sum())
+    want, want_sizes = oracle_mod.update(data, asg, n, k, d, layout, layout)
+    assert np.array_equal(sizes, want_sizes)
+    ok, err = means_close(cur, want)
+    assert ok, err
+    assert (info["update_variant"] == "fused") == (change != "fuse_update")
 
 
 def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
