@@ -1090,6 +1090,8 @@ int bkm_run_async(bkm_handle_t h, uint32_t iters)
 	h->launches_per_iter = (h->assign_variant == BKM_ASSIGN_EXACT ? 1u : 2u) + 2u;
 	uint32_t it = 0;
 	if (graph_wanted(h, iters)) {
+		// a replayed graph must hold whole iterations: a fast pass that ran behind the upload is not used
+		{ const int rc0 = drop_first_pass(h); if (rc0) return rc0; }
 		if (!h->graph_exec || h->graph_cur != h->cur || h->graph_slot != h->slot || h->graph_stream != st) {
 			drop_graph(h);
 			const int cur0 = h->cur, slot0 = h->slot;

@@ -240,6 +240,28 @@ def test_first_pass_behind_the_upload_is_dropped_when_its_inputs_change(pkg, tor
     assert (info["update_variant"] == "fused") == (change != "fuse_update")
 
 
+def test_graph_replay_after_a_chunked_upload(pkg, torch_cuda, workloads):
+    """A replayed CUDA graph holds whole iterations: forced on a problem whose first fast pass ran
+    behind the upload, it must not inherit that short first iteration.  The trajectory stays that of plain launches."""
+    n, k, d, layout = 350003, 300, 24, 1
+    rows = workloads.generate_rows("mixture", n, d, 32, seed=31, sigma=0.05)
+    data, means = workloads.to_layout(rows, layout), workloads.to_layout(np.ascontiguousarray(rows[:k]), layout)
+    outs = []
+    for graph in (1, 0):
+        km = pkg.KMeans(layout=layout)
+        km.initialize(d, k, n, 6, data, means)
+        km.set_option("use_graph", graph)
+        km.run(6)
+        outs.append((km.getAssignment(), km.getMeans(), km.getSizes()))
+        km.cleanup()
+    # The sums are added in an order that differs from run to run, so two trajectories may part by a
+    # few near-tie points after six iterations; a graph without its fast pass would part by most points.
+    differing = int((outs[0][0] != outs[1][0]).sum())
+    assert differing <= n // 1000, differing
+    assert int(np.abs(outs[0][2].astype(np.int64) - outs[1][2].astype(np.int64)).max()) <= 50
+    assert float(np.abs(outs[0][1] - outs[1][1]).max()) < 1e-2
+
+
 def test_full_size_c2_properties(pkg, torch_cuda, oracle_mod, workloads):
     """Headline configuration at full size: conservation laws + a sampled oracle check."""
     data, means, spec = workloads.make("c2")
