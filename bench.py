@@ -45,6 +45,7 @@ V100_PUBLISHED_GEVALS = 84.4  # reference's best variant, N=2M d=32 k=1024, V100
 # the point operands, read once, so it grows in proportion to the points.
 C2_ASSIGN_TC_DRAM_BYTES_PER_POINT = (138.81e6 + 6.79e6) / (1 << 19)
 PARITY_SAMPLE = 4096
+PHASE_STEPS = 8     # instrumented iterations behind the timed ones, for `phases_ms`
 
 
 def parse_args():
@@ -304,6 +305,9 @@ def timed_run(ctx, km, steps, warmup, sample_clocks=True):
     # exchange.  So the last warm-up step is enqueued behind the barrier, directly in front of the
     # timed steps: its exchange lines the ranks' streams up, and the events bracket exactly `steps`
     # iterations that all GPUs start together.
+    # The timed steps run without the library's per-phase events (six records per iteration cost 2-5 %);
+    # the phase times come from PHASE_STEPS instrumented iterations behind them.
+    km.set_option("phase_timing", 0)
     km.run(max(warmup - 1, 0))
     barrier()
     sampler = ClockSampler(physical_gpu_index(ctx["local_rank"])) if sample_clocks else None
@@ -321,6 +325,9 @@ def timed_run(ctx, km, steps, warmup, sample_clocks=True):
     km.synchronize()
     clocks = sampler.stop() if sampler else None
     ms_total = e0.elapsed_time(e1)
+    km.set_option("phase_timing", 1)
+    km.run(PHASE_STEPS)
+    barrier()
     phases = km.phase_ms()
     counters = km.counters()
     by_rank = None
@@ -625,7 +632,10 @@ def main():
                 "dtype": "f32", "data": "synthetic", "config": config, "e2e": e2e,
                 "gpu_launches": counters["launches_per_iter"] * args.steps,
                 "roofline": roofline, "iteration_roofline": iteration_roofline, "cpu_baseline": cpu_baseline,
-                "clocks": clocks, "phases_ms": phases, "phases_ms_across_ranks": by_rank, "variants": counters, "plan": plan,
+                "clocks": clocks, "phases_ms": phases, "phases_ms_across_ranks": by_rank,
+                "phases_from": "%d iterations with the library's per-phase CUDA events, directly behind the timed steps "
+                               "(which run without them)" % PHASE_STEPS,
+                "variants": counters, "plan": plan,
                 "exchange": exchange_used["mode"], "parity": parity,
                 "ns_per_input_float": ms_step * 1e6 / (n_total * dim),
                 "c5_strong": c5_strong, "configs": configs}

@@ -219,7 +219,8 @@ int bkm_destroy(bkm_handle_t h);
 int bkm_set_stream(bkm_handle_t h, void* stream);
 
 /* Tunables: "margin_scale" (multiplier on the near-tie band, default 1), "phase_timing"
- * (0/1: record per-phase CUDA events, default 1), "use_graph" (0 never, 1 always, 2 = default:
+ * (0/1: record per-phase CUDA events for the last 8 iterations of a run, default 1; they cost
+ * 2-5 % of those iterations), "use_graph" (0 never, 1 always, 2 = default:
  * replay a CUDA graph of two iterations when the problem is small enough to be bound by launch
  * latency; single GPU only), "tc_pair" (0/1, default 1: let the tensor-core assignment run on CTA
  * pairs with all means resident in shared memory where the shape allows, i.e. 257..1024 means
@@ -273,7 +274,7 @@ int bkm_set_means(bkm_handle_t h, const float* host_means);
 int bkm_iterations_done(bkm_handle_t h, uint64_t* out);
 
 /* Device time per phase, averaged over the iterations of the most recent run (at most the
- * last 256), in milliseconds: out[0]=assignment pass, out[1]=exact re-check of near-ties,
+ * last 8), in milliseconds: out[0]=assignment pass, out[1]=exact re-check of near-ties,
  * out[2]=update, out[3]=all-reduce, out[4]=divide + operand preparation, out[5]=whole
  * iteration.  Taken with CUDA events on the handle's stream. */
 int bkm_phase_ms(bkm_handle_t h, float out[6]);
