@@ -326,7 +326,7 @@ def timed_run(ctx, km, steps, warmup, sample_clocks=True):
     clocks = sampler.stop() if sampler else None
     ms_total = e0.elapsed_time(e1)
     km.set_option("phase_timing", 1)
-    km.run(PHASE_STEPS)
+    km.run(PHASE_STEPS + 1)     # the library records the last PHASE_STEPS; the one in front lines the ranks up again
     barrier()
     phases = km.phase_ms()
     counters = km.counters()
