@@ -44,6 +44,11 @@ V100_PUBLISHED_GEVALS = 84.4  # reference's best variant, N=2M d=32 k=1024, V100
 # moves per point: the capture ran on 2^19 points (138.81 MB read + 6.79 MB written); the traffic is
 # the point operands, read once, so it grows in proportion to the points.
 C2_ASSIGN_TC_DRAM_BYTES_PER_POINT = (138.81e6 + 6.79e6) / (1 << 19)
+# the same for the one-CTA tensor-core kernel on c5's shape (2^24-point capture: 2.215 GB read, 67.8 MB written)
+# and for the CUDA-core kernel on c3's shape (2^22-point capture: 33.6 MB read; the 16.8 MB of assignments
+# stayed in L2 at that size and are counted as written)
+C5_ASSIGN_TC_DRAM_BYTES_PER_POINT = (2.215e9 + 67.8e6) / (1 << 24)
+C3_ASSIGN_SIMT_DRAM_BYTES_PER_POINT = (33.6e6 + 16.8e6) / (1 << 22)
 PARITY_SAMPLE = 4096
 PHASE_STEPS = 8     # instrumented iterations behind the timed ones, for `phases_ms`
 
@@ -412,7 +417,11 @@ def roofline_of(ctx, job, phases, counters, plan, ms_step, tf32_peak):
     if assign_ms > 0:
         if counters["assign_variant"] == "tc":
             ach = flops_iter / (assign_ms * 1e-3) / 1e12
-            traffic = C2_ASSIGN_TC_DRAM_BYTES_PER_POINT * job.count if (job.name == "c2" and plan["kernel"] == "tc_pair") else None
+            traffic = None
+            if job.name == "c2" and plan["kernel"] == "tc_pair":
+                traffic = C2_ASSIGN_TC_DRAM_BYTES_PER_POINT * job.count
+            elif job.name == "c5" and plan["kernel"] == "tc_resident":
+                traffic = C5_ASSIGN_TC_DRAM_BYTES_PER_POINT * job.count
             ksteps = (min(dim, 32) + 7) // 8 if dim <= 32 else None
             issued = (3.0 * ksteps + 1.0) / ksteps if ksteps else 3.0 + 8.0 / dim
             roofline = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
@@ -421,7 +430,7 @@ def roofline_of(ctx, job, phases, counters, plan, ms_step, tf32_peak):
                         "tensor_flops_per_algorithmic_flop": issued,
                         "frac_vs_half_bf16_burst": ach / (peaks["bf16_tflops"] * 0.5),
                         "traffic": traffic,
-                        "traffic_unit": "bytes per launch (profiler DRAM read+write per point of a 2^19-point capture x points of this launch)",
+                        "traffic_unit": "bytes per launch (profiler DRAM read+write per point of a reduced-size capture x points of this launch)",
                         "kernel": "assignment (%s)" % plan["kernel"], "kernel_ms": assign_ms,
                         "peak_note": "peak = TF32 library GEMM (8192^3, best of 10) measured in this run; `frac` counts "
                                      "algorithmic flops 2*N*k*d; the split-TF32 scheme issues `tensor_flops_per_algorithmic_flop` "
@@ -430,7 +439,9 @@ def roofline_of(ctx, job, phases, counters, plan, ms_step, tf32_peak):
         else:
             ach = bytes_iter / (assign_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                        "frac": ach / peaks["hbm_gbs"],
+                        "traffic": C3_ASSIGN_SIMT_DRAM_BYTES_PER_POINT * job.count if job.name == "c3" else None,
+                        "traffic_unit": "bytes per launch (profiler DRAM read+write per point of a reduced-size capture x points of this launch)",
                         "kernel": "assignment (%s)" % plan["kernel"], "kernel_ms": assign_ms,
                         "peak_note": "%s HBM copy bandwidth; algorithmic bytes 4*N*d" % peaks["source"]}
     # the contractual whole-iteration roofline: slower of 2Nkd flops at the TF32 rate and 4Nd bytes at HBM bandwidth
