@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const floa
 		float x[D];
 		#pragma unroll
 		for (int j = 0; j < D; ++j) x[j] = pts[at<SOA>(i, j, n, D)];
-		float best = 0.0f;
+		float best = 0.0f, best_sum = 0.0f;
 		uint32_t bidx = 0;
 		for (uint32_t m = 0; m < k; ++m) {
 			float c[D];
@@ -380,8 +380,17 @@ __global__ void __launch_bounds__(256) assign_exact_list_small_kernel(const floa
 				const float diff = __fsub_rn(x[j], c[j]);
 				sum = __fadd_rn(sum, __fmul_rn(diff, diff));
 			}
-			const float dist = __fsqrt_rn(sum);
-			if (m == 0 || dist < best) { best = dist; bidx = m; }
+			// The reference compares square roots.  The correctly rounded square root never decreases
+			// with its argument, so a sum that is not below the best sum cannot give a smaller root:
+			// only the few candidates that are below it need the root itself (equal roots of different
+			// sums keep the earlier mean, as the reference's strict comparison does).
+			if (m == 0) {
+				best_sum = sum;
+				best = __fsqrt_rn(sum);
+			} else if (sum < best_sum) {
+				const float dist = __fsqrt_rn(sum);
+				if (dist < best) { best = dist; best_sum = sum; bidx = m; }
+			}
 		}
 		if (fix_acc) {
 			// the fast pass has already added this point to the sum of the cluster it picked
