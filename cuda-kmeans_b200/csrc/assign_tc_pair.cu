@@ -328,14 +328,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) assig
 					// columns [colhalf*64, +64) of the accumulator are rows h*64.. of CTA colhalf's half of tile j
 					const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * P2_UNIT_COLS + colhalf * 64u;
 					uint32_t v0[32], v1[32];
+					const uint32_t chunk0 = j * 8u + colhalf * 4u + h * 2u;    // in units of 32 means
+					// the second half of the columns travels while the first is reduced
 					ptx::tmem_ld32(taddr, v0);
+					ptx::tmem_ld_wait();
 					ptx::tmem_ld32(taddr + 32, v1);
+					chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
 					ptx::tmem_ld_wait();
 					ptx::tc_fence_before();
 					__syncwarp();
 					if (lane == 0) ptx::mbar_arrive_cluster(acc_release);
-					const uint32_t chunk0 = j * 8u + colhalf * 4u + h * 2u;    // in units of 32 means
-					chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
 					chunk_update<false>(v1, key_mult, chunk0 + 1, 32, best, second, bchunk);
 				} else {
 					__syncwarp();
