@@ -592,8 +592,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 						const uint32_t chunk0 = (j * nt_cols + colbase) >> 5;
 						const bool two = FULL ? true : c + 1 < nchunks;
 						uint32_t v0[32], v1[32];
+						const uint32_t col0 = chunk0 * 32u;
+						// columns at or behind k are padding
+						const uint32_t left = FULL ? 64u : (k > col0 ? k - col0 : 0u);
+						const bool plain = FULL || left >= 64 || (!two && left >= 32);
+						// the second chunk travels from tensor memory while the first is reduced
 						ptx::tmem_ld32(taddr, v0);
+						ptx::tmem_ld_wait();
 						if (two) ptx::tmem_ld32(taddr + 32, v1);
+						if (plain) chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
+						else if (left > 0) chunk_update<true>(v0, key_mult, chunk0, left, best, second, bchunk);
 						ptx::tmem_ld_wait();
 						if (c + 2 >= nchunks) {
 							// last load: the tensor cores may fill this accumulator again
@@ -604,15 +612,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(
 							// the chunks just loaded covers the latency
 							if (j == j_end - 1 && half == 0 && p < n) xn = xnorm[p];
 						}
-						// columns at or behind k are padding
-						const uint32_t col0 = chunk0 * 32u;
-						const uint32_t left = FULL ? 64u : (k > col0 ? k - col0 : 0u);
-						if (FULL || left >= 64 || (!two && left >= 32)) {
-							chunk_update<false>(v0, key_mult, chunk0, 32, best, second, bchunk);
+						if (plain) {
 							if (two) chunk_update<false>(v1, key_mult, chunk0 + 1, 32, best, second, bchunk);
-						} else {
-							if (left > 0) chunk_update<true>(v0, key_mult, chunk0, left, best, second, bchunk);
-							if (two && left > 32) chunk_update<true>(v1, key_mult, chunk0 + 1, left - 32, best, second, bchunk);
+						} else if (two && left > 32) {
+							chunk_update<true>(v1, key_mult, chunk0 + 1, left - 32, best, second, bchunk);
 						}
 					}
 				} else {
